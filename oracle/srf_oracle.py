@@ -1,0 +1,174 @@
+"""ctypes binding of the CPU oracle (oracle/libsrf_oracle.so).  TEST INFRASTRUCTURE.
+
+Imported only by tests/, by __graft_entry__.smoke() and by bench.py's CPU-baseline legs; the
+library and the package never import it.  PARITY UNPINNED: see oracle/srf_oracle.h.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+from sphericalrf_b200 import abi
+
+HERE = Path(__file__).resolve().parent
+LIB = HERE / "libsrf_oracle.so"
+
+
+class Model(C.Structure):
+    _fields_ = [("hash_table", C.c_void_p), ("density_mlp", C.c_void_p), ("rgb_mlp", C.c_void_p),
+                ("blobs", C.c_void_p), ("n_blobs", C.c_uint32), ("color_map", C.c_void_p)]
+
+
+class Rng(C.Structure):
+    _fields_ = [("state", C.c_uint64), ("inc", C.c_uint64)]
+
+
+def build(force=False):
+    srcs = [HERE / "srf_oracle.cpp", HERE / "srf_oracle.h", HERE.parent / "include" / "srf_abi.h",
+            HERE.parent / "include" / "srf_canon_math.h"]
+    if force or not LIB.exists() or any(s.stat().st_mtime > LIB.stat().st_mtime for s in srcs):
+        subprocess.run(["make", "-C", str(HERE)], check=True, capture_output=True)
+    return LIB
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        _lib = C.CDLL(str(LIB))
+        _lib.srfo_shard_ray_count.restype = C.c_uint64
+    return _lib
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+class Oracle:
+    """Holds a configuration, a bitfield and model arrays; numpy in, numpy out."""
+
+    def __init__(self, cfg: abi.Config, bitfield=None, hash_table=None, density_mlp=None, rgb_mlp=None,
+                 blobs=None, color_map=None):
+        self.cfg = cfg
+        self.bitfield = None if bitfield is None else np.ascontiguousarray(bitfield, dtype=np.uint8)
+        self._keep = [np.ascontiguousarray(a) if a is not None else None
+                      for a in (hash_table, density_mlp, rgb_mlp, blobs, color_map)]
+        ht, dm, rm, bl, cm = self._keep
+        self.model = Model()
+        self.model.hash_table = None if ht is None else ht.ctypes.data
+        self.model.density_mlp = None if dm is None else dm.ctypes.data
+        self.model.rgb_mlp = None if rm is None else rm.ctypes.data
+        self.model.blobs = None if bl is None else bl.ctypes.data
+        self.model.n_blobs = 0 if bl is None else bl.shape[0]
+        self.model.color_map = None if cm is None else cm.ctypes.data
+
+    def n_rays(self, view):
+        return int(lib().srfo_shard_ray_count(C.byref(view)))
+
+    def generate_rays(self, view):
+        n = self.n_rays(view)
+        d = np.zeros((n, 3), np.float32); t = np.zeros(n, np.float32)
+        alive = np.zeros(n, np.uint8); pixel = np.zeros(n, np.uint32)
+        rc = lib().srfo_generate_rays(C.byref(self.cfg), C.byref(view), _p(self.bitfield), _p(d), _p(t), _p(alive), _p(pixel))
+        assert rc == 0
+        return d, t, alive, pixel
+
+    def march(self, view, ray_first, ray_count, capacity):
+        counts = np.zeros(ray_count, np.uint32)
+        pos_dt = np.zeros((capacity, 4), np.float32)
+        ordinal = np.zeros(capacity, np.uint32); cell = np.zeros(capacity, np.uint32)
+        n_total = C.c_uint64(0); n_steps = C.c_uint64(0)
+        rc = lib().srfo_march(C.byref(self.cfg), C.byref(view), _p(self.bitfield), C.c_uint64(ray_first),
+                              C.c_uint64(ray_count), C.c_uint64(capacity), _p(counts), _p(pos_dt), _p(ordinal),
+                              _p(cell), C.byref(n_total), C.byref(n_steps))
+        if rc != 0:
+            raise RuntimeError(f"oracle march: capacity {capacity} < {n_total.value}")
+        n = n_total.value
+        return counts, pos_dt[:n], ordinal[:n], cell[:n], n_steps.value
+
+    def network_inference(self, coords):
+        coords = np.ascontiguousarray(coords, np.float32)
+        n = coords.shape[0]
+        out = np.zeros((n, 4), np.float16)
+        rc = lib().srfo_network_inference(C.byref(self.cfg), C.byref(self.model), _p(coords), C.c_uint64(n), _p(out))
+        assert rc == 0
+        return out
+
+    def network_density(self, positions):
+        positions = np.ascontiguousarray(positions, np.float32)
+        n = positions.shape[0]
+        out = np.zeros((n, 16), np.float16)
+        rc = lib().srfo_network_density(C.byref(self.cfg), C.byref(self.model), _p(positions), C.c_uint64(n), _p(out))
+        assert rc == 0
+        return out
+
+    def render_frame(self, view, post, ray_first=0, ray_count=0, accum=None):
+        n = self.n_rays(view)
+        out = np.zeros((n, 4), np.float32)
+        accum = np.zeros((n, 4), np.float32) if accum is None else accum
+        raw = np.zeros((n, 4), np.float32)
+        ns = np.zeros(n, np.uint32); nc = np.zeros(n, np.uint32)
+        stats = abi.FrameStats()
+        rc = lib().srfo_render_frame(C.byref(self.cfg), C.byref(view), C.byref(post), _p(self.bitfield),
+                                     C.byref(self.model), C.c_uint64(ray_first), C.c_uint64(ray_count), _p(out),
+                                     _p(accum), _p(raw), _p(ns), _p(nc), C.byref(stats))
+        assert rc == 0
+        return dict(out=out, accum=accum, rgba_raw=raw, n_samples=ns, n_composited=nc, stats=stats.as_dict())
+
+    def update_grid_bitfield(self, grid):
+        grid = np.ascontiguousarray(grid, np.float32)
+        bits = np.zeros(grid.shape[0] // 8, np.uint8)
+        mean = C.c_float(0)
+        rc = lib().srfo_update_grid_bitfield(C.byref(self.cfg), _p(grid), _p(bits), C.byref(mean))
+        assert rc == 0
+        return bits, np.float32(mean.value)
+
+    def refresh(self, grid, refresh_step, training_step, rng: Rng):
+        """In-place max-decay refresh of `grid`; returns (bitfield, mean, next refresh_step)."""
+        assert grid.dtype == np.float32 and grid.flags.c_contiguous
+        bits = np.zeros(grid.shape[0] // 8, np.uint8)
+        mean = C.c_float(0)
+        step = C.c_uint32(refresh_step)
+        rc = lib().srfo_refresh_grid(C.byref(self.cfg), C.byref(self.model), _p(grid), _p(bits), C.byref(mean),
+                                     C.byref(step), C.c_uint32(training_step), C.byref(rng))
+        assert rc == 0
+        return bits, np.float32(mean.value), step.value
+
+
+def rng_seed(seed) -> Rng:
+    r = Rng()
+    lib().srfo_rng_seed(C.byref(r), C.c_uint64(seed))
+    return r
+
+
+def eval_math(op, a, b=None):
+    a = np.ascontiguousarray(a, np.float32)
+    b = np.zeros_like(a) if b is None else np.ascontiguousarray(b, np.float32)
+    out = np.zeros_like(a)
+    rc = lib().srfo_eval_math(C.c_int(op), _p(a), _p(b), _p(out), C.c_size_t(a.size))
+    assert rc == 0
+    return out
+
+
+def warp_position(cfg, pos, inverse=False):
+    pos = np.ascontiguousarray(pos, np.float32)
+    out = np.zeros_like(pos)
+    lib().srfo_warp_position(C.byref(cfg), _p(pos), _p(out), C.c_size_t(pos.shape[0]), C.c_int(1 if inverse else 0))
+    return out
+
+
+def hashgrid_layout(cfg):
+    off = np.zeros(cfg.n_levels + 1, np.uint32); res = np.zeros(cfg.n_levels, np.uint32)
+    sc = np.zeros(cfg.n_levels, np.float32)
+    lib().srfo_hashgrid_layout(C.byref(cfg), _p(off), _p(res), _p(sc))
+    return off, res, sc
+
+
+def num_threads():
+    return int(lib().srfo_num_threads())
