@@ -1,0 +1,305 @@
+#!/usr/bin/env python
+"""Benchmark of the render hot path (rays/s), one JSON line on stdout.
+
+Workload: the full inference frame of the seed-generated configuration 1 (1245x825, camera inside
+the unit sphere, 128^3 spherical occupancy bitfield, 16x2 hash grid with 2^19 entries per level,
+64-wide fp16 MLPs, random-init parameters; synthetic stand-in for the datasets the reference is
+evaluated on).  A step renders N such frames on N GPUs: every frame's rays are cut into blocks
+of 8 image rows dealt round-robin to the ranks (weights, grid and bitfield replicated), and the
+ranks' tiles are gathered on rank 0 over NCCL -- so the work per GPU is one frame's worth of rays
+whatever N is (weak scaling), and N = 1 is exactly one configuration-1 frame per step.
+
+  value : Mrays/s with the camera already on the device side of the call and the image left in HBM
+  e2e   : Mrays/s through srf_render(), the call a user of the reference's Testbed.render makes:
+          camera in host memory, image copied back to (pinned) host memory inside the timed region
+  --impl reference : the CPU oracle (a restatement of the reference's algorithm; the reference
+          itself is GPU-only and cannot be built here) on the host cores, on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WIDTH, HEIGHT = 1245, 825
+ALG_BYTES_PER_SAMPLE = 588.0      # hash encoding: 12 B position + 16 levels x 8 corners x 4 B + 64 B encoded
+ALG_FLOP_PER_SAMPLE = 18816.0     # the two MLPs
+
+
+def _peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_scene():
+    from sphericalrf_b200 import abi, synth
+    sc = synth.scene_config1(grid_size=128, width=WIDTH, height=HEIGHT)
+    return sc
+
+
+def cpu_reference_sample(sc, target_seconds=15.0):
+    """Times the oracle on a bounded stripe of the frame's rays; returns (Mrays/s, cores, description)."""
+    from oracle import srf_oracle
+    from sphericalrf_b200 import abi, synth
+    cfg = sc["cfg"]
+    bits = synth.bitfield_from_grid(cfg, sc["grid"])
+    orc = srf_oracle.Oracle(cfg, bits, sc["hash_table"], sc["density_mlp"], sc["rgb_mlp"])
+    b2, _ = orc.update_grid_bitfield(sc["grid"])
+    orc.bitfield = b2
+    view = abi.make_view(sc["cameras"][0], WIDTH, HEIGHT, sc["rfl"])
+    n = orc.n_rays(view)
+    first = (HEIGHT // 2) * WIDTH
+    probe = 256
+    t0 = time.perf_counter()
+    orc.render_frame(view, abi.default_post(), first, probe)
+    dt = time.perf_counter() - t0
+    count = int(max(probe, min(n - first - probe, probe * target_seconds / max(dt, 1e-3))))
+    t0 = time.perf_counter()
+    res = orc.render_frame(view, abi.default_post(), first + probe, count)
+    dt = time.perf_counter() - t0
+    return count / dt / 1e6, srf_oracle.num_threads(), (f"{count} consecutive rays from the middle rows of the frame "
+                                                        f"({res['stats']['n_samples']} samples), OpenMP over rays"), dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sc = build_scene()
+    vals, cores, desc = [], 1, ""
+    for _ in range(max(0, args.warmup)):
+        cpu_reference_sample(sc, target_seconds=2.0)
+    t_tot = 0.0
+    for _ in range(max(1, args.steps)):
+        v, cores, desc, dt = cpu_reference_sample(sc, target_seconds=12.0)
+        vals.append(v); t_tot += dt
+    value = float(np.mean(vals))
+    line = {
+        "impl": "reference", "metric": "render throughput", "value": value, "unit": "Mrays/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t_tot / max(1, args.steps), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "config1 full inference frame 1245x825, fp16 network, 128^3 bitfield", "rays_per_frame": WIDTH * HEIGHT},
+        "cpu_baseline": {"value": value, "unit": "Mrays/s", "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": "Mrays/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from sphericalrf_b200 import abi
+    from sphericalrf_b200.testbed import Renderer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    n_views = world                                  # frames per step
+
+    sc = build_scene()
+    cfg = sc["cfg"]
+    r = Renderer(cfg, local_rank)
+    r.upload_network(sc["hash_table"], sc["density_mlp"], sc["rgb_mlp"])
+    r.upload_density_grid(sc["grid"])
+    r.update_grid_bitfield()
+    post = abi.default_post()
+    view = abi.make_view(sc["cameras"][0], WIDTH, HEIGHT, sc["rfl"], shard_rows=8, shard_count=world, shard_rank=rank)
+    n_local = r.n_rays(view)
+    rays_per_step = WIDTH * HEIGHT * n_views
+
+    # tiles are padded to the largest shard so that the gather moves equal-sized buffers
+    counts = [r.n_rays(abi.make_view(sc["cameras"][0], WIDTH, HEIGHT, sc["rfl"], shard_rows=8, shard_count=world, shard_rank=k))
+              for k in range(world)]
+    n_pad = max(counts)
+    out = torch.zeros((n_views, n_pad, 4), dtype=torch.float32, device=dev)
+    accum = torch.zeros((n_pad, 4), dtype=torch.float32, device=dev)
+    gathered, pix_index, image = None, None, None
+    if world > 1:
+        if rank == 0:
+            gathered = [torch.zeros((n_views, n_pad, 4), dtype=torch.float32, device=dev) for _ in range(world)]
+            image = torch.zeros((n_views, HEIGHT * WIDTH, 4), dtype=torch.float32, device=dev)
+            pix_index = []
+            for rk in range(world):
+                rows = torch.tensor([y for y in range(HEIGHT) if (y // 8) % world == rk], dtype=torch.int64, device=dev)
+                pix_index.append((rows[:, None] * WIDTH + torch.arange(WIDTH, device=dev)[None, :]).reshape(-1))
+    host_img = torch.zeros((n_views, HEIGHT, WIDTH, 4), dtype=torch.float32).pin_memory() if rank == 0 else None
+    stats = abi.FrameStats()
+
+    def step_device():
+        for k in range(n_views):
+            r.render_frame_device(view, post, out[k], accum, None, None, None, None)
+        if world > 1:
+            dist.gather(out, gathered, dst=0)
+            if rank == 0:
+                for rk in range(world):
+                    image[:, pix_index[rk]] = gathered[rk][:, :counts[rk]]
+
+    def step_e2e():
+        if world == 1:
+            # the reference-facing call: host camera in, host image out
+            st = r.lib.srf_render(r.ctx, C.byref(view), C.byref(post), 1, C.c_void_p(host_img[0].data_ptr()), None)
+            assert st == 0, r.lib.srf_last_error(r.ctx)
+        else:
+            step_device()
+            if rank == 0:
+                host_img.view(n_views, HEIGHT * WIDTH, 4).copy_(image, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+
+    def timed(fn, steps, warmup, sample_clocks=False):
+        for _ in range(warmup):
+            fn()
+        sampler = ClockSampler(local_rank) if (sample_clocks and rank == 0) else None
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        if sampler:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        clocks = sampler.stop() if sampler else None
+        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()), clocks
+
+    ms_total, clocks = timed(step_device, args.steps, args.warmup, sample_clocks=True)
+    ms_step = ms_total / args.steps
+    value = rays_per_step / (ms_step * 1e-3) / 1e6
+    ms_e2e, _ = timed(step_e2e, args.steps, 1)
+    e2e_value = rays_per_step / (ms_e2e / args.steps * 1e-3) / 1e6
+
+    # per-kernel durations of the dominant kernel (field: hash encoding + MLPs), CUDA events inside the library
+    r.set_timing(True)
+    t_field = t_sampler = t_comp = 0.0
+    n_samples = n_batches = 0
+    for _ in range(args.steps):
+        r.render_frame_device(view, post, out[0], accum, None, None, stats, None)
+        t_field += stats.ms_field; t_sampler += stats.ms_sampler; t_comp += stats.ms_composite
+        n_samples = stats.n_samples; n_batches = stats.n_batches
+    r.set_timing(False)
+    t_field /= args.steps; t_sampler /= args.steps; t_comp /= args.steps
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peak, peak_kind = _peaks()
+    launches_per_frame = 4 + 3 * n_batches           # count, 3 scan kernels, then emit/field/composite per batch
+    achieved = ALG_BYTES_PER_SAMPLE * n_samples / max(n_batches, 1) / (t_field / max(n_batches, 1) * 1e-3) / 1e9 if t_field > 0 else 0.0
+    line = {
+        "metric": "render throughput", "value": value, "unit": "Mrays/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "config1 full inference frame 1245x825, fp16 network, 128^3 bitfield",
+                   "frames_per_step": n_views, "rays_per_frame": WIDTH * HEIGHT, "samples_per_frame_shard": int(n_samples),
+                   "partition": f"rows in blocks of 8 round-robin over {world} rank(s), gather to rank 0",
+                   "l2": "per-frame working set (sample buffers) far larger than L2; no flush needed"},
+        "frames_per_s": n_views / (ms_step * 1e-3),
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": "Mrays/s", "h2d_bytes_per_step": int(C.sizeof(abi.View) + C.sizeof(abi.Post)) * n_views,
+                "d2h_bytes_per_step": int(HEIGHT * WIDTH * 16 * n_views)},
+        "gpu_launches": int(launches_per_frame * n_views * args.steps),
+        "roofline": {"kernel": "k_field_network (hash-grid gather + MLPs)", "bound": "hbm", "achieved": achieved, "peak": peak,
+                     "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                     "ms_per_launch": t_field / max(n_batches, 1), "launches_per_frame": int(n_batches),
+                     "mlp_tflops": ALG_FLOP_PER_SAMPLE * n_samples / (t_field * 1e-3) / 1e12 if t_field > 0 else 0.0},
+        "stage_ms": {"sampler": t_sampler, "field": t_field, "composite_output": t_comp},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        v, cores, desc, _ = cpu_reference_sample(sc, target_seconds=15.0)
+        line["cpu_baseline"] = {"value": v, "unit": "Mrays/s", "cores": cores, "kind": "port", "sample": desc}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

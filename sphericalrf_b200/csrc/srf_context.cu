@@ -1,0 +1,849 @@
+// srf_context.cu -- the C-ABI of libsrf_b200.so (include/srf_abi.h): context, parameter upload,
+// stage entry points and the frame loop that replaces Testbed::render_frame
+// (internal/testbed.cu:479-606).
+//
+// Frame loop.  The reference alternates compaction, <= 8 samples per ray, the network and
+// compositing under host control, reading a counter back every iteration.  Here a frame is:
+// count pass -> exclusive scan -> ONE read-back (the sample total and a coarse offset table) ->
+// per batch of rays { emit -> field -> composite+output }.  Batches exist only to bound the
+// sample scratch; a frame whose samples fit the scratch is a single batch.
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "srf_kernels.cuh"
+
+using namespace srf;
+
+namespace {
+
+thread_local std::string g_create_error;
+
+constexpr uint64_t kCoarse = 4096;                    // rays per entry of the coarse offset table
+constexpr uint64_t kAutoSampleCapacity = 256ull << 20;  // default upper bound of the sample scratch
+
+struct DevBuf {
+    void* p = nullptr;
+    size_t bytes = 0;
+};
+
+}  // namespace
+
+struct srf_ctx {
+    srf_config_t cfg;
+    DevCfg g;
+    NetMeta net;
+    int device = 0;
+    std::string err;
+    uint32_t n_table_entries = 0;
+    float min_optical_thickness = 0.01f;
+
+    // model
+    float* grid = nullptr;
+    float* grid_current = nullptr;
+    float* partial_a = nullptr;
+    float* partial_b = nullptr;
+    float* mean = nullptr;
+    uint8_t* bits = nullptr;
+    __half* table = nullptr;
+    __half* w_density = nullptr;
+    __half* w_rgb = nullptr;
+    bool have_net = false;
+    float* blobs = nullptr;
+    float* cmap = nullptr;
+    uint32_t n_blobs = 0;
+
+    // per-frame scratch
+    DevBuf ray_dir_t, ray_end, counts, offsets, scan_scratch;
+    DevBuf pos_dt, sample_ray, rgbs;
+    DevBuf img_out, img_accum;
+    FrameCounters* d_counters = nullptr;
+    FrameCounters* h_counters = nullptr;     // pinned
+    uint64_t* h_coarse = nullptr;            // pinned
+    size_t h_coarse_entries = 0;
+    uint64_t reserve_samples = 0;
+
+    // refresh
+    uint32_t refresh_step = 0;
+    RefreshRng rng = {0, 0};
+
+    // timing
+    bool timing = false;
+    cudaEvent_t ev[8] = {};
+};
+
+namespace {
+
+#define SRF_CK(ctx, call)                                                                      \
+    do {                                                                                       \
+        cudaError_t e_ = (call);                                                               \
+        if (e_ != cudaSuccess) {                                                               \
+            (ctx)->err = std::string(#call) + ": " + cudaGetErrorString(e_);                   \
+            return SRF_ERR_CUDA;                                                               \
+        }                                                                                      \
+    } while (0)
+
+srf_status fail(srf_ctx* ctx, srf_status st, const std::string& msg) {
+    if (ctx) ctx->err = msg; else g_create_error = msg;
+    return st;
+}
+
+srf_status ensure(srf_ctx* ctx, DevBuf& b, size_t bytes) {
+    if (bytes <= b.bytes) return SRF_OK;
+    if (b.p) SRF_CK(ctx, cudaFree(b.p));
+    b.p = nullptr; b.bytes = 0;
+    const size_t want = bytes + bytes / 8;           // grow with slack
+    SRF_CK(ctx, cudaMalloc(&b.p, want));
+    b.bytes = want;
+    return SRF_OK;
+}
+
+float resolved_per_level_scale(const srf_config_t& c) {
+    float pls = c.per_level_scale;
+    if (pls <= 0.f && c.n_levels > 1)
+        pls = std::exp(std::log(c.desired_resolution / (float)c.base_resolution) / (float)(c.n_levels - 1));
+    return pls;
+}
+
+// Level geometry of the hash grid (Mueller et al. 2022): scale_l = base * b^l - 1,
+// resolution_l = ceil(scale_l) + 1, entries_l = min(2^T, round_up(res^3, 8)).
+void build_net_meta(const srf_config_t& c, NetMeta* net) {
+    memset(net, 0, sizeof(*net));
+    net->n_levels = c.n_levels;
+    net->n_features = c.n_features_per_level;
+    const float pls = resolved_per_level_scale(c);
+    const uint64_t T = 1ull << c.log2_hashmap_size;
+    uint32_t off = 0;
+    for (uint32_t l = 0; l < c.n_levels; ++l) {
+        const double s = (double)c.base_resolution * std::pow((double)pls, (double)l) - 1.0;
+        const float sf = (float)s;
+        const uint32_t res = (uint32_t)std::ceil(sf) + 1u;
+        const uint64_t dense = (uint64_t)res * res * res;
+        uint64_t n = (dense + 7ull) / 8ull * 8ull;
+        if (n > T) n = T;
+        net->level[l].scale = sf;
+        net->level[l].res = res;
+        net->level[l].offset = off;
+        net->level[l].size = (uint32_t)n;
+        net->level[l].dense = dense <= n ? 1u : 0u;
+        off += (uint32_t)n;
+    }
+}
+
+uint32_t table_entries(const NetMeta& net) {
+    const LevelMeta& L = net.level[net.n_levels - 1];
+    return L.offset + L.size;
+}
+
+srf_status validate(const srf_config_t* c, std::string* why) {
+    auto bad = [&](const char* m) { *why = m; return SRF_ERR_ARG; };
+    if (!c) return bad("config is NULL");
+    if (c->struct_size != sizeof(srf_config_t)) return bad("srf_config_t.struct_size does not match this library");
+    if (c->version != SRF_ABI_VERSION) return bad("srf_config_t.version does not match this library");
+    if (c->warping_type < 0 || c->warping_type > SRF_WARP_SINUSOIDAL) return bad("Unknown warping type.");
+    if (c->sampling_type < 0 || c->sampling_type > SRF_SAMPLING_LOG) return bad("Unknown sampling type.");
+    if (c->grid_distribution_type < 0 || c->grid_distribution_type > SRF_GRID_METRIC_RECIPROCAL)
+        return bad("Unknown grid distribution type.");
+    if (c->grid_size < 8 || c->grid_size > 1024 || (c->grid_size & (c->grid_size - 1))) return bad("grid_size must be a power of two in [8, 1024]");
+    if (c->num_cascades < 1 || c->num_cascades > 8) return bad("num_cascades must be in [1, 8]");
+    if ((uint64_t)c->grid_size * c->grid_size * c->grid_size * c->num_cascades > (1ull << 31)) return bad("grid too large");
+    if (c->maximum_marching_steps == 0) return bad("maximum_marching_steps must be positive");
+    if (c->aabb_scale == 0) return bad("aabb_scale must be positive");
+    if (c->field_type == SRF_FIELD_NETWORK) {
+        if (c->n_levels * c->n_features_per_level != 32) return bad("n_levels * n_features_per_level must be 32");
+        if (c->n_features_per_level != 2 && c->n_features_per_level != 4) return bad("n_features_per_level must be 2 or 4");
+        if (c->log2_hashmap_size < 10 || c->log2_hashmap_size > 24) return bad("log2_hashmap_size must be in [10, 24]");
+        if (c->base_resolution < 2) return bad("base_resolution must be >= 2");
+    } else if (c->field_type != SRF_FIELD_BLOBS) {
+        return bad("unknown field_type");
+    }
+    if (c->density_activation < 0 || c->density_activation > 3 || c->rgb_activation < 0 || c->rgb_activation > 3)
+        return bad("unknown activation");
+    return SRF_OK;
+}
+
+void resolve(const srf_config_t& c, DevCfg* g, float* min_thick) {
+    memset(g, 0, sizeof(*g));
+    g->warping_type = c.warping_type;
+    g->grid_dist = c.grid_distribution_type;
+    g->sampling_type = c.sampling_type;
+    g->use_grid = c.use_grid;
+    g->grid_size = c.grid_size;
+    g->n_cascades = c.num_cascades;
+    g->cells = c.grid_size * c.grid_size * c.grid_size;
+    const float amount = 0.5f * (float)c.aabb_scale;
+    g->box_min = 0.5f - amount;
+    g->box_max = 0.5f + amount;
+    g->box_diag = g->box_max - g->box_min;
+    const float sqrt3 = 1.73205080757f;
+    g->min_step = c.min_cone_stepsize > 0.f ? c.min_cone_stepsize : sqrt3 / (float)c.maximum_marching_steps;
+    g->max_step = c.max_cone_stepsize > 0.f ? c.max_cone_stepsize
+                : (c.use_grid ? (sqrt3 * (float)(1u << (c.num_cascades - 1)) / (float)c.grid_size) : g->min_step);
+    g->cone_angle = c.cone_angle_constant;
+    g->near_distance = c.near_distance;
+    g->far_distance = c.far_distance;
+    g->ds = 1.f / (float)c.maximum_marching_steps;
+    if (c.sampling_type == SRF_SAMPLING_LOG) {
+        g->g_far = srf_logf(c.far_distance);
+        g->g_near = srf_logf(c.near_distance);
+    } else {
+        g->g_far = 1.f / c.far_distance;
+        g->g_near = 1.f / c.near_distance;
+    }
+    g->g_diff = g->g_far - g->g_near;
+    uint32_t cap = c.march_iter ? c.march_iter - 1 : 9999u;
+    if (c.max_samples_per_ray && c.max_samples_per_ray < cap) cap = c.max_samples_per_ray;
+    g->sample_cap = cap;
+    g->step_limit = 1u << 24;
+    g->snap = c.snap_to_pixel_centers_in_rendering;
+    g->transmittance_keep = 1.0f - c.transmittance_threshold;
+    g->density_activation = c.density_activation;
+    g->rgb_activation = c.rgb_activation;
+    g->train_in_linear_color = c.train_in_linear_color;
+    g->field_type = c.field_type;
+    *min_thick = c.min_optical_thickness;
+}
+
+uint64_t shard_rows_total(const srf_view_t& v) {
+    const uint32_t sr = v.shard_rows ? v.shard_rows : 8, sc = v.shard_count ? v.shard_count : 1;
+    const uint32_t n_blocks = (v.height + sr - 1) / sr;
+    uint64_t rows = 0;
+    for (uint32_t b = v.shard_rank; b < n_blocks; b += sc) rows += std::min(sr, v.height - b * sr);
+    return rows;
+}
+
+srf_status make_view(srf_ctx* ctx, const srf_view_t* view, DevView* v) {
+    if (!view) return fail(ctx, SRF_ERR_ARG, "view is NULL");
+    if (view->width == 0 || view->height == 0) return fail(ctx, SRF_ERR_ARG, "empty image");
+    const uint32_t sc = view->shard_count ? view->shard_count : 1;
+    if (view->shard_rank >= sc) return fail(ctx, SRF_ERR_ARG, "shard_rank >= shard_count");
+    if (view->render_mode == SRF_MODE_NORMALS)
+        return fail(ctx, SRF_ERR_ARG, "render mode Normals needs the network's input gradient, which this library does not provide");
+    if (view->render_mode < 0 || view->render_mode > SRF_MODE_COST) return fail(ctx, SRF_ERR_ARG, "unknown render mode");
+    memset(v, 0, sizeof(*v));
+    memcpy(v->cam, view->camera, sizeof(v->cam));
+    v->width = view->width; v->height = view->height;
+    v->rw = (float)view->width; v->rh = (float)view->height;
+    v->fx = v->rw * view->relative_focal_length[0];          // testbed.cu:483
+    v->fy = v->rh * view->relative_focal_length[1];
+    v->ppx = view->principal_point[0]; v->ppy = view->principal_point[1];
+    v->spp_index = view->spp_index;
+    const bool snap = ctx ? ctx->cfg.snap_to_pixel_centers_in_rendering != 0 : true;
+    ld_random_pixel_offset_host(snap ? 0u : view->spp_index, &v->off_x, &v->off_y);   // common_device.h:152
+    v->render_mode = view->render_mode;
+    v->depth_scale = view->depth_scale;
+    v->shard_rows = view->shard_rows ? view->shard_rows : 8;
+    v->shard_count = sc;
+    v->shard_rank = view->shard_rank;
+    v->n_rays = shard_rows_total(*view) * view->width;
+    return SRF_OK;
+}
+
+float host_powf(float x, float y) { return x > 0.f ? srf_expf(y * srf_logf(x)) : 0.f; }
+float host_srgb_to_linear(float s) { return s <= 0.04045f ? s / 12.92f : host_powf((s + 0.055f) / 1.055f, 2.4f); }
+
+void make_post(const srf_post_t* post, DevPost* p) {
+    srf_post_t def;
+    memset(&def, 0, sizeof(def));
+    def.background_color[3] = 1.f;
+    if (!post) post = &def;
+    p->exposure_scale = host_powf(2.0f, post->exposure);      // render_buffer.cu:155
+    for (int i = 0; i < 4; ++i) p->bg[i] = post->background_color[i];
+    if (post->color_space != SRF_COLOR_SRGB) for (int i = 0; i < 3; ++i) p->bg[i] = host_srgb_to_linear(p->bg[i]);   // :160-162
+    p->color_space = post->color_space;
+    p->tonemap_curve = post->tonemap_curve;
+    p->to_srgb = post->to_srgb;
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) { cudaGetDevice(&prev); if (prev != dev) cudaSetDevice(dev); else prev = -1; }
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+srf_status ensure_ray_buffers(srf_ctx* ctx, uint64_t n_rays) {
+    srf_status st;
+    if ((st = ensure(ctx, ctx->ray_dir_t, n_rays * sizeof(float4))) != SRF_OK) return st;
+    if ((st = ensure(ctx, ctx->ray_end, n_rays)) != SRF_OK) return st;
+    if ((st = ensure(ctx, ctx->counts, n_rays * sizeof(uint32_t))) != SRF_OK) return st;
+    if ((st = ensure(ctx, ctx->offsets, (n_rays + 1) * sizeof(uint64_t))) != SRF_OK) return st;
+    if ((st = ensure(ctx, ctx->scan_scratch, scan_scratch_bytes(n_rays))) != SRF_OK) return st;
+    const size_t coarse = (size_t)(n_rays / kCoarse) + 2;
+    if (coarse > ctx->h_coarse_entries) {
+        if (ctx->h_coarse) cudaFreeHost(ctx->h_coarse);
+        ctx->h_coarse = nullptr;
+        SRF_CK(ctx, cudaMallocHost((void**)&ctx->h_coarse, coarse * sizeof(uint64_t)));
+        ctx->h_coarse_entries = coarse;
+    }
+    return SRF_OK;
+}
+
+srf_status ensure_sample_buffers(srf_ctx* ctx, uint64_t n_samples) {
+    srf_status st;
+    if ((st = ensure(ctx, ctx->pos_dt, n_samples * sizeof(float4))) != SRF_OK) return st;
+    if ((st = ensure(ctx, ctx->sample_ray, n_samples * sizeof(uint32_t))) != SRF_OK) return st;
+    const size_t per = ctx->cfg.field_type == SRF_FIELD_BLOBS ? sizeof(float4) : sizeof(uint2);
+    if ((st = ensure(ctx, ctx->rgbs, n_samples * per)) != SRF_OK) return st;
+    return SRF_OK;
+}
+
+srf_status check_ready(srf_ctx* ctx) {
+    if (ctx->cfg.field_type == SRF_FIELD_NETWORK && !ctx->have_net)
+        return fail(ctx, SRF_ERR_STATE, "network parameters were not uploaded (srf_upload_network)");
+    if (ctx->cfg.field_type == SRF_FIELD_BLOBS && ctx->n_blobs == 0)
+        return fail(ctx, SRF_ERR_STATE, "blob scene was not uploaded (srf_upload_blobs)");
+    return SRF_OK;
+}
+
+// count + scan for a view; leaves per-ray records in the context.
+srf_status count_and_scan(srf_ctx* ctx, const DevView& v, cudaStream_t s) {
+    srf_status st = ensure_ray_buffers(ctx, v.n_rays);
+    if (st != SRF_OK) return st;
+    SRF_CK(ctx, cudaMemsetAsync(ctx->d_counters, 0, sizeof(FrameCounters), s));
+    launch_ray_count(ctx->g, v, ctx->cfg.use_grid ? ctx->bits : nullptr, (float4*)ctx->ray_dir_t.p, (uint8_t*)ctx->ray_end.p,
+                     (uint32_t*)ctx->counts.p, ctx->d_counters, s);
+    launch_scan((const uint32_t*)ctx->counts.p, v.n_rays, (uint64_t*)ctx->offsets.p, ctx->scan_scratch.p, s);
+    SRF_CK(ctx, cudaGetLastError());
+    return SRF_OK;
+}
+
+// Copies offsets[k * kCoarse] (k = 0 .. n/kCoarse) and offsets[n] to the pinned table; synchronises.
+srf_status read_coarse_offsets(srf_ctx* ctx, uint64_t n_rays, cudaStream_t s, uint64_t* total) {
+    const size_t n_coarse = (size_t)(n_rays / kCoarse) + 1;     // entries 0, kCoarse, 2*kCoarse, ... <= n_rays
+    const uint64_t* off = (const uint64_t*)ctx->offsets.p;
+    SRF_CK(ctx, cudaMemcpy2DAsync(ctx->h_coarse, sizeof(uint64_t), off, kCoarse * sizeof(uint64_t), sizeof(uint64_t),
+                                  n_coarse, cudaMemcpyDeviceToHost, s));
+    SRF_CK(ctx, cudaMemcpyAsync(ctx->h_coarse + n_coarse, off + n_rays, sizeof(uint64_t), cudaMemcpyDeviceToHost, s));
+    SRF_CK(ctx, cudaStreamSynchronize(s));
+    *total = ctx->h_coarse[n_coarse];
+    return SRF_OK;
+}
+
+}  // namespace
+
+// =====================================================================================================
+extern "C" {
+
+void srf_config_default(srf_config_t* c) {
+    memset(c, 0, sizeof(*c));
+    c->struct_size = sizeof(*c);
+    c->version = SRF_ABI_VERSION;
+    c->warping_type = SRF_WARP_NGP;
+    c->aabb_scale = 1;
+    c->use_grid = 1;
+    c->grid_size = 128;
+    c->num_cascades = 1;
+    c->ema_decay = 0.95f;
+    c->grid_distribution_type = SRF_GRID_WARPED_EXP;
+    c->maximum_marching_steps = 1024;
+    c->near_distance = 0.2f;
+    c->far_distance = 100.f;
+    c->sampling_type = SRF_SAMPLING_ORIGINAL;
+    c->snap_to_pixel_centers_in_rendering = 1;
+    c->min_optical_thickness = 0.01f;
+    c->transmittance_threshold = 1e-4f;
+    c->n_levels = 16;
+    c->n_features_per_level = 2;
+    c->log2_hashmap_size = 19;
+    c->base_resolution = 16;
+    c->desired_resolution = 2048.f;
+    c->density_activation = SRF_ACT_EXPONENTIAL;
+    c->rgb_activation = SRF_ACT_LOGISTIC;
+    c->field_type = SRF_FIELD_NETWORK;
+    c->march_iter = 10000;
+}
+
+const char* srf_last_error(const srf_ctx* ctx) { return ctx ? ctx->err.c_str() : g_create_error.c_str(); }
+
+srf_status srf_create(const srf_config_t* cfg, int device, srf_ctx** out) {
+    if (!out) return fail(nullptr, SRF_ERR_ARG, "out is NULL");
+    *out = nullptr;
+    std::string why;
+    srf_status st = validate(cfg, &why);
+    if (st != SRF_OK) return fail(nullptr, st, why);
+    int n_dev = 0;
+    if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev == 0)
+        return fail(nullptr, SRF_ERR_CUDA, "no CUDA device: this library has no CPU path");
+    if (device < 0 || device >= n_dev) return fail(nullptr, SRF_ERR_ARG, "device index out of range");
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return fail(nullptr, SRF_ERR_CUDA, "cudaGetDeviceProperties failed");
+    if (prop.major != 10) return fail(nullptr, SRF_ERR_CUDA, "this library is built for sm_100a (B200) only");
+    srf_ctx* ctx = new (std::nothrow) srf_ctx();
+    if (!ctx) return fail(nullptr, SRF_ERR_CUDA, "out of host memory");
+    ctx->cfg = *cfg;
+    ctx->device = device;
+    resolve(*cfg, &ctx->g, &ctx->min_optical_thickness);
+    DeviceGuard guard(device);
+    auto cleanup = [&](srf_status s) { g_create_error = ctx->err; srf_destroy(ctx); return s; };
+#define CK_CREATE(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) { ctx->err = std::string(#call) + ": " + cudaGetErrorString(e_); return cleanup(SRF_ERR_CUDA); } } while (0)
+    const size_t total = (size_t)ctx->g.cells * ctx->g.n_cascades;
+    CK_CREATE(cudaMalloc((void**)&ctx->grid, total * sizeof(float)));
+    CK_CREATE(cudaMalloc((void**)&ctx->grid_current, total * sizeof(float)));
+    const size_t n_partial = (ctx->g.cells + 1023) / 1024 + 1;
+    CK_CREATE(cudaMalloc((void**)&ctx->partial_a, n_partial * sizeof(float)));
+    CK_CREATE(cudaMalloc((void**)&ctx->partial_b, n_partial * sizeof(float)));
+    CK_CREATE(cudaMalloc((void**)&ctx->mean, sizeof(float)));
+    CK_CREATE(cudaMalloc((void**)&ctx->bits, total / 8));
+    CK_CREATE(cudaMemset(ctx->grid, 0, total * sizeof(float)));
+    CK_CREATE(cudaMemset(ctx->bits, 0, total / 8));
+    CK_CREATE(cudaMemset(ctx->mean, 0, sizeof(float)));
+    if (cfg->field_type == SRF_FIELD_NETWORK) {
+        build_net_meta(*cfg, &ctx->net);
+        ctx->n_table_entries = table_entries(ctx->net);
+        CK_CREATE(cudaMalloc((void**)&ctx->table, (size_t)ctx->n_table_entries * cfg->n_features_per_level * sizeof(__half)));
+        CK_CREATE(cudaMalloc((void**)&ctx->w_density, (64 * 32 + 16 * 64) * sizeof(__half)));
+        CK_CREATE(cudaMalloc((void**)&ctx->w_rgb, (64 * 32 + 64 * 64 + 16 * 64) * sizeof(__half)));
+    }
+    CK_CREATE(cudaMalloc((void**)&ctx->d_counters, sizeof(FrameCounters)));
+    CK_CREATE(cudaMallocHost((void**)&ctx->h_counters, sizeof(FrameCounters)));
+    for (int i = 0; i < 8; ++i) CK_CREATE(cudaEventCreate(&ctx->ev[i]));
+#undef CK_CREATE
+    // OccupancySampler::init (occupancy_sampler.cu:956-957): Testbed seeds its generator with 43 and
+    // hands the sampler default_rng_t{rng.next_uint()}; srf_refresh_reset overrides.
+    srf_refresh_reset(ctx, 43);
+    *out = ctx;
+    return SRF_OK;
+}
+
+void srf_destroy(srf_ctx* ctx) {
+    if (!ctx) return;
+    DeviceGuard guard(ctx->device);
+    void* ptrs[] = {ctx->grid, ctx->grid_current, ctx->partial_a, ctx->partial_b, ctx->mean, ctx->bits, ctx->table,
+                    ctx->w_density, ctx->w_rgb, ctx->blobs, ctx->cmap, ctx->d_counters, ctx->ray_dir_t.p, ctx->ray_end.p,
+                    ctx->counts.p, ctx->offsets.p, ctx->scan_scratch.p, ctx->pos_dt.p, ctx->sample_ray.p, ctx->rgbs.p,
+                    ctx->img_out.p, ctx->img_accum.p};
+    for (void* p : ptrs) if (p) cudaFree(p);
+    if (ctx->h_counters) cudaFreeHost(ctx->h_counters);
+    if (ctx->h_coarse) cudaFreeHost(ctx->h_coarse);
+    for (int i = 0; i < 8; ++i) if (ctx->ev[i]) cudaEventDestroy(ctx->ev[i]);
+    delete ctx;
+}
+
+srf_status srf_set_timing(srf_ctx* ctx, int enabled) {
+    if (!ctx) return SRF_ERR_ARG;
+    ctx->timing = enabled != 0;
+    return SRF_OK;
+}
+
+srf_status srf_hashgrid_layout(const srf_config_t* cfg, uint32_t* offsets, uint32_t* resolutions, float* scales) {
+    if (!cfg || cfg->n_levels == 0 || cfg->n_levels > (uint32_t)kMaxLevels) return fail(nullptr, SRF_ERR_ARG, "bad n_levels");
+    NetMeta net;
+    build_net_meta(*cfg, &net);
+    for (uint32_t l = 0; l < cfg->n_levels; ++l) {
+        if (offsets) offsets[l] = net.level[l].offset;
+        if (resolutions) resolutions[l] = net.level[l].res;
+        if (scales) scales[l] = net.level[l].scale;
+    }
+    if (offsets) offsets[cfg->n_levels] = table_entries(net);
+    return SRF_OK;
+}
+
+srf_status srf_upload_network(srf_ctx* ctx, const uint16_t* h_table, size_t n_table, const uint16_t* h_d, size_t n_d,
+                              const uint16_t* h_c, size_t n_c) {
+    if (!ctx) return SRF_ERR_ARG;
+    if (ctx->cfg.field_type != SRF_FIELD_NETWORK) return fail(ctx, SRF_ERR_STATE, "context was created without a network field");
+    if (!h_table || !h_d || !h_c) return fail(ctx, SRF_ERR_ARG, "NULL parameter array");
+    if (n_table != (size_t)ctx->n_table_entries * ctx->cfg.n_features_per_level)
+        return fail(ctx, SRF_ERR_ARG, "hash table size does not match srf_hashgrid_layout");
+    if (n_d != 64 * 32 + 16 * 64) return fail(ctx, SRF_ERR_ARG, "density MLP must hold 64x32 + 16x64 halves");
+    if (n_c != 64 * 32 + 64 * 64 + 16 * 64) return fail(ctx, SRF_ERR_ARG, "colour MLP must hold 64x32 + 64x64 + 16x64 halves");
+    DeviceGuard guard(ctx->device);
+    SRF_CK(ctx, cudaMemcpy(ctx->table, h_table, n_table * sizeof(__half), cudaMemcpyHostToDevice));
+    SRF_CK(ctx, cudaMemcpy(ctx->w_density, h_d, n_d * sizeof(__half), cudaMemcpyHostToDevice));
+    SRF_CK(ctx, cudaMemcpy(ctx->w_rgb, h_c, n_c * sizeof(__half), cudaMemcpyHostToDevice));
+    ctx->have_net = true;
+    return SRF_OK;
+}
+
+srf_status srf_upload_blobs(srf_ctx* ctx, const float* h_blobs, uint32_t n_blobs, const float* h_cmap) {
+    if (!ctx) return SRF_ERR_ARG;
+    if (!h_blobs || !h_cmap || n_blobs == 0) return fail(ctx, SRF_ERR_ARG, "empty blob scene");
+    if (n_blobs > 2048) return fail(ctx, SRF_ERR_CAPACITY, "at most 2048 blobs");
+    DeviceGuard guard(ctx->device);
+    if (ctx->blobs) { cudaFree(ctx->blobs); ctx->blobs = nullptr; }
+    if (!ctx->cmap) SRF_CK(ctx, cudaMalloc((void**)&ctx->cmap, 9 * sizeof(float)));
+    SRF_CK(ctx, cudaMalloc((void**)&ctx->blobs, (size_t)n_blobs * 5 * sizeof(float)));
+    SRF_CK(ctx, cudaMemcpy(ctx->blobs, h_blobs, (size_t)n_blobs * 5 * sizeof(float), cudaMemcpyHostToDevice));
+    SRF_CK(ctx, cudaMemcpy(ctx->cmap, h_cmap, 9 * sizeof(float), cudaMemcpyHostToDevice));
+    ctx->n_blobs = n_blobs;
+    return SRF_OK;
+}
+
+// ---- grid ------------------------------------------------------------------------------------------
+srf_status srf_upload_density_grid(srf_ctx* ctx, const float* h, size_t n, void* stream) {
+    if (!ctx || !h) return SRF_ERR_ARG;
+    if (n != (size_t)ctx->g.cells * ctx->g.n_cascades) return fail(ctx, SRF_ERR_ARG, "density grid size mismatch");
+    DeviceGuard guard(ctx->device);
+    SRF_CK(ctx, cudaMemcpyAsync(ctx->grid, h, n * sizeof(float), cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    SRF_CK(ctx, cudaStreamSynchronize((cudaStream_t)stream));
+    return SRF_OK;
+}
+srf_status srf_download_density_grid(srf_ctx* ctx, float* h, size_t n, void* stream) {
+    if (!ctx || !h) return SRF_ERR_ARG;
+    if (n != (size_t)ctx->g.cells * ctx->g.n_cascades) return fail(ctx, SRF_ERR_ARG, "density grid size mismatch");
+    DeviceGuard guard(ctx->device);
+    SRF_CK(ctx, cudaMemcpyAsync(h, ctx->grid, n * sizeof(float), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    SRF_CK(ctx, cudaStreamSynchronize((cudaStream_t)stream));
+    return SRF_OK;
+}
+srf_status srf_upload_bitfield(srf_ctx* ctx, const uint8_t* h, size_t n, void* stream) {
+    if (!ctx || !h) return SRF_ERR_ARG;
+    if (n != (size_t)ctx->g.cells * ctx->g.n_cascades / 8) return fail(ctx, SRF_ERR_ARG, "bitfield size mismatch");
+    DeviceGuard guard(ctx->device);
+    SRF_CK(ctx, cudaMemcpyAsync(ctx->bits, h, n, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    SRF_CK(ctx, cudaStreamSynchronize((cudaStream_t)stream));
+    return SRF_OK;
+}
+srf_status srf_download_bitfield(srf_ctx* ctx, uint8_t* h, size_t n, void* stream) {
+    if (!ctx || !h) return SRF_ERR_ARG;
+    if (n != (size_t)ctx->g.cells * ctx->g.n_cascades / 8) return fail(ctx, SRF_ERR_ARG, "bitfield size mismatch");
+    DeviceGuard guard(ctx->device);
+    SRF_CK(ctx, cudaMemcpyAsync(h, ctx->bits, n, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    SRF_CK(ctx, cudaStreamSynchronize((cudaStream_t)stream));
+    return SRF_OK;
+}
+srf_status srf_download_grid_mean(srf_ctx* ctx, float* h_mean, void* stream) {
+    if (!ctx || !h_mean) return SRF_ERR_ARG;
+    DeviceGuard guard(ctx->device);
+    SRF_CK(ctx, cudaMemcpyAsync(h_mean, ctx->mean, sizeof(float), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    SRF_CK(ctx, cudaStreamSynchronize((cudaStream_t)stream));
+    return SRF_OK;
+}
+
+srf_status srf_update_grid_bitfield(srf_ctx* ctx, void* stream) {
+    if (!ctx) return SRF_ERR_ARG;
+    DeviceGuard guard(ctx->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    const uint32_t total = ctx->g.cells * ctx->g.n_cascades;
+    launch_decay_and_mean(ctx->grid, ctx->grid_current, total, ctx->g.cells, 0.f, 0, ctx->partial_a, ctx->partial_b, ctx->mean, s);
+    launch_grid_to_bitfield(ctx->g, ctx->grid, ctx->bits, ctx->mean, ctx->min_optical_thickness, s);
+    SRF_CK(ctx, cudaGetLastError());
+    return SRF_OK;
+}
+
+static void host_pcg_step(RefreshRng& r) { r.state = r.state * 0x5851f42d4c957f2dULL + r.inc; }
+static void host_pcg_advance(RefreshRng& r, uint64_t delta) {
+    uint64_t cur_mult = 0x5851f42d4c957f2dULL, cur_plus = r.inc, acc_mult = 1u, acc_plus = 0u;
+    while (delta > 0) {
+        if (delta & 1) { acc_mult *= cur_mult; acc_plus = acc_plus * cur_mult + cur_plus; }
+        cur_plus = (cur_mult + 1) * cur_plus;
+        cur_mult *= cur_mult;
+        delta >>= 1;
+    }
+    r.state = acc_mult * r.state + acc_plus;
+}
+
+srf_status srf_refresh_reset(srf_ctx* ctx, uint64_t seed) {
+    if (!ctx) return SRF_ERR_ARG;
+    // PCG32 seeding (O'Neill): state = 0, inc = (seq << 1) | 1 with seq = 1, step, add the seed, step.
+    ctx->rng.state = 0;
+    ctx->rng.inc = (1ull << 1) | 1ull;
+    host_pcg_step(ctx->rng);
+    ctx->rng.state += seed;
+    host_pcg_step(ctx->rng);
+    ctx->refresh_step = 0;
+    return SRF_OK;
+}
+
+srf_status srf_refresh_grid(srf_ctx* ctx, uint32_t training_step, void* stream) {
+    if (!ctx) return SRF_ERR_ARG;
+    if (ctx->cfg.field_type != SRF_FIELD_NETWORK) return fail(ctx, SRF_ERR_STATE, "the grid refresh queries the network field");
+    srf_status st = check_ready(ctx);
+    if (st != SRF_OK) return st;
+    DeviceGuard guard(ctx->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    const uint32_t total = ctx->g.cells * ctx->g.n_cascades;
+    const uint32_t n_uniform = training_step >= 256 ? total / 4 : total;          // testbed.cu:206
+    const uint32_t n_nonuniform = training_step >= 256 ? total / 4 : 0;           // testbed.cu:207
+    SRF_CK(ctx, cudaMemsetAsync(ctx->grid_current, 0, (size_t)total * sizeof(float), s));   // occupancy_sampler.cu:1039
+    launch_refresh_sample(ctx->g, ctx->net, ctx->table, ctx->w_density, ctx->grid, ctx->grid_current, n_uniform,
+                          ctx->refresh_step, ctx->rng, (float)-0.01, ctx->cfg.aabb_scale, s);
+    host_pcg_advance(ctx->rng, 1ull << 32);                                        // rng.advance(), :1009
+    launch_refresh_sample(ctx->g, ctx->net, ctx->table, ctx->w_density, ctx->grid, ctx->grid_current, n_nonuniform,
+                          ctx->refresh_step, ctx->rng, ctx->min_optical_thickness, ctx->cfg.aabb_scale, s);
+    host_pcg_advance(ctx->rng, 1ull << 32);                                        // :1028
+    launch_decay_and_mean(ctx->grid, ctx->grid_current, total, ctx->g.cells, ctx->cfg.ema_decay, 1, ctx->partial_a,
+                          ctx->partial_b, ctx->mean, s);
+    ++ctx->refresh_step;                                                            // :1060
+    launch_grid_to_bitfield(ctx->g, ctx->grid, ctx->bits, ctx->mean, ctx->min_optical_thickness, s);
+    SRF_CK(ctx, cudaGetLastError());
+    return SRF_OK;
+}
+
+// ---- stages ------------------------------------------------------------------------------------------
+srf_status srf_shard_ray_count(const srf_view_t* view, uint64_t* n_rays) {
+    if (!view || !n_rays) return SRF_ERR_ARG;
+    *n_rays = shard_rows_total(*view) * view->width;
+    return SRF_OK;
+}
+
+srf_status srf_generate_rays(srf_ctx* ctx, const srf_view_t* view, float* d_dir, float* d_t, uint8_t* d_alive,
+                             uint32_t* d_pixel, void* stream) {
+    if (!ctx) return SRF_ERR_ARG;
+    DevView v;
+    srf_status st = make_view(ctx, view, &v);
+    if (st != SRF_OK) return st;
+    DeviceGuard guard(ctx->device);
+    launch_generate_rays(ctx->g, v, ctx->cfg.use_grid ? ctx->bits : nullptr, d_dir, d_t, d_alive, d_pixel, (cudaStream_t)stream);
+    SRF_CK(ctx, cudaGetLastError());
+    return SRF_OK;
+}
+
+srf_status srf_sample_count(srf_ctx* ctx, const srf_view_t* view, uint32_t* d_counts, void* stream) {
+    if (!ctx || !d_counts) return SRF_ERR_ARG;
+    DevView v;
+    srf_status st = make_view(ctx, view, &v);
+    if (st != SRF_OK) return st;
+    DeviceGuard guard(ctx->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    if ((st = ensure_ray_buffers(ctx, v.n_rays)) != SRF_OK) return st;
+    SRF_CK(ctx, cudaMemsetAsync(ctx->d_counters, 0, sizeof(FrameCounters), s));
+    launch_ray_count(ctx->g, v, ctx->cfg.use_grid ? ctx->bits : nullptr, (float4*)ctx->ray_dir_t.p, (uint8_t*)ctx->ray_end.p,
+                     d_counts, ctx->d_counters, s);
+    SRF_CK(ctx, cudaGetLastError());
+    return SRF_OK;
+}
+
+srf_status srf_sample_offsets(srf_ctx* ctx, const uint32_t* d_counts, uint64_t n_rays, uint64_t* d_offsets, void* stream) {
+    if (!ctx || !d_counts || !d_offsets) return SRF_ERR_ARG;
+    DeviceGuard guard(ctx->device);
+    srf_status st = ensure(ctx, ctx->scan_scratch, scan_scratch_bytes(n_rays));
+    if (st != SRF_OK) return st;
+    launch_scan(d_counts, n_rays, d_offsets, ctx->scan_scratch.p, (cudaStream_t)stream);
+    SRF_CK(ctx, cudaGetLastError());
+    return SRF_OK;
+}
+
+srf_status srf_sample_emit(srf_ctx* ctx, const srf_view_t* view, const uint64_t* d_offsets, uint64_t capacity,
+                           float* d_coords, uint32_t* d_ordinal, uint32_t* d_cell, void* stream) {
+    if (!ctx || !d_offsets || !d_coords) return SRF_ERR_ARG;
+    DevView v;
+    srf_status st = make_view(ctx, view, &v);
+    if (st != SRF_OK) return st;
+    DeviceGuard guard(ctx->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (ctx->ray_dir_t.bytes < v.n_rays * sizeof(float4))
+        return fail(ctx, SRF_ERR_STATE, "srf_sample_emit must follow srf_sample_count of the same view");
+    uint64_t total = 0;
+    SRF_CK(ctx, cudaMemcpyAsync(&total, d_offsets + v.n_rays, sizeof(uint64_t), cudaMemcpyDeviceToHost, s));
+    SRF_CK(ctx, cudaStreamSynchronize(s));
+    if (total > capacity) return fail(ctx, SRF_ERR_CAPACITY, "coordinate buffer too small for the samples of this view");
+    launch_ray_emit(ctx->g, v, ctx->cfg.use_grid ? ctx->bits : nullptr, (const float4*)ctx->ray_dir_t.p, d_offsets, 0, v.n_rays,
+                    nullptr, nullptr, d_coords, d_ordinal, d_cell, ctx->d_counters, s);
+    SRF_CK(ctx, cudaGetLastError());
+    return SRF_OK;
+}
+
+srf_status srf_network_inference(srf_ctx* ctx, const float* d_coords, uint64_t n, uint16_t* d_rgbsigma, void* stream) {
+    if (!ctx || (!d_coords && n) || (!d_rgbsigma && n)) return SRF_ERR_ARG;
+    if (ctx->cfg.field_type != SRF_FIELD_NETWORK) return fail(ctx, SRF_ERR_STATE, "context has no network field");
+    srf_status st = check_ready(ctx);
+    if (st != SRF_OK) return st;
+    DeviceGuard guard(ctx->device);
+    launch_field_network(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, nullptr, nullptr, nullptr, d_coords, n,
+                         (uint2*)d_rgbsigma, (cudaStream_t)stream);
+    SRF_CK(ctx, cudaGetLastError());
+    return SRF_OK;
+}
+
+srf_status srf_network_density(srf_ctx* ctx, const float* d_positions, uint64_t n, uint16_t* d_out, void* stream) {
+    if (!ctx || (!d_positions && n) || (!d_out && n)) return SRF_ERR_ARG;
+    if (ctx->cfg.field_type != SRF_FIELD_NETWORK) return fail(ctx, SRF_ERR_STATE, "context has no network field");
+    srf_status st = check_ready(ctx);
+    if (st != SRF_OK) return st;
+    DeviceGuard guard(ctx->device);
+    launch_field_density(ctx->net, ctx->table, ctx->w_density, d_positions, 3, n, (__half*)d_out, (cudaStream_t)stream);
+    SRF_CK(ctx, cudaGetLastError());
+    return SRF_OK;
+}
+
+srf_status srf_volume_rendering(srf_ctx* ctx, const srf_view_t* view, const uint64_t* d_offsets, uint64_t n_rays,
+                                const float* d_coords, const uint16_t* d_rgbsigma, float* d_rgba, uint32_t* d_n_composited,
+                                void* stream) {
+    if (!ctx || !d_offsets || !d_coords || !d_rgbsigma) return SRF_ERR_ARG;
+    DevView v;
+    srf_status st = make_view(ctx, view, &v);
+    if (st != SRF_OK) return st;
+    DeviceGuard guard(ctx->device);
+    launch_composite_coords(ctx->g, v, d_offsets, n_rays, d_coords, (const uint2*)d_rgbsigma, (float4*)d_rgba, d_n_composited,
+                            (cudaStream_t)stream);
+    SRF_CK(ctx, cudaGetLastError());
+    return SRF_OK;
+}
+
+// ---- frames -------------------------------------------------------------------------------------------
+srf_status srf_render_frame(srf_ctx* ctx, const srf_view_t* view, const srf_post_t* post, float* d_out, float* d_accum,
+                            float* d_rgba_raw, uint32_t* d_n_samples, srf_frame_stats_t* stats, void* stream) {
+    if (!ctx) return SRF_ERR_ARG;
+    srf_status st = check_ready(ctx);
+    if (st != SRF_OK) return st;
+    DevView v;
+    if ((st = make_view(ctx, view, &v)) != SRF_OK) return st;
+    DevPost dp;
+    make_post(post, &dp);
+    DeviceGuard guard(ctx->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (stats) memset(stats, 0, sizeof(*stats));
+    if (v.n_rays == 0) return SRF_OK;
+    const bool tm = ctx->timing && stats;
+    float ms_sampler = 0.f, ms_field = 0.f, ms_comp = 0.f;
+    auto lap = [&](int a, int b, float* acc) {
+        float ms = 0.f;
+        cudaEventSynchronize(ctx->ev[b]);
+        cudaEventElapsedTime(&ms, ctx->ev[a], ctx->ev[b]);
+        *acc += ms;
+    };
+
+    if (tm) cudaEventRecord(ctx->ev[0], s);
+    if ((st = count_and_scan(ctx, v, s)) != SRF_OK) return st;
+    if (tm) cudaEventRecord(ctx->ev[1], s);
+    uint64_t total = 0;
+    if ((st = read_coarse_offsets(ctx, v.n_rays, s, &total)) != SRF_OK) return st;
+    if (tm) lap(0, 1, &ms_sampler);
+    if (d_n_samples) SRF_CK(ctx, cudaMemcpyAsync(d_n_samples, ctx->counts.p, v.n_rays * sizeof(uint32_t), cudaMemcpyDeviceToDevice, s));
+
+    // batches of whole coarse groups whose samples fit the scratch
+    const uint64_t cap_limit = ctx->reserve_samples ? ctx->reserve_samples : kAutoSampleCapacity;
+    const size_t n_groups = (size_t)((v.n_rays + kCoarse - 1) / kCoarse);
+    auto group_begin = [&](size_t k) { return k < n_groups ? ctx->h_coarse[k] : total; };   // offsets[k*kCoarse]
+    uint64_t largest_group = 0;
+    for (size_t k = 0; k < n_groups; ++k) largest_group = std::max(largest_group, group_begin(k + 1) - group_begin(k));
+    if (largest_group > cap_limit && ctx->reserve_samples)
+        return fail(ctx, SRF_ERR_CAPACITY, "srf_reserve limit is smaller than the samples of one group of 4096 rays");
+    const uint64_t capacity = std::max(std::min(total, cap_limit), largest_group);
+    if ((st = ensure_sample_buffers(ctx, std::max<uint64_t>(capacity, 1))) != SRF_OK) return st;
+
+    const bool blobs = ctx->cfg.field_type == SRF_FIELD_BLOBS;
+    uint32_t n_batches = 0;
+    size_t k0 = 0;
+    while (k0 < n_groups) {
+        size_t k1 = k0 + 1;
+        while (k1 < n_groups && group_begin(k1 + 1) - group_begin(k0) <= capacity) ++k1;
+        const uint64_t r0 = (uint64_t)k0 * kCoarse, r1 = std::min<uint64_t>((uint64_t)k1 * kCoarse, v.n_rays);
+        const uint64_t n_s = group_begin(k1) - group_begin(k0);
+        if (tm) cudaEventRecord(ctx->ev[2], s);
+        launch_ray_emit(ctx->g, v, ctx->cfg.use_grid ? ctx->bits : nullptr, (const float4*)ctx->ray_dir_t.p,
+                        (const uint64_t*)ctx->offsets.p, r0, r1, (float4*)ctx->pos_dt.p, (uint32_t*)ctx->sample_ray.p, nullptr,
+                        nullptr, nullptr, ctx->d_counters, s);
+        if (tm) cudaEventRecord(ctx->ev[3], s);
+        if (blobs)
+            launch_field_blobs(ctx->g, ctx->blobs, ctx->n_blobs, ctx->cmap, (const float4*)ctx->pos_dt.p, n_s, (float4*)ctx->rgbs.p, s);
+        else
+            launch_field_network(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, (const float4*)ctx->pos_dt.p,
+                                 (const uint32_t*)ctx->sample_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, n_s,
+                                 (uint2*)ctx->rgbs.p, s);
+        if (tm) cudaEventRecord(ctx->ev[4], s);
+        launch_composite(ctx->g, v, dp, (const uint64_t*)ctx->offsets.p, r0, r1, (const float4*)ctx->pos_dt.p,
+                         blobs ? nullptr : (const uint2*)ctx->rgbs.p, blobs ? (const float4*)ctx->rgbs.p : nullptr,
+                         (const uint8_t*)ctx->ray_end.p, (float4*)d_out, (float4*)d_accum, (float4*)d_rgba_raw, nullptr,
+                         ctx->d_counters, s);
+        if (tm) {
+            cudaEventRecord(ctx->ev[5], s);
+            lap(2, 3, &ms_sampler); lap(3, 4, &ms_field); lap(4, 5, &ms_comp);
+        }
+        ++n_batches;
+        k0 = k1;
+    }
+    SRF_CK(ctx, cudaGetLastError());
+    if (stats) {
+        SRF_CK(ctx, cudaMemcpyAsync(ctx->h_counters, ctx->d_counters, sizeof(FrameCounters), cudaMemcpyDeviceToHost, s));
+        SRF_CK(ctx, cudaStreamSynchronize(s));
+        stats->n_rays = v.n_rays;
+        stats->n_rays_alive = ctx->h_counters->n_alive;
+        stats->n_march_steps = ctx->h_counters->n_march_steps;
+        stats->n_samples = ctx->h_counters->n_samples;
+        stats->n_samples_composited = ctx->h_counters->n_composited;
+        stats->n_rays_hit = ctx->h_counters->n_hit;
+        stats->n_batches = n_batches;
+        stats->error_flags = ctx->h_counters->error_flags;
+        stats->ms_sampler = ms_sampler; stats->ms_field = ms_field; stats->ms_composite = ms_comp; stats->ms_post = 0.f;
+        if (stats->error_flags & 1u) return fail(ctx, SRF_ERR_TIMEOUT, "a ray hit the march loop's iteration bound");
+    }
+    return SRF_OK;
+}
+
+srf_status srf_render(srf_ctx* ctx, const srf_view_t* view, const srf_post_t* post, uint32_t spp, float* h_image,
+                      srf_frame_stats_t* stats) {
+    if (!ctx || !view || !h_image) return SRF_ERR_ARG;
+    if ((view->shard_count ? view->shard_count : 1) != 1) return fail(ctx, SRF_ERR_ARG, "srf_render renders whole images: shard_count must be 1");
+    if (spp == 0) return fail(ctx, SRF_ERR_ARG, "spp must be positive");
+    DeviceGuard guard(ctx->device);
+    const size_t n = (size_t)view->width * view->height;
+    srf_status st;
+    if ((st = ensure(ctx, ctx->img_out, n * sizeof(float4))) != SRF_OK) return st;
+    if ((st = ensure(ctx, ctx->img_accum, n * sizeof(float4))) != SRF_OK) return st;
+    srf_view_t v = *view;
+    for (uint32_t i = 0; i < spp; ++i) {          // python_api.cu:22-27
+        v.spp_index = i;
+        st = srf_render_frame(ctx, &v, post, (float*)ctx->img_out.p, (float*)ctx->img_accum.p, nullptr, nullptr,
+                              i + 1 == spp ? stats : nullptr, nullptr);
+        if (st != SRF_OK) return st;
+    }
+    SRF_CK(ctx, cudaMemcpy(h_image, ctx->img_out.p, n * sizeof(float4), cudaMemcpyDeviceToHost));   // :30-38
+    return SRF_OK;
+}
+
+srf_status srf_dump_samples(srf_ctx* ctx, const srf_view_t* view, uint64_t ray_first, uint64_t ray_count, uint64_t capacity,
+                            uint32_t* h_counts, float* h_pos_dt, uint32_t* h_ordinal, uint32_t* h_cell, uint64_t* n_total) {
+    if (!ctx || !h_counts) return SRF_ERR_ARG;
+    DevView v;
+    srf_status st = make_view(ctx, view, &v);
+    if (st != SRF_OK) return st;
+    if (ray_first + ray_count > v.n_rays) return fail(ctx, SRF_ERR_ARG, "ray range exceeds the shard");
+    DeviceGuard guard(ctx->device);
+    cudaStream_t s = nullptr;
+    if ((st = count_and_scan(ctx, v, s)) != SRF_OK) return st;
+    std::vector<uint64_t> off(ray_count + 1);
+    SRF_CK(ctx, cudaMemcpy(off.data(), (const uint64_t*)ctx->offsets.p + ray_first, (ray_count + 1) * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+    SRF_CK(ctx, cudaMemcpy(h_counts, (const uint32_t*)ctx->counts.p + ray_first, ray_count * sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    const uint64_t total = off[ray_count] - off[0];
+    if (n_total) *n_total = total;
+    if (total > capacity) return fail(ctx, SRF_ERR_CAPACITY, "sample arrays too small");
+    if (total == 0) return SRF_OK;
+    if ((st = ensure_sample_buffers(ctx, total)) != SRF_OK) return st;
+    DevBuf ord, cell;
+    if ((st = ensure(ctx, ord, total * sizeof(uint32_t))) != SRF_OK) return st;
+    if ((st = ensure(ctx, cell, total * sizeof(uint32_t))) != SRF_OK) { cudaFree(ord.p); return st; }
+    launch_ray_emit(ctx->g, v, ctx->cfg.use_grid ? ctx->bits : nullptr, (const float4*)ctx->ray_dir_t.p, (const uint64_t*)ctx->offsets.p,
+                    ray_first, ray_first + ray_count, (float4*)ctx->pos_dt.p, (uint32_t*)ctx->sample_ray.p, nullptr,
+                    (uint32_t*)ord.p, (uint32_t*)cell.p, ctx->d_counters, s);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess && h_pos_dt) e = cudaMemcpy(h_pos_dt, ctx->pos_dt.p, total * sizeof(float4), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && h_ordinal) e = cudaMemcpy(h_ordinal, ord.p, total * sizeof(uint32_t), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && h_cell) e = cudaMemcpy(h_cell, cell.p, total * sizeof(uint32_t), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    cudaFree(ord.p);
+    cudaFree(cell.p);
+    if (e != cudaSuccess) { ctx->err = std::string("srf_dump_samples: ") + cudaGetErrorString(e); return SRF_ERR_CUDA; }
+    return SRF_OK;
+}
+
+srf_status srf_reserve(srf_ctx* ctx, uint64_t max_samples) {
+    if (!ctx) return SRF_ERR_ARG;
+    ctx->reserve_samples = max_samples;
+    return SRF_OK;
+}
+
+srf_status srf_eval_math(int device, int op, const float* h_a, const float* h_b, float* h_out, size_t n) {
+    if (!h_a || !h_out || op < 0 || op > 5) return fail(nullptr, SRF_ERR_ARG, "bad arguments");
+    int n_dev = 0;
+    if (cudaGetDeviceCount(&n_dev) != cudaSuccess || device < 0 || device >= n_dev) return fail(nullptr, SRF_ERR_CUDA, "no such CUDA device");
+    DeviceGuard guard(device);
+    float *a = nullptr, *b = nullptr, *o = nullptr;
+    cudaError_t e = cudaMalloc((void**)&a, n * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc((void**)&b, n * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc((void**)&o, n * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemcpy(a, h_a, n * sizeof(float), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = h_b ? cudaMemcpy(b, h_b, n * sizeof(float), cudaMemcpyHostToDevice) : cudaMemset(b, 0, n * sizeof(float));
+    if (e == cudaSuccess) { launch_eval_math(op, a, b, o, n, nullptr); e = cudaGetLastError(); }
+    if (e == cudaSuccess) e = cudaMemcpy(h_out, o, n * sizeof(float), cudaMemcpyDeviceToHost);
+    cudaFree(a); cudaFree(b); cudaFree(o);
+    if (e != cudaSuccess) return fail(nullptr, SRF_ERR_CUDA, cudaGetErrorString(e));
+    return SRF_OK;
+}
+
+}  // extern "C"

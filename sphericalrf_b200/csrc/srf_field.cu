@@ -1,0 +1,247 @@
+// srf_field.cu -- what a sample looks like: (r, g, b, sigma) from the network or from the analytic
+// stand-in scene.
+//
+// Network path = NGPNetwork::inference_mixed_precision (internal/network/ngp_network.h:212-279):
+// multiresolution hash encoding of the position (32 halves) and degree-4 spherical harmonics of
+// the direction (16 halves); density MLP 32 -> 64 -> 16; colour MLP [density out(16), SH(16)] ->
+// 64 -> 64 -> 3; output (r, g, b, density out[0]).  The reference runs six tiny-cuda-nn kernels
+// with every intermediate in global memory and two glue kernels (grab_density_network_output,
+// assemble_rgbd, :38-78); here one kernel keeps a tile of samples on chip from the table gathers
+// to the four output halves.
+//
+// tiny-cuda-nn is not part of the reference tree; the arithmetic is the library's own statement of
+// the published algorithm (Mueller et al. 2022): fp16 parameters and activations, fp32
+// accumulation, one rounding to fp16 per layer; trilinear interpolation with fp32 weights in
+// corner order 0..7 (bit d of the corner index selects the upper neighbour along axis d).
+#include "srf_network.cuh"
+
+namespace srf {
+
+namespace {
+
+template <int F>
+__global__ void __launch_bounds__(kFieldBlock)
+k_field_network(const NetMeta net, const __half* __restrict__ table, const __half* __restrict__ wd, const __half* __restrict__ wc,
+                const float4* __restrict__ pos_dt, const uint32_t* __restrict__ sample_ray,
+                const float4* __restrict__ ray_dir_t, const float* __restrict__ coords7, uint64_t n,
+                uint2* __restrict__ rgbsigma) {
+    __shared__ __align__(16) __half sW[kWeightHalves];
+    __shared__ __align__(16) __half sRows[kFieldBlock * kRowLd];
+    load_weights(wd, wc, sW, true);
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    __half* my_row = sRows + threadIdx.x * kRowLd;
+    const __half* warp_rows = sRows + warp * 32 * kRowLd;
+    const uint64_t n_tiles = (n + kFieldBlock - 1) / kFieldBlock;
+
+    for (uint64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const uint64_t s = tile * kFieldBlock + threadIdx.x;
+        // ---- encode: one thread per sample ----
+        float x = 0.f, y = 0.f, z = 0.f, dx = 0.5f, dy = 0.5f, dz = 0.5f;
+        if (s < n) {
+            if (coords7) {
+                const float* c = coords7 + s * 7;
+                x = c[0]; y = c[1]; z = c[2]; dx = c[4]; dy = c[5]; dz = c[6];
+            } else {
+                const float4 p = pos_dt[s];
+                const float4 d = ray_dir_t[sample_ray[s]];
+                x = p.x; y = p.y; z = p.z;
+                dx = (d.x + 1.f) * 0.5f; dy = (d.y + 1.f) * 0.5f; dz = (d.z + 1.f) * 0.5f;   // warp_direction
+            }
+        }
+        hash_encode<F>(net, table, x, y, z, my_row);
+        sh_encode(dx, dy, dz, my_row + 32);
+        __syncwarp();
+
+        // ---- density MLP: 32 -> 64 (ReLU) -> 16 ----
+        uint32_t a_in[2][2][4];
+        {
+            uint32_t f0[2][4], f1[2][4];
+            load_a_frag(warp_rows, 0, f0);
+            load_a_frag(warp_rows, 16, f1);
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) { a_in[mt][0][k] = f0[mt][k]; a_in[mt][1][k] = f1[mt][k]; }
+        }
+        uint32_t a_h[2][4][4];
+        {
+            float c1[2][8][4];
+            mlp_layer<2, 8>(a_in, sW + kOffD1, kLd32, c1);
+            acc_to_frag<4, true>(c1, a_h);
+        }
+        uint32_t a_rgb[2][2][4];
+        uint32_t sigma_bits[2];     // density output 0 of rows g and g+8 (valid in lanes with t == 0)
+        {
+            float c2[2][2][4];
+            mlp_layer<4, 2>(a_h, sW + kOffD2, kLd64, c2);
+            uint32_t a_d[2][1][4];
+            acc_to_frag<1, false>(c2, a_d);
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) a_rgb[mt][0][k] = a_d[mt][0][k];
+                // a_d[mt][0][0] = (row g, cols 2t,2t+1), a_d[mt][0][1] = (row g+8, cols 2t,2t+1)
+                sigma_bits[mt] = (a_d[mt][0][0] & 0xffffu) | (a_d[mt][0][1] << 16);
+            }
+            uint32_t f[2][4];
+            load_a_frag(warp_rows, 32, f);      // SH occupies input rows 16..31 of the colour MLP
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) a_rgb[mt][1][k] = f[mt][k];
+        }
+        // ---- colour MLP: 32 -> 64 (ReLU) -> 64 (ReLU) -> 3 ----
+        {
+            float c1[2][8][4];
+            mlp_layer<2, 8>(a_rgb, sW + kOffC1, kLd32, c1);
+            acc_to_frag<4, true>(c1, a_h);
+        }
+        uint32_t a_h2[2][4][4];
+        {
+            float c2[2][8][4];
+            mlp_layer<4, 8>(a_h, sW + kOffC2, kLd64, c2);
+            acc_to_frag<4, true>(c2, a_h2);
+        }
+        float c3[2][1][4];
+        mlp_layer<4, 1>(a_h2, sW + kOffC3, kLd64, c3);
+        // c3[mt][0] = {(row g, col 2t), (row g, col 2t+1), (row g+8, col 2t), (row g+8, col 2t+1)}
+        // lanes t == 0 hold r,g; lanes t == 1 hold b (col 2).
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+            const float b_lo = __shfl_down_sync(0xffffffffu, c3[mt][0][0], 1);   // from lane t+1: col 2 of row g
+            const float b_hi = __shfl_down_sync(0xffffffffu, c3[mt][0][2], 1);   // col 2 of row g+8
+            if (t == 0) {
+                const uint64_t base = tile * kFieldBlock + warp * 32 + mt * 16;
+                const uint64_t s0 = base + g, s1 = base + g + 8;
+                const uint32_t sg0 = sigma_bits[mt] & 0xffffu, sg1 = sigma_bits[mt] >> 16;
+                if (s0 < n) rgbsigma[s0] = make_uint2(pack_half2(c3[mt][0][0], c3[mt][0][1]),
+                                                      (pack_half2(b_lo, 0.f) & 0xffffu) | (sg0 << 16));
+                if (s1 < n) rgbsigma[s1] = make_uint2(pack_half2(c3[mt][0][2], c3[mt][0][3]),
+                                                      (pack_half2(b_hi, 0.f) & 0xffffu) | (sg1 << 16));
+            }
+        }
+        __syncwarp();
+    }
+}
+
+// Density only: positions -> 16 halves (NGPNetwork::density, ngp_network.h:281-310).
+template <int F>
+__global__ void __launch_bounds__(kFieldBlock)
+k_field_density(const NetMeta net, const __half* __restrict__ table, const __half* __restrict__ wd, const float* __restrict__ positions,
+                uint32_t stride, uint64_t n, __half* __restrict__ out16) {
+    __shared__ __align__(16) __half sW[kOffC1];
+    __shared__ __align__(16) __half sRows[kFieldBlock * kRowLd];
+    load_weights(wd, nullptr, sW, false);
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    __half* my_row = sRows + threadIdx.x * kRowLd;
+    const __half* warp_rows = sRows + warp * 32 * kRowLd;
+    const uint64_t n_tiles = (n + kFieldBlock - 1) / kFieldBlock;
+    for (uint64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const uint64_t s = tile * kFieldBlock + threadIdx.x;
+        float x = 0.f, y = 0.f, z = 0.f;
+        if (s < n) { const float* p = positions + s * stride; x = p[0]; y = p[1]; z = p[2]; }
+        hash_encode<F>(net, table, x, y, z, my_row);
+        __syncwarp();
+        uint32_t a_in[2][2][4];
+        {
+            uint32_t f0[2][4], f1[2][4];
+            load_a_frag(warp_rows, 0, f0);
+            load_a_frag(warp_rows, 16, f1);
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) { a_in[mt][0][k] = f0[mt][k]; a_in[mt][1][k] = f1[mt][k]; }
+        }
+        uint32_t a_h[2][4][4];
+        {
+            float c1[2][8][4];
+            mlp_layer<2, 8>(a_in, sW + kOffD1, kLd32, c1);
+            acc_to_frag<4, true>(c1, a_h);
+        }
+        float c2[2][2][4];
+        mlp_layer<4, 2>(a_h, sW + kOffD2, kLd64, c2);
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const uint64_t base = tile * kFieldBlock + warp * 32 + mt * 16;
+                const uint64_t s0 = base + g, s1 = base + g + 8;
+                const int col = nt * 8 + 2 * t;
+                if (s0 < n) *reinterpret_cast<uint32_t*>(out16 + s0 * 16 + col) = pack_half2(c2[mt][nt][0], c2[mt][nt][1]);
+                if (s1 < n) *reinterpret_cast<uint32_t*>(out16 + s1 * 16 + col) = pack_half2(c2[mt][nt][2], c2[mt][nt][3]);
+            }
+        __syncwarp();
+    }
+}
+
+// Analytic stand-in scene, fp32, one thread per sample.
+__global__ void __launch_bounds__(256)
+k_field_blobs(const DevCfg g, const float* __restrict__ blobs, uint32_t n_blobs, const float* __restrict__ cmap,
+              const float4* __restrict__ pos_dt, uint64_t n, float4* __restrict__ out) {
+    extern __shared__ float s_blobs[];
+    for (uint32_t i = threadIdx.x; i < n_blobs * 5; i += blockDim.x) s_blobs[i] = blobs[i];
+    __syncthreads();
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float4 p = pos_dt[i];
+    const V3 x = unwarp_position(g, mk3(p.x, p.y, p.z));
+    float sigma = 0.f;
+    for (uint32_t b = 0; b < n_blobs; ++b) {
+        const float* q = s_blobs + 5 * b;
+        const float dx = x.x - q[0], dy = x.y - q[1], dz = x.z - q[2];
+        const float d2 = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
+        const float inv = -0.5f / (q[3] * q[3]);
+        sigma = fmaf(q[4], srf_expf(d2 * inv), sigma);
+    }
+    const float px = x.x - 0.5f, py = x.y - 0.5f, pz = x.z - 0.5f;
+    float4 r;
+    r.x = fmaf(cmap[2], pz, fmaf(cmap[1], py, cmap[0] * px));
+    r.y = fmaf(cmap[5], pz, fmaf(cmap[4], py, cmap[3] * px));
+    r.z = fmaf(cmap[8], pz, fmaf(cmap[7], py, cmap[6] * px));
+    r.w = sigma;
+    out[i] = r;
+}
+
+int field_grid(uint64_t n) {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const uint64_t tiles = (n + kFieldBlock - 1) / kFieldBlock;
+    const uint64_t cap = (uint64_t)sms * 8;      // a multiple of the SM count; each CTA strides over tiles
+    return (int)(tiles < cap ? tiles : cap);
+}
+
+}  // namespace
+
+void launch_field_network(const NetMeta& net, const __half* table, const __half* w_density, const __half* w_rgb,
+                          const float4* pos_dt, const uint32_t* sample_ray, const float4* ray_dir_t,
+                          const float* coords7, uint64_t n, uint2* rgbsigma, cudaStream_t stream) {
+    if (n == 0) return;
+    const int grid = field_grid(n);
+    if (net.n_features == 2)
+        k_field_network<2><<<grid, kFieldBlock, 0, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma);
+    else
+        k_field_network<4><<<grid, kFieldBlock, 0, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma);
+}
+
+void launch_field_density(const NetMeta& net, const __half* table, const __half* w_density, const float* positions,
+                          uint32_t stride, uint64_t n, __half* out16, cudaStream_t stream) {
+    if (n == 0) return;
+    const int grid = field_grid(n);
+    if (net.n_features == 2)
+        k_field_density<2><<<grid, kFieldBlock, 0, stream>>>(net, table, w_density, positions, stride, n, out16);
+    else
+        k_field_density<4><<<grid, kFieldBlock, 0, stream>>>(net, table, w_density, positions, stride, n, out16);
+}
+
+void launch_field_blobs(const DevCfg& g, const float* blobs, uint32_t n_blobs, const float* color_map,
+                        const float4* pos_dt, uint64_t n, float4* rgbsigma, cudaStream_t stream) {
+    if (n == 0) return;
+    k_field_blobs<<<(unsigned int)((n + 255) / 256), 256, n_blobs * 5 * sizeof(float), stream>>>(
+        g, blobs, n_blobs, color_map, pos_dt, n, rgbsigma);
+}
+
+}  // namespace srf

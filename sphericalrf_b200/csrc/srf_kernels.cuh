@@ -1,0 +1,105 @@
+// srf_kernels.cuh -- launch wrappers of the device kernels (implemented in the .cu files of this
+// directory) and the small structures they share with the context.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "srf_device.cuh"
+
+namespace srf {
+
+constexpr int kMaxLevels = 16;
+
+// One level of the multiresolution hash grid.
+struct LevelMeta {
+    float scale;        // position scale: p = x * scale + 0.5
+    uint32_t res;       // grid resolution
+    uint32_t offset;    // first entry of the level (entries, not halves)
+    uint32_t size;      // entries in the level
+    uint32_t dense;     // 1: x + y*res + z*res^2, 0: spatial hash
+};
+
+struct NetMeta {
+    LevelMeta level[kMaxLevels];
+    uint32_t n_levels, n_features;
+};
+
+// Device counters of one frame; zeroed before the count kernel.
+struct FrameCounters {
+    unsigned long long n_alive, n_march_steps, n_samples, n_composited, n_hit;
+    unsigned int error_flags;
+    unsigned int pad;
+};
+
+// Per-ray record written by the count pass.
+//   ray_dir_t: direction (xyz) and the ray parameter after the jitter (w)
+//   ray_end:   RayEnd of the full march
+void launch_ray_count(const DevCfg& g, const DevView& v, const uint8_t* bits, float4* ray_dir_t, uint8_t* ray_end,
+                      uint32_t* counts, FrameCounters* counters, cudaStream_t stream);
+
+// Exclusive scan of counts[0..n) into offsets[0..n] (offsets[n] = total). scratch: >= scan_scratch_bytes(n).
+size_t scan_scratch_bytes(uint64_t n);
+void launch_scan(const uint32_t* counts, uint64_t n, uint64_t* offsets, void* scratch, cudaStream_t stream);
+
+// Emit pass over rays [ray_begin, ray_end): sample j of ray r goes to slot offsets[r] - offsets[ray_begin] + j.
+//   pos_dt:     warped position (xyz) and step width (w)
+//   sample_ray: the ray (shard index) of each sample
+//   coords7:    alternatively the reference's Coordinate records (pos.xyz, dt, dir.xyz), 7 floats
+//   ordinal/cell: optional march-step ordinal and Morton cell index (parity taps)
+void launch_ray_emit(const DevCfg& g, const DevView& v, const uint8_t* bits, const float4* ray_dir_t,
+                     const uint64_t* offsets, uint64_t ray_begin, uint64_t ray_end, float4* pos_dt,
+                     uint32_t* sample_ray, float* coords7, uint32_t* ordinal, uint32_t* cell,
+                     FrameCounters* counters, cudaStream_t stream);
+
+// Rays only (generate_rays_from_camera_matrix): direction, t at the first occupied step, alive, pixel.
+void launch_generate_rays(const DevCfg& g, const DevView& v, const uint8_t* bits, float* dir, float* t,
+                          uint8_t* alive, uint32_t* pixel, cudaStream_t stream);
+
+// Field evaluation on n samples.
+//   network: hash-grid encoding + SH + density MLP + colour MLP -> (r,g,b,sigma) raw, 4 halves per sample.
+//   dirs come either from ray_dir_t[sample_ray[i]] (compact layout) or from coords7 (Coordinate records).
+void launch_field_network(const NetMeta& net, const __half* table, const __half* w_density, const __half* w_rgb,
+                          const float4* pos_dt, const uint32_t* sample_ray, const float4* ray_dir_t,
+                          const float* coords7, uint64_t n, uint2* rgbsigma, cudaStream_t stream);
+//   density only: positions (3 floats, stride given in floats) -> 16 halves per position.
+void launch_field_density(const NetMeta& net, const __half* table, const __half* w_density, const float* positions,
+                          uint32_t stride, uint64_t n, __half* out16, cudaStream_t stream);
+//   analytic blob field in fp32 -> (r,g,b logits, sigma), 4 floats per sample.
+void launch_field_blobs(const DevCfg& g, const float* blobs, uint32_t n_blobs, const float* color_map,
+                        const float4* pos_dt, uint64_t n, float4* rgbsigma, cudaStream_t stream);
+
+struct DevPost {
+    float exposure_scale;      // 2^exposure
+    float bg[4];               // background colour, already converted to the accumulation space
+    int color_space, tonemap_curve, to_srgb;
+};
+
+// Compositing of rays [ray_begin, ray_end) over the compact layout, followed by shade, accumulate and
+// tonemap of the ray's pixel.  Exactly one of rgbs_half / rgbs_float is non-null.  Any output may be null.
+void launch_composite(const DevCfg& g, const DevView& v, const DevPost& post, const uint64_t* offsets,
+                      uint64_t ray_begin, uint64_t ray_end, const float4* pos_dt, const uint2* rgbs_half,
+                      const float4* rgbs_float, const uint8_t* ray_end_reason, float4* out, float4* accum,
+                      float4* rgba_raw, uint32_t* n_composited, FrameCounters* counters, cudaStream_t stream);
+
+// Compositing over Coordinate records (stage entry srf_volume_rendering): no post stage.
+void launch_composite_coords(const DevCfg& g, const DevView& v, const uint64_t* offsets, uint64_t n_rays,
+                             const float* coords7, const uint2* rgbs_half, float4* rgba, uint32_t* n_composited,
+                             cudaStream_t stream);
+
+// Grid refresh pieces (srf_refresh.cu).
+struct RefreshRng { uint64_t state, inc; };
+// One sampling pass: cell pick, jitter, encoding, density output 0, atomicMax into grid_current.
+void launch_refresh_sample(const DevCfg& g, const NetMeta& net, const __half* table, const __half* w_density,
+                           const float* grid, float* grid_current, uint32_t n_elements, uint32_t step, RefreshRng rng,
+                           float thresh, uint32_t aabb_scale, cudaStream_t stream);
+// Max-decay of every cell (when do_decay) and the mean of max(v,0) over the first `cells` entries.
+void launch_decay_and_mean(float* grid, const float* grid_current, uint32_t total, uint32_t cells, float decay,
+                           int do_decay, float* partial_a, float* partial_b, float* mean, cudaStream_t stream);
+void launch_grid_to_bitfield(const DevCfg& g, const float* grid, uint8_t* bits, const float* mean,
+                             float min_optical_thickness, cudaStream_t stream);
+
+void launch_eval_math(int op, const float* a, const float* b, float* out, size_t n, cudaStream_t stream);
+
+}  // namespace srf

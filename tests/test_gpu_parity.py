@@ -1,0 +1,278 @@
+"""GPU parity tests: the CUDA library, called through its C-ABI, against the CPU oracle on the same
+seeded inputs.  Integers (sample counts, march-step ordinals, Morton cells, occupancy bits) and the
+sampler's floats must be bit-exact; RGBA within 1e-3 for the fp16 network (tensor-core accumulation
+order is unspecified) and bit-exact (checked as <= 1e-5) for the fp32 analytic field."""
+import numpy as np
+import pytest
+
+from sphericalrf_b200 import abi
+
+from helpers import make_oracle, make_renderer, small_scene
+
+pytestmark = pytest.mark.gpu
+
+
+def _bits_equal(a, b):
+    return np.array_equal(np.ascontiguousarray(a).view(np.uint32), np.ascontiguousarray(b).view(np.uint32))
+
+
+def test_device_math_matches_oracle_bit_for_bit(built_lib, oracle_mod):
+    from sphericalrf_b200.testbed import eval_math
+    rng = np.random.default_rng(3)
+    n = 1 << 20
+    cases = {
+        0: (rng.normal(size=n), rng.normal(size=n)),
+        1: (rng.random(n) * 2.002 - 1.001, None),
+        2: ((rng.random(n) * 2 - 1) * 300, None),
+        3: ((rng.random(n) * 2 - 1) * 300, None),
+        4: ((rng.random(n) * 2 - 1) * 100, None),
+        5: (np.exp((rng.random(n) * 2 - 1) * 80), None),
+    }
+    for op, (a, b) in cases.items():
+        a = a.astype(np.float32)
+        b = None if b is None else b.astype(np.float32)
+        dev = eval_math(op, a, b)
+        ref = oracle_mod.eval_math(op, a, b)
+        assert _bits_equal(dev, ref), f"op {op}: {np.count_nonzero(dev.view(np.uint32) != ref.view(np.uint32))} mismatches"
+
+
+SAMPLER_CASES = [
+    dict(sampling="Disparity", warp=abi.WARP_ERP),
+    dict(sampling="Original", warp=abi.WARP_ERP, radius=4.0),
+    dict(sampling="Log", warp=abi.WARP_SINUSOIDAL, aabb_scale=64),
+    dict(sampling="Original", warp=abi.WARP_NGP, aabb_scale=4, radius=1.2),
+    dict(sampling="Original", warp=abi.WARP_MIPNERF360, aabb_scale=8, radius=1.5),
+    dict(sampling="Original", warp=abi.WARP_DONERF, aabb_scale=4, radius=1.5),
+    dict(sampling="Original", warp=abi.WARP_SIGMOID, aabb_scale=8, radius=2.0),
+    dict(sampling="Original", warp=abi.WARP_NGP, aabb_scale=4, radius=1.5, cascades=3, grid_dist=abi.GRID_WARPED_EXP),
+    dict(sampling="Original", warp=abi.WARP_NGP, aabb_scale=4, radius=1.5, cascades=2, grid_dist=abi.GRID_METRIC_RECIPROCAL),
+]
+
+
+@pytest.mark.parametrize("case", SAMPLER_CASES, ids=lambda c: f"{c['sampling']}-warp{c['warp']}-c{c.get('cascades', 1)}")
+def test_sampler_bit_exact(built_lib, oracle_mod, case):
+    kw = dict(case)
+    sampling = kw.pop("sampling")
+    sc = small_scene(kind="blobs", sampling="Disparity" if sampling == "Log" else sampling, **kw)
+    if sampling == "Log":
+        sc["cfg"].sampling_type = abi.SAMPLING_LOG
+        sc["cfg"].far_distance = 100.0
+    r = make_renderer(sc)
+    bits = r.download_bitfield()
+    orc = make_oracle(oracle_mod, sc, bits)
+    b2, mean = orc.update_grid_bitfield(sc["grid"])
+    assert np.array_equal(bits, b2)
+    assert _bits_equal(np.float32(mean), np.float32(r.grid_mean()))
+    view = sc["view"]
+    n = orc.n_rays(view)
+    cap = 1 << 22
+    oc, opd, oo, ocell, _ = orc.march(view, 0, n, cap)
+    gc, gpd, go, gcell = r.dump_samples(view, 0, n, cap)
+    assert np.array_equal(oc, gc), "per-ray sample counts"
+    assert np.array_equal(oo, go), "march-step ordinals"
+    assert np.array_equal(ocell, gcell), "Morton cell indices"
+    assert _bits_equal(opd, gpd), "warped positions and step widths"
+    assert oc.sum() > 0
+    # rays: direction, t at the first occupied step, alive flag
+    import torch
+    dev = torch.device("cuda", 0)
+    d = torch.zeros((n, 3), device=dev); t = torch.zeros(n, device=dev)
+    al = torch.zeros(n, dtype=torch.uint8, device=dev); px = torch.zeros(n, dtype=torch.int32, device=dev)
+    st = built_lib.srf_generate_rays(r.ctx, view, d.data_ptr(), t.data_ptr(), al.data_ptr(), px.data_ptr(), None)
+    assert st == 0
+    torch.cuda.synchronize()
+    od, ot, oal, opx = orc.generate_rays(view)
+    assert np.array_equal(oal, al.cpu().numpy())
+    assert np.array_equal(opx, px.cpu().numpy().astype(np.uint32))
+    assert _bits_equal(od, d.cpu().numpy())
+    assert _bits_equal(ot, t.cpu().numpy())
+
+
+@pytest.mark.parametrize("sampling,radius", [("Disparity", 0.5), ("Original", 4.0)])
+@pytest.mark.parametrize("mode", [abi.MODE_SHADE, abi.MODE_DEPTH, abi.MODE_AO, abi.MODE_COST])
+def test_blob_field_frame_bit_exact(built_lib, oracle_mod, sampling, radius, mode):
+    sc = small_scene(kind="blobs", sampling=sampling, radius=radius, width=32, height=24)
+    sc["view"].render_mode = mode
+    r = make_renderer(sc)
+    bits = r.download_bitfield()
+    orc = make_oracle(oracle_mod, sc, bits)
+    post = abi.default_post()
+    got = r.render_frame(sc["view"], post, want_raw=True, want_counts=True, want_stats=True)
+    ref = orc.render_frame(sc["view"], post)
+    counts, *_ = orc.march(sc["view"], 0, orc.n_rays(sc["view"]), 1 << 22)
+    assert np.array_equal(counts, got["n_samples"])
+    assert got["stats"]["n_samples_composited"] == ref["stats"]["n_samples_composited"]
+    assert got["stats"]["n_rays_hit"] == ref["stats"]["n_rays_hit"]
+    assert np.abs(got["rgba_raw"] - ref["rgba_raw"]).max() <= 1e-5
+    assert np.abs(got["out"] - ref["out"]).max() <= 1e-5
+    assert _bits_equal(got["rgba_raw"], ref["rgba_raw"]), "analytic field: premultiplied RGBA bit-exact"
+    assert _bits_equal(got["out"], ref["out"]), "analytic field: output pixels bit-exact"
+    assert ref["stats"]["n_rays_hit"] > 0
+
+
+def test_early_termination_bit_exact(built_lib, oracle_mod):
+    sc = small_scene(kind="blobs", sampling="Original", radius=4.0, width=32, height=24)
+    sc["blobs"][:, 4] = 4000.0            # opaque blobs: rays stop inside them
+    r = make_renderer(sc)
+    orc = make_oracle(oracle_mod, sc, r.download_bitfield())
+    got = r.render_frame(sc["view"], abi.default_post(), want_raw=True, want_stats=True)
+    ref = orc.render_frame(sc["view"], abi.default_post())
+    assert ref["stats"]["n_samples_composited"] < ref["stats"]["n_samples"] or ref["stats"]["n_samples_composited"] < got["stats"]["n_samples"]
+    assert got["stats"]["n_samples_composited"] == ref["stats"]["n_samples_composited"]
+    assert _bits_equal(got["rgba_raw"], ref["rgba_raw"])
+
+
+@pytest.mark.parametrize("levels,features", [(16, 2), (8, 4)])
+def test_network_frame_within_tolerance(built_lib, oracle_mod, levels, features):
+    sc = small_scene(kind="net", width=24, height=16)
+    cfg = sc["cfg"]
+    cfg.n_levels, cfg.n_features_per_level = levels, features
+    if features == 4:
+        cfg.per_level_scale = 2.0
+        from sphericalrf_b200 import synth
+        sc["hash_table"], sc["density_mlp"], sc["rgb_mlp"] = synth.network_params(cfg, 11, 12, table_range=0.5)
+    r = make_renderer(sc)
+    orc = make_oracle(oracle_mod, sc, r.download_bitfield())
+    post = abi.default_post()
+    got = r.render_frame(sc["view"], post, want_raw=True, want_counts=True)
+    ref = orc.render_frame(sc["view"], post)
+    counts, *_ = orc.march(sc["view"], 0, orc.n_rays(sc["view"]), 1 << 22)
+    assert np.array_equal(counts, got["n_samples"])
+    assert np.abs(got["rgba_raw"] - ref["rgba_raw"]).max() <= 1e-3     # fp16 MLP tolerance
+    assert np.abs(got["out"] - ref["out"]).max() <= 1e-3
+    assert ref["rgba_raw"][:, 3].max() > 0.05
+
+
+def test_network_stage_entry_points(built_lib, oracle_mod):
+    """srf_sample_count/offsets/emit -> srf_network_inference -> srf_volume_rendering, the reference's
+    class-method sequence, against the oracle stage by stage."""
+    import torch
+    sc = small_scene(kind="net", width=16, height=12)
+    r = make_renderer(sc)
+    orc = make_oracle(oracle_mod, sc, r.download_bitfield())
+    view = sc["view"]
+    n = r.n_rays(view)
+    dev = torch.device("cuda", 0)
+    counts = torch.zeros(n, dtype=torch.int32, device=dev)
+    offsets = torch.zeros(n + 1, dtype=torch.int64, device=dev)
+    assert built_lib.srf_sample_count(r.ctx, view, counts.data_ptr(), None) == 0
+    assert built_lib.srf_sample_offsets(r.ctx, counts.data_ptr(), n, offsets.data_ptr(), None) == 0
+    total = int(offsets[-1].item())
+    coords = torch.zeros((total, 7), device=dev)
+    assert built_lib.srf_sample_emit(r.ctx, view, offsets.data_ptr(), total, coords.data_ptr(), None, None, None) == 0
+    rgbs = torch.zeros((total, 4), dtype=torch.float16, device=dev)
+    assert built_lib.srf_network_inference(r.ctx, coords.data_ptr(), total, rgbs.data_ptr(), None) == 0
+    rgba = torch.zeros((n, 4), device=dev)
+    ncomp = torch.zeros(n, dtype=torch.int32, device=dev)
+    assert built_lib.srf_volume_rendering(r.ctx, view, offsets.data_ptr(), n, coords.data_ptr(), rgbs.data_ptr(),
+                                          rgba.data_ptr(), ncomp.data_ptr(), None) == 0
+    dens = torch.zeros((total, 16), dtype=torch.float16, device=dev)
+    pos = coords[:, :3].contiguous()
+    assert built_lib.srf_network_density(r.ctx, pos.data_ptr(), total, dens.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    oc, opd, _, _, _ = orc.march(view, 0, n, total + 1)
+    assert np.array_equal(oc, counts.cpu().numpy().astype(np.uint32))
+    c = coords.cpu().numpy()
+    assert _bits_equal(c[:, :4], opd)
+    ref = orc.network_inference(c).astype(np.float32)
+    got = rgbs.cpu().numpy().astype(np.float32)
+    assert np.abs(ref - got).max() <= 2e-2 * max(1.0, np.abs(ref).max())   # raw fp16 network outputs
+    refd = orc.network_density(c[:, :3]).astype(np.float32)
+    gotd = dens.cpu().numpy().astype(np.float32)
+    assert np.abs(refd - gotd).max() <= 2e-2 * max(1.0, np.abs(refd).max())
+    assert np.abs(got[:, 3] - gotd[:, 0]).max() == 0.0     # sigma is density output 0
+    frame = orc.render_frame(view, abi.default_post())
+    assert np.abs(frame["rgba_raw"] - rgba.cpu().numpy()).max() <= 1e-3
+
+
+def test_grid_refresh_bit_exact(built_lib, oracle_mod):
+    """16 consecutive refreshes: every float of the grid and every bit after every step."""
+    sc = small_scene(kind="net", grid_size=32)
+    cfg = sc["cfg"]
+    min_step = np.float32(np.sqrt(3.0) / cfg.maximum_marching_steps)
+    rng = np.random.Generator(np.random.PCG64(3000))
+    prior = (sc["grid"].astype(np.float64) * min_step * rng.uniform(0.5, 1.5, sc["grid"].shape[0])).astype(np.float32)
+    prior[::97] = -1.0                       # masked cells stay negative
+    sc["grid"] = prior
+    r = make_renderer(sc)
+    r.refresh_reset(3001)
+    orc = make_oracle(oracle_mod, sc, None)
+    grid = prior.copy()
+    orng = oracle_mod.rng_seed(3001)
+    step = 0
+    for k in range(16):
+        training_step = 0 if k < 12 else 256 + k       # the last refreshes use the quarter/quarter sampling
+        obits, omean, step = orc.refresh(grid, step, training_step, orng)
+        r.refresh_grid(training_step)
+        g = r.download_density_grid()
+        assert _bits_equal(g, grid), f"refresh {k}: grid floats"
+        assert np.array_equal(r.download_bitfield(), obits), f"refresh {k}: bits"
+        assert _bits_equal(np.float32(r.grid_mean()), np.float32(omean)), f"refresh {k}: mean"
+    assert np.unpackbits(obits).mean() > 0.0
+
+
+def test_sharded_frame_equals_whole_frame(built_lib):
+    """Rays partitioned into row-block shards give byte-identical pixels to the single-shard frame."""
+    sc = small_scene(kind="net", width=24, height=21)      # 21 rows: a partial last block
+    r = make_renderer(sc)
+    post = abi.default_post()
+    whole = r.render_frame(sc["view"], post)["out"].reshape(21, 24, 4)
+    for count in (2, 3):
+        img = np.zeros_like(whole)
+        for rank in range(count):
+            v = abi.View.from_buffer_copy(sc["view"])
+            v.shard_count, v.shard_rank, v.shard_rows = count, rank, 4
+            part = r.render_frame(v, post)["out"]
+            rows = [y for y in range(21) if (y // 4) % count == rank]
+            img[rows] = part.reshape(len(rows), 24, 4)
+        assert np.array_equal(img.view(np.uint32), whole.view(np.uint32))
+
+
+def test_batched_frame_equals_single_batch(built_lib):
+    sc = small_scene(kind="blobs", width=160, height=128, sampling="Original", radius=4.0)   # > 4096 rays: several groups
+    r = make_renderer(sc)
+    a = r.render_frame(sc["view"], abi.default_post(), want_stats=True)
+    assert a["stats"]["n_batches"] == 1
+    r.reserve(max(1, a["stats"]["n_samples"] // 3))
+    b = r.render_frame(sc["view"], abi.default_post(), want_stats=True)
+    assert b["stats"]["n_batches"] > 1
+    assert np.array_equal(a["out"].view(np.uint32), b["out"].view(np.uint32))
+
+
+def test_host_image_and_spp_accumulation(built_lib, oracle_mod):
+    sc = small_scene(kind="blobs", width=20, height=12)
+    sc["cfg"].snap_to_pixel_centers_in_rendering = 0      # spp passes differ
+    r = make_renderer(sc)
+    orc = make_oracle(oracle_mod, sc, r.download_bitfield())
+    post = abi.default_post()
+    post.background_color[:] = [1.0, 1.0, 1.0, 1.0]
+    post.tonemap_curve = abi.TONEMAP_ACES
+    post.to_srgb = 1
+    img = r.render(sc["view"], post, spp=3)
+    accum = None
+    for i in range(3):
+        v = abi.View.from_buffer_copy(sc["view"])
+        v.spp_index = i
+        ref = orc.render_frame(v, post, accum=accum)
+        accum = ref["accum"]
+    assert np.abs(img.reshape(-1, 4) - ref["out"]).max() <= 1e-5
+    assert _bits_equal(img.reshape(-1, 4), ref["out"])
+
+
+def test_errors_are_reported_not_faked(built_lib):
+    from sphericalrf_b200.testbed import Renderer
+    cfg = abi.default_config()
+    cfg.grid_size = 100
+    with pytest.raises(abi.SrfError) as e:
+        Renderer(cfg, 0)
+    assert e.value.status == abi.ERR_ARG
+    sc = small_scene(kind="net")
+    r = Renderer(sc["cfg"], 0)
+    with pytest.raises(abi.SrfError) as e:      # no weights uploaded
+        r.render_frame(sc["view"], abi.default_post())
+    assert e.value.status == abi.ERR_STATE
+    sc["view"].render_mode = abi.MODE_NORMALS
+    r.upload_network(sc["hash_table"], sc["density_mlp"], sc["rgb_mlp"])
+    with pytest.raises(abi.SrfError) as e:
+        r.render_frame(sc["view"], abi.default_post())
+    assert e.value.status == abi.ERR_ARG
