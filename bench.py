@@ -264,7 +264,7 @@ def run_ours(args):
         "metric": "render throughput", "value": value, "unit": "Mrays/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
-        "config": {"workload": "config1 full inference frame 1245x825, fp16 network, 128^3 bitfield",
+        "config": {"workload": f"config1 full inference frame {WIDTH}x{HEIGHT}, fp16 network, 128^3 bitfield",
                    "frames_per_step": n_views, "rays_per_frame": WIDTH * HEIGHT, "samples_per_frame_shard": int(n_samples),
                    "partition": f"rows in blocks of 8 round-robin over {world} rank(s), gather to rank 0",
                    "l2": "per-frame working set (sample buffers) far larger than L2; no flush needed"},
@@ -294,7 +294,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--res", default=None, help="WxH: a smaller image of the same scene, for profiler captures only "
+                                                "(the benchmark number is the default 1245x825)")
     args = ap.parse_args()
+    if args.res:
+        global WIDTH, HEIGHT
+        WIDTH, HEIGHT = (int(x) for x in args.res.lower().split("x"))
     if args.impl == "reference":
         run_reference(args)
     else:
