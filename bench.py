@@ -174,21 +174,11 @@ def run_ours(args):
     n_local = r.n_rays(view)
     rays_per_step = WIDTH * HEIGHT * n_views
 
-    # tiles are padded to the largest shard so that the gather moves equal-sized buffers
-    counts = [r.n_rays(abi.make_view(sc["cameras"][0], WIDTH, HEIGHT, sc["rfl"], shard_rows=8, shard_count=world, shard_rank=k))
-              for k in range(world)]
-    n_pad = max(counts)
-    out = torch.zeros((n_views, n_pad, 4), dtype=torch.float32, device=dev)
-    accum = torch.zeros((n_pad, 4), dtype=torch.float32, device=dev)
-    gathered, pix_index, image = None, None, None
-    if world > 1:
-        if rank == 0:
-            gathered = [torch.zeros((n_views, n_pad, 4), dtype=torch.float32, device=dev) for _ in range(world)]
-            image = torch.zeros((n_views, HEIGHT * WIDTH, 4), dtype=torch.float32, device=dev)
-            pix_index = []
-            for rk in range(world):
-                rows = torch.tensor([y for y in range(HEIGHT) if (y // 8) % world == rk], dtype=torch.int64, device=dev)
-                pix_index.append((rows[:, None] * WIDTH + torch.arange(WIDTH, device=dev)[None, :]).reshape(-1))
+    from sphericalrf_b200.sharding import TileGather
+    tg = TileGather(WIDTH, HEIGHT, n_views, 4, 8, dev)
+    assert tg.n_local == n_local
+    out = tg.tiles
+    accum = torch.zeros((tg.n_pad, 4), dtype=torch.float32, device=dev)
     host_img = torch.zeros((n_views, HEIGHT, WIDTH, 4), dtype=torch.float32).pin_memory() if rank == 0 else None
     stats = abi.FrameStats()
 
@@ -196,10 +186,7 @@ def run_ours(args):
         for k in range(n_views):
             r.render_frame_device(view, post, out[k], accum, None, None, None, None)
         if world > 1:
-            dist.gather(out, gathered, dst=0)
-            if rank == 0:
-                for rk in range(world):
-                    image[:, pix_index[rk]] = gathered[rk][:, :counts[rk]]
+            tg.gather()
 
     def step_e2e():
         if world == 1:
@@ -209,7 +196,7 @@ def run_ours(args):
         else:
             step_device()
             if rank == 0:
-                host_img.view(n_views, HEIGHT * WIDTH, 4).copy_(image, non_blocking=True)
+                host_img.view(n_views, HEIGHT * WIDTH, 4).copy_(tg.image, non_blocking=True)
                 torch.cuda.current_stream().synchronize()
 
     def timed(fn, steps, warmup, sample_clocks=False):

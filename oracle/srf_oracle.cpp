@@ -999,13 +999,20 @@ int srfo_update_grid_bitfield(const srf_config_t* cfg, const float* grid, uint8_
     return 0;
 }
 
-void srfo_rng_seed(srfo_rng_t* rng, uint64_t seed) {
+void srfo_rng_seed_seq(srfo_rng_t* rng, uint64_t seed, uint64_t seq) {
     rng->state = 0u;
-    rng->inc = (1ull << 1u) | 1u;
+    rng->inc = (seq << 1u) | 1u;
     pcg_next_uint(*rng);
     rng->state += seed;
     pcg_next_uint(*rng);
 }
+void srfo_rng_seed(srfo_rng_t* rng, uint64_t seed) { srfo_rng_seed_seq(rng, seed, 1u); }
+uint32_t srfo_rng_next_uint(srfo_rng_t* rng) { return pcg_next_uint(*rng); }
+float srfo_rng_next_float(srfo_rng_t* rng) { return pcg_next_float(*rng); }
+void srfo_rng_advance(srfo_rng_t* rng, uint64_t delta) { pcg_advance(*rng, delta); }
+float srfo_ld_random_val(uint32_t index, uint32_t seed, uint32_t dim) { return ld_random_val(index, seed, dim); }
+uint32_t srfo_morton3d(uint32_t x, uint32_t y, uint32_t z) { return morton3D(x, y, z); }
+uint32_t srfo_sobol(uint32_t index, uint32_t dim) { return sobol(index, dim); }
 
 /* Testbed::train_prep_nerf (testbed.cu:203-239). */
 int srfo_refresh_grid(const srf_config_t* cfg, const srfo_model_t* model, float* grid, uint8_t* bitfield,

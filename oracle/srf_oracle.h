@@ -60,6 +60,14 @@ int srfo_render_frame(const srf_config_t* cfg, const srf_view_t* view, const srf
 
 int srfo_update_grid_bitfield(const srf_config_t* cfg, const float* grid, uint8_t* bitfield, float* mean);
 void srfo_rng_seed(srfo_rng_t* rng, uint64_t seed);
+/* small taps for known-answer tests */
+void srfo_rng_seed_seq(srfo_rng_t* rng, uint64_t seed, uint64_t seq);
+uint32_t srfo_rng_next_uint(srfo_rng_t* rng);
+float srfo_rng_next_float(srfo_rng_t* rng);
+void srfo_rng_advance(srfo_rng_t* rng, uint64_t delta);
+float srfo_ld_random_val(uint32_t index, uint32_t seed, uint32_t dim);
+uint32_t srfo_morton3d(uint32_t x, uint32_t y, uint32_t z);
+uint32_t srfo_sobol(uint32_t index, uint32_t dim);
 int srfo_refresh_grid(const srf_config_t* cfg, const srfo_model_t* model, float* grid, uint8_t* bitfield,
                       float* mean, uint32_t* refresh_step, uint32_t training_step, srfo_rng_t* rng);
 

@@ -1,0 +1,65 @@
+"""Ray sharding across ranks and the gather of rendered tiles.
+
+A frame's rays are cut into blocks of `shard_rows` image rows; block b belongs to rank
+b % world.  Every rank renders its blocks into a compact tile buffer (blocks concatenated, the
+layout srf_render_frame writes) and rank 0 gathers the tiles and scatters them back into image
+order.  The per-ray arithmetic does not depend on the partition, so the assembled image is
+byte-identical to the single-rank image.  The only exchange step is this gather; weights, grid
+and bitfield are replicated.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def shard_row_indices(height: int, shard_rows: int, world: int, rank: int):
+    """Image rows owned by `rank`, in the order they appear in its tile buffer."""
+    return [y for y in range(height) if (y // shard_rows) % world == rank]
+
+
+def shard_ray_count(width: int, height: int, shard_rows: int, world: int, rank: int) -> int:
+    return len(shard_row_indices(height, shard_rows, world, rank)) * width
+
+
+class TileGather:
+    """Gathers per-rank tile buffers (n_views, n_local_rays, C) on rank 0 and assembles images.
+
+    Tiles are padded to the largest shard so that every rank contributes an equal-sized buffer
+    (a plain `gather`); the padding rows are never read."""
+
+    def __init__(self, width: int, height: int, n_views: int, channels: int = 4, shard_rows: int = 8,
+                 device="cpu", dtype=torch.float32, group=None):
+        self.width, self.height, self.n_views, self.channels = width, height, n_views, channels
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.counts = [shard_ray_count(width, height, shard_rows, self.world, r) for r in range(self.world)]
+        self.n_local = self.counts[self.rank]
+        self.n_pad = max(self.counts)
+        self.device = torch.device(device)
+        # the tile buffer the renderer writes into
+        self.tiles = torch.zeros((n_views, self.n_pad, channels), dtype=dtype, device=self.device)
+        self.image = None
+        self._recv = None
+        self._pix = None
+        if self.rank == 0:
+            self.image = torch.zeros((n_views, height * width, channels), dtype=dtype, device=self.device)
+            if self.world > 1:
+                self._recv = [torch.zeros_like(self.tiles) for _ in range(self.world)]
+            cols = torch.arange(width, device=self.device)[None, :]
+            self._pix = []
+            for r in range(self.world):
+                rows = torch.tensor(shard_row_indices(height, shard_rows, self.world, r), dtype=torch.int64, device=self.device)
+                self._pix.append((rows[:, None] * width + cols).reshape(-1))
+
+    def gather(self):
+        """Collective: after it, rank 0's `image` holds the n_views assembled images."""
+        if self.world == 1:
+            self.image[:, self._pix[0]] = self.tiles[:, : self.counts[0]]
+            return self.image
+        dist.gather(self.tiles, self._recv if self.rank == 0 else None, dst=0, group=self.group)
+        if self.rank == 0:
+            for r in range(self.world):
+                self.image[:, self._pix[r]] = self._recv[r][:, : self.counts[r]]
+        return self.image
