@@ -84,3 +84,12 @@ def test_product_never_touches_the_oracle():
             list((ROOT / "include").glob("*.h")):
         if p.is_file() and p.suffix in (".py", ".cu", ".cuh", ".h"):
             assert "oracle" not in p.read_text().replace("test oracle", "").lower() or p.name == "synth.py", p
+
+
+def test_cpp_shim_compiles():
+    cxx = "/usr/bin/g++" if Path("/usr/bin/g++").exists() else shutil.which("g++")
+    if not cxx:
+        pytest.skip("no C++ compiler")
+    r = subprocess.run([cxx, "-std=c++17", "-fsyntax-only", "-Wall", "-Werror", "-I", str(ROOT / "include"), "-x", "c++",
+                        str(ROOT / "include" / "srf_shim.hpp")], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
