@@ -90,6 +90,6 @@ def test_cpp_shim_compiles():
     cxx = "/usr/bin/g++" if Path("/usr/bin/g++").exists() else shutil.which("g++")
     if not cxx:
         pytest.skip("no C++ compiler")
-    r = subprocess.run([cxx, "-std=c++17", "-fsyntax-only", "-Wall", "-Werror", "-I", str(ROOT / "include"), "-x", "c++",
-                        str(ROOT / "include" / "srf_shim.hpp")], capture_output=True, text=True)
+    r = subprocess.run([cxx, "-std=c++17", "-fsyntax-only", "-Wall", "-Werror", "-I", str(ROOT / "include"), "-x", "c++", "-"],
+                       input='#include "srf_shim.hpp"\nint main() { return 0; }\n', capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
