@@ -266,6 +266,24 @@ srf_status srf_dump_samples(srf_ctx* ctx, const srf_view_t* view, uint64_t ray_f
    rendered in several batches.  0 = grow on demand (the default). */
 srf_status srf_reserve(srf_ctx* ctx, uint64_t max_samples);
 
+/* No counterpart in the reference.  srf_sample_offsets for callers that may not allocate device
+   memory: programs that gave the whole GPU to their own pool at start-up, frame loops that must avoid
+   the device-wide synchronisation cudaMalloc/cudaFree imply, hosts that forbid allocation after
+   initialisation.  The tile sums of the scan live in a fixed array inside the library image instead of
+   a context buffer, so this call performs no cudaMalloc/cudaFree and calls no allocating routine.
+   Limits and rules:
+     - at most 33 554 432 counts (16 384 tile sums of 2048 counts; 128 KiB held by every GPU that loads
+       the library, until the process exits); more is refused with SRF_ERR_CAPACITY and a message;
+     - the first call on a device looks the array's device address up (cudaGetSymbolAddress with that
+       device current); make that first call before any stream capture begins;
+     - all calls on a device share the array: calls whose kernels may overlap on the GPU (different
+       streams without ordering) race and must be serialised by the caller.  Nothing has to be cleared
+       between calls: each call overwrites every entry it later reads.
+   `err`/`err_len` (may be NULL/0) receive the message of a failure.  Inputs and outputs are as in
+   srf_sample_offsets; no context is needed. */
+srf_status srf_sample_offsets_static(int device, const uint32_t* d_counts, uint64_t n_rays, uint64_t* d_offsets,
+                                     void* stream, char* err, size_t err_len);
+
 /* Evaluates the canonical elementary functions on the device (self-test tap):
    op 0 atan2(a,b), 1 asin(a), 2 cos(a), 3 sin(a), 4 exp(a), 5 log(a). */
 srf_status srf_eval_math(int device, int op, const float* h_a, const float* h_b, float* h_out, size_t n);

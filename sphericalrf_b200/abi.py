@@ -173,6 +173,7 @@ SYMBOLS = {
     "srf_dump_samples": (C.c_int, [_ctx, _P(View), C.c_uint64, C.c_uint64, C.c_uint64, _vp, _vp, _vp, _vp,
                                    _P(C.c_uint64)]),
     "srf_reserve": (C.c_int, [_ctx, C.c_uint64]),
+    "srf_sample_offsets_static": (C.c_int, [C.c_int, _vp, C.c_uint64, _vp, _vp, C.c_char_p, C.c_size_t]),
     "srf_eval_math": (C.c_int, [C.c_int, C.c_int, _vp, _vp, _vp, C.c_size_t]),
 }
 

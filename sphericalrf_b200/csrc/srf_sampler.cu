@@ -244,4 +244,76 @@ void launch_eval_math(int op, const float* a, const float* b, float* out, size_t
     k_eval_math<<<blocks_for(n, 256), 256, 0, stream>>>(op, a, b, out, n);
 }
 
+// ---- srf_sample_offsets_static: the exclusive scan with its scratch inside the library ----------
+//
+// Some callers of the scan cannot allocate device memory at all: a renderer embedded in an
+// application that handed the whole GPU to its own memory pool at start-up, a frame loop that must
+// never hit the implicit device synchronisation of cudaMalloc/cudaFree, or a plug-in host that
+// forbids allocation after initialisation.  srf_sample_offsets() keeps its tile sums in a buffer the
+// context allocates (and grows) on demand; this variant keeps them in a fixed array that is part of
+// the library image instead, so the call itself never allocates.
+//
+// The price: the array is sized for a stated maximum, every GPU that loads the library carries it
+// until the process exits, and all calls on one device share it (see the header for the rules).
+namespace {
+
+constexpr uint64_t kStaticScanMaxTiles = 16384;                                  // 128 KiB of tile sums
+constexpr uint64_t kStaticScanMaxRays = kStaticScanMaxTiles * (uint64_t)kScanTile;   // 33 554 432 counts
+
+static __device__ __align__(256) unsigned long long g_static_scan_tile_sums[kStaticScanMaxTiles + 1];
+
+constexpr int kMaxDevices = 64;
+// Device address of the array above, per device.  In host code the array's NAME is only a handle for
+// the runtime, not a device address; each device has its own copy at its own address, found once with
+// cudaGetSymbolAddress while that device is current.
+void* g_static_scan_ptr[kMaxDevices] = {};
+
+void write_error(char* err, size_t err_len, const char* msg) {
+    if (!err || err_len == 0) return;
+    size_t i = 0;
+    for (; msg[i] && i + 1 < err_len; ++i) err[i] = msg[i];
+    err[i] = 0;
+}
+
+}  // namespace
 }  // namespace srf
+
+extern "C" srf_status srf_sample_offsets_static(int device, const uint32_t* d_counts, uint64_t n_rays,
+                                                uint64_t* d_offsets, void* stream, char* err, size_t err_len) {
+    using namespace srf;
+    if (!d_counts || !d_offsets) { write_error(err, err_len, "srf_sample_offsets_static: NULL buffer"); return SRF_ERR_ARG; }
+    if (device < 0 || device >= kMaxDevices) { write_error(err, err_len, "srf_sample_offsets_static: device index out of range"); return SRF_ERR_ARG; }
+    if (n_rays > kStaticScanMaxRays) {
+        write_error(err, err_len, "srf_sample_offsets_static: more than 33554432 counts; the built-in scratch holds "
+                                  "16384 tile sums of 2048 counts each - use srf_sample_offsets");
+        return SRF_ERR_CAPACITY;
+    }
+    int prev = -1;
+    if (cudaGetDevice(&prev) != cudaSuccess) { write_error(err, err_len, "srf_sample_offsets_static: cudaGetDevice failed"); return SRF_ERR_CUDA; }
+    if (prev != device && cudaSetDevice(device) != cudaSuccess) {
+        write_error(err, err_len, "srf_sample_offsets_static: cudaSetDevice failed");
+        return SRF_ERR_CUDA;
+    }
+    srf_status st = SRF_OK;
+    if (!g_static_scan_ptr[device]) {
+        // first call on this device: look the array's device address up (no allocation; the array is
+        // part of the loaded module)
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scan_tile_sums);
+        if (e != cudaSuccess || !p) {
+            write_error(err, err_len, cudaGetErrorString(e));
+            st = SRF_ERR_CUDA;
+        } else {
+            g_static_scan_ptr[device] = p;
+        }
+    }
+    if (st == SRF_OK) {
+        // every tile sum the later kernels read is written by the first kernel of this call, so
+        // nothing left over from an earlier call needs clearing
+        launch_scan(d_counts, n_rays, d_offsets, g_static_scan_ptr[device], (cudaStream_t)stream);
+        const cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) { write_error(err, err_len, cudaGetErrorString(e)); st = SRF_ERR_CUDA; }
+    }
+    if (prev != device) cudaSetDevice(prev);
+    return st;
+}
