@@ -10,6 +10,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -70,6 +71,9 @@ struct srf_ctx {
     // refresh
     uint32_t refresh_step = 0;
     RefreshRng rng = {0, 0};
+
+    // which engine runs the MLPs of the render path: tcgen05/TMEM (default) or the mma.sync kernel
+    bool use_tcgen05 = true;
 
     // timing
     bool timing = false;
@@ -377,6 +381,7 @@ srf_status srf_create(const srf_config_t* cfg, int device, srf_ctx** out) {
     ctx->cfg = *cfg;
     ctx->device = device;
     resolve(*cfg, &ctx->g, &ctx->min_optical_thickness);
+    if (const char* e = getenv("SRF_B200_MLP")) ctx->use_tcgen05 = std::string(e) != "mma_sync";
     DeviceGuard guard(device);
     auto cleanup = [&](srf_status s) { g_create_error = ctx->err; srf_destroy(ctx); return s; };
 #define CK_CREATE(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) { ctx->err = std::string(#call) + ": " + cudaGetErrorString(e_); return cleanup(SRF_ERR_CUDA); } } while (0)
@@ -644,8 +649,12 @@ srf_status srf_network_inference(srf_ctx* ctx, const float* d_coords, uint64_t n
     srf_status st = check_ready(ctx);
     if (st != SRF_OK) return st;
     DeviceGuard guard(ctx->device);
-    launch_field_network(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, nullptr, nullptr, nullptr, d_coords, n,
-                         (uint2*)d_rgbsigma, (cudaStream_t)stream);
+    if (ctx->use_tcgen05)
+        launch_field_network_tc(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, nullptr, nullptr, nullptr, d_coords, n,
+                                (uint2*)d_rgbsigma, &ctx->d_counters->error_flags, (cudaStream_t)stream);
+    else
+        launch_field_network(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, nullptr, nullptr, nullptr, d_coords, n,
+                             (uint2*)d_rgbsigma, (cudaStream_t)stream);
     SRF_CK(ctx, cudaGetLastError());
     return SRF_OK;
 }
@@ -732,6 +741,10 @@ srf_status srf_render_frame(srf_ctx* ctx, const srf_view_t* view, const srf_post
         if (tm) cudaEventRecord(ctx->ev[3], s);
         if (blobs)
             launch_field_blobs(ctx->g, ctx->blobs, ctx->n_blobs, ctx->cmap, (const float4*)ctx->pos_dt.p, n_s, (float4*)ctx->rgbs.p, s);
+        else if (ctx->use_tcgen05)
+            launch_field_network_tc(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, (const float4*)ctx->pos_dt.p,
+                                    (const uint32_t*)ctx->sample_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, n_s,
+                                    (uint2*)ctx->rgbs.p, &ctx->d_counters->error_flags, s);
         else
             launch_field_network(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, (const float4*)ctx->pos_dt.p,
                                  (const uint32_t*)ctx->sample_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, n_s,
@@ -762,6 +775,7 @@ srf_status srf_render_frame(srf_ctx* ctx, const srf_view_t* view, const srf_post
         stats->error_flags = ctx->h_counters->error_flags;
         stats->ms_sampler = ms_sampler; stats->ms_field = ms_field; stats->ms_composite = ms_comp; stats->ms_post = 0.f;
         if (stats->error_flags & 1u) return fail(ctx, SRF_ERR_TIMEOUT, "a ray hit the march loop's iteration bound");
+        if (stats->error_flags & 2u) return fail(ctx, SRF_ERR_TIMEOUT, "a wait on the tensor-core commit barrier expired");
     }
     return SRF_OK;
 }

@@ -1,0 +1,317 @@
+// srf_field_tc.cu -- the network field on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+// Same data flow as srf_field.cu (NGPNetwork::inference_mixed_precision,
+// internal/network/ngp_network.h:212-279), different engine for the five dense layers: one CTA of
+// 128 threads owns a tile of 128 samples; thread r gathers and interpolates the hash-grid features
+// and the spherical harmonics of sample r straight into the shared-memory image of the MMA's A
+// operand; one thread issues tcgen05.mma (M = 128 samples, N = 64 or 16 neurons, K = 16 per
+// instruction) with the fp32 accumulator in tensor memory; after the commit barrier every thread
+// reads its own sample's row back with tcgen05.ld, applies ReLU, rounds to fp16 and writes the next
+// layer's A operand.  Weights (20 KB) sit in shared memory in the B-operand layout for the lifetime
+// of the CTA.
+//
+// Operand layout (no swizzle, K-major): a matrix of R rows x K halves is stored as K/8 column
+// blocks; block j holds, for every row, the 8 halves k = 8j..8j+7 as one 16-byte unit, rows
+// consecutive: offset(row, k) = (k/8)*R*16 + row*16 + (k%8)*2.  In the tensor core's terms the
+// 8-row x 16-byte core matrices are contiguous (128 B), the stride between 8-row groups (SBO) is
+// 128 B and the stride between the two core matrices along K of one instruction (LBO) is R*16 B.
+//
+// Tensor memory: 128 columns per CTA (columns 0..63 for the 64-wide layers, 64..79 for the 16-wide
+// ones).  At most four such CTAs share an SM: the kernel asks for enough dynamic shared memory that
+// a fifth cannot be resident, so tensor-memory allocation never has to wait.
+//
+// Every wait on the commit barrier is bounded; on expiry the CTA raises an error flag, leaves the
+// tile loop, frees its tensor memory and returns.
+#include "srf_network.cuh"
+
+namespace srf {
+
+namespace {
+
+constexpr int kTcBlock = 128;
+constexpr uint32_t kTmemCols = 128;
+constexpr uint32_t kWaitLimit = 1u << 20;
+
+// shared-memory map (bytes)
+constexpr int kSmW_D1 = 0;                        // [4][64][8]
+constexpr int kSmW_D2 = kSmW_D1 + 4 * 64 * 16;    // [8][16][8]
+constexpr int kSmW_C1 = kSmW_D2 + 8 * 16 * 16;    // [4][64][8]
+constexpr int kSmW_C2 = kSmW_C1 + 4 * 64 * 16;    // [8][64][8]
+constexpr int kSmW_C3 = kSmW_C2 + 8 * 64 * 16;    // [8][16][8]
+constexpr int kSmA0 = kSmW_C3 + 8 * 16 * 16;      // [4][128][8]  hash encoding
+constexpr int kSmA1 = kSmA0 + 4 * 128 * 16;       // [4][128][8]  colour input: density out (0,1), SH (2,3)
+constexpr int kSmH = kSmA1 + 4 * 128 * 16;        // [8][128][8]  hidden activations
+constexpr int kSmBar = kSmH + 8 * 128 * 16;       // mbarrier (8 B) + tensor-memory base (4 B)
+constexpr int kSmTotal = kSmBar + 16;
+static_assert(kSmTotal > 227 * 1024 / 5, "a fifth CTA must not fit: 5 x 128 tensor-memory columns exceed 512");
+static_assert(kSmTotal <= 227 * 1024 / 4, "four CTAs per SM are intended");
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// K-major, no-swizzle shared-memory matrix descriptor.
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;                      // descriptor version of this architecture
+    return d;                                    // base offset 0, layout type 0 (no swizzle)
+}
+
+// kind::f16 instruction descriptor: fp16 A and B (K-major), fp32 accumulator, M = 128.
+__host__ __device__ constexpr uint32_t make_idesc(uint32_t n) {
+    return (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n"
+        :: "r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Bounded wait on the commit barrier; false when the bound expired.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kWaitLimit; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t"
+            "}\n"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+// Weights W[n][k] (row-major, global) -> B-operand image [(k/8)][n][k%8] in shared memory.
+__device__ __forceinline__ void load_weight_image(const __half* __restrict__ w, int n_rows, int k_cols, unsigned char* dst) {
+    const int units = n_rows * (k_cols / 8);                 // 16-byte units
+    for (int u = threadIdx.x; u < units; u += kTcBlock) {
+        const int n = u / (k_cols / 8), j = u % (k_cols / 8);
+        const uint4 v = *reinterpret_cast<const uint4*>(w + n * k_cols + j * 8);
+        *reinterpret_cast<uint4*>(dst + ((size_t)j * n_rows + n) * 16) = v;
+    }
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// 16 fp32 accumulators (as bits) -> two 16-byte units of fp16, optional ReLU; written as column
+// blocks j0, j0+1 of an A image with 128 rows.
+template <bool RELU>
+__device__ __forceinline__ void store_units(const uint32_t (&acc)[16], unsigned char* image, int j0, int row) {
+    float v[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+        v[k] = __uint_as_float(acc[k]);
+        if (RELU) v[k] = v[k] > 0.f ? v[k] : 0.f;
+    }
+    const uint4 u0 = make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
+    const uint4 u1 = make_uint4(pack2(v[8], v[9]), pack2(v[10], v[11]), pack2(v[12], v[13]), pack2(v[14], v[15]));
+    *reinterpret_cast<uint4*>(image + ((size_t)j0 * 128 + row) * 16) = u0;
+    *reinterpret_cast<uint4*>(image + ((size_t)(j0 + 1) * 128 + row) * 16) = u1;
+}
+
+template <int F>
+__global__ void __launch_bounds__(kTcBlock)
+k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __half* __restrict__ wd,
+                   const __half* __restrict__ wc, const float4* __restrict__ pos_dt,
+                   const uint32_t* __restrict__ sample_ray, const float4* __restrict__ ray_dir_t,
+                   const float* __restrict__ coords7, uint64_t n, uint2* __restrict__ rgbsigma,
+                   unsigned int* __restrict__ error_flags) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int tid = threadIdx.x, warp = tid >> 5;
+    uint64_t* bar_ptr = reinterpret_cast<uint64_t*>(smem + kSmBar);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kSmBar + 8);
+    const uint32_t bar = smem_u32(bar_ptr);
+
+    load_weight_image(wd, 64, 32, smem + kSmW_D1);
+    load_weight_image(wd + 64 * 32, 16, 64, smem + kSmW_D2);
+    load_weight_image(wc, 64, 32, smem + kSmW_C1);
+    load_weight_image(wc + 64 * 32, 64, 64, smem + kSmW_C2);
+    load_weight_image(wc + 64 * 32 + 64 * 64, 16, 64, smem + kSmW_C3);
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_row = tmem_base + ((uint32_t)(warp * 32) << 16);     // this warp's quarter of the lanes
+
+    const uint32_t a0 = smem_u32(smem + kSmA0), a1 = smem_u32(smem + kSmA1), ah = smem_u32(smem + kSmH);
+    const uint32_t wD1 = smem_u32(smem + kSmW_D1), wD2 = smem_u32(smem + kSmW_D2), wC1 = smem_u32(smem + kSmW_C1),
+                   wC2 = smem_u32(smem + kSmW_C2), wC3 = smem_u32(smem + kSmW_C3);
+    constexpr uint32_t kIdesc64 = make_idesc(64), kIdesc16 = make_idesc(16);
+    constexpr uint32_t kALbo = 128 * 16, kSbo = 128;          // A images have 128 rows
+
+    // One dense layer: K/16 instructions over an A image (128 rows) and a B image (n_out rows).
+    auto issue_layer = [&](uint32_t a_img, uint32_t b_img, uint32_t n_out, int k16, uint32_t tmem_col, uint32_t idesc) {
+        if (tid == 0) {
+            tc_fence_after();
+            for (int kk = 0; kk < k16; ++kk) {
+                const uint64_t da = make_desc(a_img + (uint32_t)kk * 2u * kALbo, kALbo, kSbo);
+                const uint64_t db = make_desc(b_img + (uint32_t)kk * 2u * n_out * 16u, n_out * 16u, kSbo);
+                mma_f16(tmem_base + tmem_col, da, db, idesc, kk > 0 ? 1u : 0u);
+            }
+            mma_commit(bar);
+        }
+    };
+
+    uint32_t phase = 0;
+    bool failed = false;
+    const uint64_t n_tiles = (n + kTcBlock - 1) / kTcBlock;
+    for (uint64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const uint64_t s = tile * kTcBlock + tid;
+        // ---- encode: one thread per sample, written as 16-byte units of the A images ----
+        float x = 0.f, y = 0.f, z = 0.f, dx = 0.5f, dy = 0.5f, dz = 0.5f;
+        if (s < n) {
+            if (coords7) {
+                const float* c = coords7 + s * 7;
+                x = c[0]; y = c[1]; z = c[2]; dx = c[4]; dy = c[5]; dz = c[6];
+            } else {
+                const float4 p = pos_dt[s];
+                const float4 d = ray_dir_t[sample_ray[s]];
+                x = p.x; y = p.y; z = p.z;
+                dx = (d.x + 1.f) * 0.5f; dy = (d.y + 1.f) * 0.5f; dz = (d.z + 1.f) * 0.5f;   // warp_direction
+            }
+        }
+        {
+            __align__(16) __half enc[32];
+            hash_encode<F>(net, table, x, y, z, enc);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                *reinterpret_cast<uint4*>(smem + kSmA0 + ((size_t)j * 128 + tid) * 16) = *reinterpret_cast<const uint4*>(enc + 8 * j);
+            __align__(16) __half sh[16];
+            sh_encode(dx, dy, dz, sh);
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+                *reinterpret_cast<uint4*>(smem + kSmA1 + ((size_t)(2 + j) * 128 + tid) * 16) = *reinterpret_cast<const uint4*>(sh + 8 * j);
+        }
+        fence_async_smem();
+        __syncthreads();
+
+        uint32_t acc[16];
+        // ---- density layer 1: 32 -> 64, ReLU ----
+        issue_layer(a0, wD1, 64, 2, 0, kIdesc64);
+        failed = !mbar_wait(bar, phase); phase ^= 1;
+        if (__syncthreads_or(failed)) { failed = true; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            tmem_ld16(tmem_row + q * 16, acc);
+            tmem_ld_wait();
+            store_units<true>(acc, smem + kSmH, 2 * q, tid);
+        }
+        tc_fence_before();
+        fence_async_smem();
+        __syncthreads();
+        // ---- density layer 2: 64 -> 16 ----
+        issue_layer(ah, wD2, 16, 4, 64, kIdesc16);
+        failed = !mbar_wait(bar, phase); phase ^= 1;
+        if (__syncthreads_or(failed)) { failed = true; break; }
+        tc_fence_after();
+        tmem_ld16(tmem_row + 64, acc);
+        tmem_ld_wait();
+        store_units<false>(acc, smem + kSmA1, 0, tid);
+        const uint32_t sigma_half = pack2(__uint_as_float(acc[0]), 0.f) & 0xffffu;     // density output 0
+        tc_fence_before();
+        fence_async_smem();
+        __syncthreads();
+        // ---- colour layer 1: [density out, SH] 32 -> 64, ReLU ----
+        issue_layer(a1, wC1, 64, 2, 0, kIdesc64);
+        failed = !mbar_wait(bar, phase); phase ^= 1;
+        if (__syncthreads_or(failed)) { failed = true; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            tmem_ld16(tmem_row + q * 16, acc);
+            tmem_ld_wait();
+            store_units<true>(acc, smem + kSmH, 2 * q, tid);
+        }
+        tc_fence_before();
+        fence_async_smem();
+        __syncthreads();
+        // ---- colour layer 2: 64 -> 64, ReLU (the MMA has finished reading the hidden image when its commit arrives) ----
+        issue_layer(ah, wC2, 64, 4, 0, kIdesc64);
+        failed = !mbar_wait(bar, phase); phase ^= 1;
+        if (__syncthreads_or(failed)) { failed = true; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            tmem_ld16(tmem_row + q * 16, acc);
+            tmem_ld_wait();
+            store_units<true>(acc, smem + kSmH, 2 * q, tid);
+        }
+        tc_fence_before();
+        fence_async_smem();
+        __syncthreads();
+        // ---- colour layer 3: 64 -> 16 (3 used) ----
+        issue_layer(ah, wC3, 16, 4, 64, kIdesc16);
+        failed = !mbar_wait(bar, phase); phase ^= 1;
+        if (__syncthreads_or(failed)) { failed = true; break; }
+        tc_fence_after();
+        tmem_ld16(tmem_row + 64, acc);
+        tmem_ld_wait();
+        if (s < n)
+            rgbsigma[s] = make_uint2(pack2(__uint_as_float(acc[0]), __uint_as_float(acc[1])),
+                                     (pack2(__uint_as_float(acc[2]), 0.f) & 0xffffu) | (sigma_half << 16));
+        tc_fence_before();
+        __syncthreads();
+    }
+    if (failed && tid == 0 && error_flags) atomicOr(error_flags, 2u);
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(kTmemCols) : "memory");
+}
+
+}  // namespace
+
+void launch_field_network_tc(const NetMeta& net, const __half* table, const __half* w_density, const __half* w_rgb,
+                             const float4* pos_dt, const uint32_t* sample_ray, const float4* ray_dir_t,
+                             const float* coords7, uint64_t n, uint2* rgbsigma, unsigned int* error_flags,
+                             cudaStream_t stream) {
+    if (n == 0) return;
+    // per device and cheap: set on every launch rather than cached per process
+    cudaFuncSetAttribute(k_field_network_tc<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmTotal);
+    cudaFuncSetAttribute(k_field_network_tc<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmTotal);
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const uint64_t tiles = (n + kTcBlock - 1) / kTcBlock;
+    const uint64_t cap = (uint64_t)sms * 4;                  // four resident CTAs per SM
+    const int grid = (int)(tiles < cap ? tiles : cap);
+    if (net.n_features == 2)
+        k_field_network_tc<2><<<grid, kTcBlock, kSmTotal, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, error_flags);
+    else
+        k_field_network_tc<4><<<grid, kTcBlock, kSmTotal, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, error_flags);
+}
+
+}  // namespace srf

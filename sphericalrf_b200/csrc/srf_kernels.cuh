@@ -63,6 +63,12 @@ void launch_generate_rays(const DevCfg& g, const DevView& v, const uint8_t* bits
 void launch_field_network(const NetMeta& net, const __half* table, const __half* w_density, const __half* w_rgb,
                           const float4* pos_dt, const uint32_t* sample_ray, const float4* ray_dir_t,
                           const float* coords7, uint64_t n, uint2* rgbsigma, cudaStream_t stream);
+//   the same on tcgen05 tensor cores with TMEM accumulators (srf_field_tc.cu); error_flags bit 1 reports an
+//   expired wait on the MMA commit barrier.
+void launch_field_network_tc(const NetMeta& net, const __half* table, const __half* w_density, const __half* w_rgb,
+                             const float4* pos_dt, const uint32_t* sample_ray, const float4* ray_dir_t,
+                             const float* coords7, uint64_t n, uint2* rgbsigma, unsigned int* error_flags,
+                             cudaStream_t stream);
 //   density only: positions (3 floats, stride given in floats) -> 16 halves per position.
 void launch_field_density(const NetMeta& net, const __half* table, const __half* w_density, const float* positions,
                           uint32_t stride, uint64_t n, __half* out16, cudaStream_t stream);

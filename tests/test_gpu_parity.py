@@ -122,8 +122,15 @@ def test_early_termination_bit_exact(built_lib, oracle_mod):
     assert _bits_equal(got["rgba_raw"], ref["rgba_raw"])
 
 
+@pytest.fixture(params=["tcgen05", "mma_sync"])
+def mlp_engine(request, monkeypatch):
+    """Both MLP engines of the render path: tcgen05/TMEM (the default) and the mma.sync kernel."""
+    monkeypatch.setenv("SRF_B200_MLP", request.param)
+    return request.param
+
+
 @pytest.mark.parametrize("levels,features", [(16, 2), (8, 4)])
-def test_network_frame_within_tolerance(built_lib, oracle_mod, levels, features):
+def test_network_frame_within_tolerance(built_lib, oracle_mod, levels, features, mlp_engine):
     sc = small_scene(kind="net", width=24, height=16)
     cfg = sc["cfg"]
     cfg.n_levels, cfg.n_features_per_level = levels, features
@@ -143,7 +150,7 @@ def test_network_frame_within_tolerance(built_lib, oracle_mod, levels, features)
     assert ref["rgba_raw"][:, 3].max() > 0.05
 
 
-def test_network_stage_entry_points(built_lib, oracle_mod):
+def test_network_stage_entry_points(built_lib, oracle_mod, mlp_engine):
     """srf_sample_count/offsets/emit -> srf_network_inference -> srf_volume_rendering, the reference's
     class-method sequence, against the oracle stage by stage."""
     import torch
@@ -183,6 +190,31 @@ def test_network_stage_entry_points(built_lib, oracle_mod):
     assert np.abs(got[:, 3] - gotd[:, 0]).max() == 0.0     # sigma is density output 0
     frame = orc.render_frame(view, abi.default_post())
     assert np.abs(frame["rgba_raw"] - rgba.cpu().numpy()).max() <= 1e-3
+
+
+def test_mlp_engines_agree_on_raw_outputs(built_lib, oracle_mod, monkeypatch):
+    """The tcgen05 kernel and the mma.sync kernel on the same 100k random coordinates (ragged tail included)."""
+    import torch
+    sc = small_scene(kind="net")
+    rng = np.random.default_rng(9)
+    n = 100_003
+    coords = rng.random((n, 7)).astype(np.float32)
+    dev = torch.device("cuda", 0)
+    c = torch.from_numpy(coords).to(dev)
+    outs = {}
+    for engine in ("tcgen05", "mma_sync"):
+        monkeypatch.setenv("SRF_B200_MLP", engine)
+        r = make_renderer(sc)
+        o = torch.zeros((n, 4), dtype=torch.float16, device=dev)
+        assert built_lib.srf_network_inference(r.ctx, c.data_ptr(), n, o.data_ptr(), None) == 0
+        torch.cuda.synchronize()
+        outs[engine] = o.cpu().numpy().astype(np.float32)
+    ref = make_oracle(oracle_mod, sc, None).network_inference(coords[:4096]).astype(np.float32)
+    scale = max(1.0, np.abs(ref).max())
+    assert np.abs(outs["tcgen05"][:4096] - ref).max() <= 2e-2 * scale
+    assert np.abs(outs["mma_sync"][:4096] - ref).max() <= 2e-2 * scale
+    assert np.abs(outs["tcgen05"] - outs["mma_sync"]).max() <= 2e-2 * scale
+    assert np.isfinite(outs["tcgen05"]).all()
 
 
 def test_grid_refresh_bit_exact(built_lib, oracle_mod):
