@@ -122,14 +122,15 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 // blocks j0, j0+1 of an A image with 128 rows.
 template <bool RELU>
 __device__ __forceinline__ void store_units(const uint32_t (&acc)[16], unsigned char* image, int j0, int row) {
-    float v[16];
+    uint32_t h[8];
 #pragma unroll
-    for (int k = 0; k < 16; ++k) {
-        v[k] = __uint_as_float(acc[k]);
-        if (RELU) v[k] = v[k] > 0.f ? v[k] : 0.f;
+    for (int k = 0; k < 8; ++k) {
+        __half2 v = __floats2half2_rn(__uint_as_float(acc[2 * k]), __uint_as_float(acc[2 * k + 1]));
+        if (RELU) v = __hmax2(v, __float2half2_rn(0.f));     // ReLU commutes with the rounding
+        h[k] = *reinterpret_cast<const uint32_t*>(&v);
     }
-    const uint4 u0 = make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
-    const uint4 u1 = make_uint4(pack2(v[8], v[9]), pack2(v[10], v[11]), pack2(v[12], v[13]), pack2(v[14], v[15]));
+    const uint4 u0 = make_uint4(h[0], h[1], h[2], h[3]);
+    const uint4 u1 = make_uint4(h[4], h[5], h[6], h[7]);
     *reinterpret_cast<uint4*>(image + ((size_t)j0 * 128 + row) * 16) = u0;
     *reinterpret_cast<uint4*>(image + ((size_t)(j0 + 1) * 128 + row) * 16) = u1;
 }
@@ -205,11 +206,12 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
             }
         }
         {
-            __align__(16) __half enc[32];
-            hash_encode<F>(net, table, x, y, z, enc);
+            uint32_t enc[16];
+            hash_encode_packed<F>(net, table, x, y, z, enc);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-                *reinterpret_cast<uint4*>(smem + kSmA0 + ((size_t)j * 128 + tid) * 16) = *reinterpret_cast<const uint4*>(enc + 8 * j);
+                *reinterpret_cast<uint4*>(smem + kSmA0 + ((size_t)j * 128 + tid) * 16) =
+                    make_uint4(enc[4 * j], enc[4 * j + 1], enc[4 * j + 2], enc[4 * j + 3]);
             __align__(16) __half sh[16];
             sh_encode(dx, dy, dz, sh);
 #pragma unroll

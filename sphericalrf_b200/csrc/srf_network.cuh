@@ -7,59 +7,108 @@
 namespace srf {
 
 // ---- hash-grid encoding -------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t grid_index(uint32_t gx, uint32_t gy, uint32_t gz, const LevelMeta& L) {
-    uint32_t idx;
-    if (L.dense) {
-        idx = gx + gy * L.res + gz * L.res * L.res;
-        if (idx >= L.size) {                   // only cells on the upper faces wrap
-            idx -= L.size;
-            if (idx >= L.size) idx %= L.size;
-        }
-    } else {
-        idx = (gx ^ (gy * 2654435761u) ^ (gz * 805459861u)) & (L.size - 1u);   // hashed levels hold 2^k entries
-    }
-    return idx;
+// Trilinear interpolation of F fp16 features per level over the eight corners of the sample's cell
+// (Mueller et al. 2022).  Corner c takes the upper neighbour along axis d when bit d of c is set; its
+// weight is ((wx' * wy') * wz') in fp32; features accumulate in fp32 in corner order 0..7 with one
+// fused multiply-add per corner and feature, and are rounded to fp16 once.
+
+struct LevelCell {
+    uint32_t ix, iy, iz;     // lower corner of the cell
+    float wx, wy, wz;        // position inside the cell
+};
+
+__device__ __forceinline__ LevelCell level_cell(const LevelMeta& L, float x, float y, float z) {
+    LevelCell c;
+    const float px = fmaf(L.scale, x, 0.5f), py = fmaf(L.scale, y, 0.5f), pz = fmaf(L.scale, z, 0.5f);
+    const float fx = floorf(px), fy = floorf(py), fz = floorf(pz);
+    c.wx = px - fx; c.wy = py - fy; c.wz = pz - fz;
+    c.ix = (uint32_t)srf_f2i_rz(fx); c.iy = (uint32_t)srf_f2i_rz(fy); c.iz = (uint32_t)srf_f2i_rz(fz);
+    return c;
 }
 
-// Encodes one position into 32 halves written to out[0..31] (stride 1).  F = features per level.
+// The eight corner entries of a cell, as raw 32-bit words (F/2 per corner).
+// dense level:  index = x + y*res + z*res^2 (mod size); hashed level: (x ^ y*2654435761 ^ z*805459861) & (size-1).
 template <int F>
-__device__ __forceinline__ void hash_encode(const NetMeta& net, const __half* __restrict__ table, float x, float y, float z, __half* out) {
-    const int n_levels = 32 / F;
+__device__ __forceinline__ void level_gather(const LevelMeta& L, const uint32_t* __restrict__ table32, const LevelCell& c,
+                                             uint32_t (&raw)[8][F / 2]) {
+    const uint32_t* base = table32 + (size_t)L.offset * (F / 2);
+    uint32_t idx[8];
+    if (L.dense) {
+        const uint32_t r2 = L.res * L.res;
+        const uint32_t y0 = c.iy * L.res, z0 = c.iz * r2;
+        const uint32_t xy[4] = {c.ix + y0, c.ix + 1u + y0, c.ix + y0 + L.res, c.ix + 1u + y0 + L.res};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            uint32_t i = xy[k & 3] + ((k & 4) ? z0 + r2 : z0);
+            if (i >= L.size) {                   // only cells touching the upper faces wrap
+                i -= L.size;
+                if (i >= L.size) i %= L.size;
+            }
+            idx[k] = i;
+        }
+    } else {
+        const uint32_t mask = L.size - 1u;       // hashed levels hold 2^k entries
+        const uint32_t y0 = c.iy * 2654435761u, y1 = y0 + 2654435761u;
+        const uint32_t z0 = c.iz * 805459861u, z1 = z0 + 805459861u;
+        const uint32_t xy[4] = {c.ix ^ y0, (c.ix + 1u) ^ y0, c.ix ^ y1, (c.ix + 1u) ^ y1};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) idx[k] = (xy[k & 3] ^ ((k & 4) ? z1 : z0)) & mask;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const uint32_t* e = base + (size_t)idx[k] * (F / 2);
+#pragma unroll
+        for (int f = 0; f < F / 2; ++f) raw[k][f] = __ldg(e + f);
+    }
+}
+
+template <int F>
+__device__ __forceinline__ void level_interpolate(const LevelCell& c, const uint32_t (&raw)[8][F / 2], float (&acc)[F]) {
+    const float ux = 1.f - c.wx, uy = 1.f - c.wy, uz = 1.f - c.wz;
+    const float wxy[4] = {ux * uy, c.wx * uy, ux * c.wy, c.wx * c.wy};
+#pragma unroll
+    for (int f = 0; f < F; ++f) acc[f] = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float wt = wxy[k & 3] * ((k & 4) ? c.wz : uz);
+#pragma unroll
+        for (int f = 0; f < F / 2; ++f) {
+            const __half2 h = *reinterpret_cast<const __half2*>(&raw[k][f]);
+            acc[2 * f] = fmaf(wt, __low2float(h), acc[2 * f]);
+            acc[2 * f + 1] = fmaf(wt, __high2float(h), acc[2 * f + 1]);
+        }
+    }
+}
+
+// Encodes one position into 32 halves, returned as 16 packed pairs (pair i = features 2i, 2i+1).
+template <int F>
+__device__ __forceinline__ void hash_encode_packed(const NetMeta& net, const __half* __restrict__ table, float x, float y,
+                                                   float z, uint32_t (&out)[16]) {
+    const uint32_t* table32 = reinterpret_cast<const uint32_t*>(table);
+    constexpr int n_levels = 32 / F;
 #pragma unroll 2
     for (int l = 0; l < n_levels; ++l) {
         const LevelMeta& L = net.level[l];
-        const float px = fmaf(L.scale, x, 0.5f), py = fmaf(L.scale, y, 0.5f), pz = fmaf(L.scale, z, 0.5f);
-        const float fx = floorf(px), fy = floorf(py), fz = floorf(pz);
-        const float wx = px - fx, wy = py - fy, wz = pz - fz;
-        const uint32_t ix = (uint32_t)srf_f2i_rz(fx), iy = (uint32_t)srf_f2i_rz(fy), iz = (uint32_t)srf_f2i_rz(fz);
-        float acc[F];
-#pragma unroll
-        for (int f = 0; f < F; ++f) acc[f] = 0.f;
-        // issue the eight gathers first, then interpolate
+        const LevelCell c = level_cell(L, x, y, z);
         uint32_t raw[8][F / 2];
+        level_gather<F>(L, table32, c, raw);
+        float acc[F];
+        level_interpolate<F>(c, raw, acc);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            const uint32_t gx = ix + (c & 1), gy = iy + ((c >> 1) & 1), gz = iz + ((c >> 2) & 1);
-            const uint32_t idx = grid_index(gx, gy, gz, L);
-            const uint32_t* e = reinterpret_cast<const uint32_t*>(table) + (size_t)(L.offset + idx) * (F / 2);
-#pragma unroll
-            for (int f = 0; f < F / 2; ++f) raw[c][f] = __ldg(e + f);
+        for (int f = 0; f < F / 2; ++f) {
+            const __half2 h = __floats2half2_rn(acc[2 * f], acc[2 * f + 1]);
+            out[l * (F / 2) + f] = *reinterpret_cast<const uint32_t*>(&h);
         }
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            float wt = (c & 1) ? wx : 1.f - wx;
-            wt *= ((c >> 1) & 1) ? wy : 1.f - wy;
-            wt *= ((c >> 2) & 1) ? wz : 1.f - wz;
-#pragma unroll
-            for (int f = 0; f < F / 2; ++f) {
-                const __half2 h = *reinterpret_cast<const __half2*>(&raw[c][f]);
-                acc[2 * f] = fmaf(wt, __low2float(h), acc[2 * f]);
-                acc[2 * f + 1] = fmaf(wt, __high2float(h), acc[2 * f + 1]);
-            }
-        }
-#pragma unroll
-        for (int f = 0; f < F; ++f) out[l * F + f] = __float2half_rn(acc[f]);
     }
+}
+
+// Same, written as 32 consecutive halves.
+template <int F>
+__device__ __forceinline__ void hash_encode(const NetMeta& net, const __half* __restrict__ table, float x, float y, float z, __half* out) {
+    uint32_t packed[16];
+    hash_encode_packed<F>(net, table, x, y, z, packed);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) *reinterpret_cast<uint32_t*>(out + 2 * i) = packed[i];
 }
 
 // Real spherical harmonics up to degree 3 of the direction 2*d - 1 (d = warped direction in [0,1]).
