@@ -1,14 +1,14 @@
 // srf_field_tc.cu -- the network field on the 5th-generation tensor cores (tcgen05 + TMEM).
 //
 // Same data flow as srf_field.cu (NGPNetwork::inference_mixed_precision,
-// internal/network/ngp_network.h:212-279), different engine for the five dense layers: one CTA of
-// 128 threads owns a tile of 128 samples; thread r gathers and interpolates the hash-grid features
-// and the spherical harmonics of sample r straight into the shared-memory image of the MMA's A
-// operand; one thread issues tcgen05.mma (M = 128 samples, N = 64 or 16 neurons, K = 16 per
-// instruction) with the fp32 accumulator in tensor memory; after the commit barrier every thread
-// reads its own sample's row back with tcgen05.ld, applies ReLU, rounds to fp16 and writes the next
-// layer's A operand.  Weights (20 KB) sit in shared memory in the B-operand layout for the lifetime
-// of the CTA.
+// internal/network/ngp_network.h:212-279), different engine for the five dense layers.  A CTA of
+// 256 threads is two independent groups of 128 threads; a group owns a tile of 128 samples: thread
+// r gathers and interpolates the hash-grid features of sample r straight into the shared-memory
+// image of the MMA's A operand; the group's first thread issues tcgen05.mma (M = 128 samples,
+// N = 64 or 16 neurons, K = 16 per instruction) with the fp32 accumulator in tensor memory; after
+// the commit barrier every thread reads its own sample's row back with tcgen05.ld, applies ReLU,
+// rounds to fp16 and writes the next layer's A operand.  Weights (20 KB) sit in shared memory in the
+// B-operand layout for the lifetime of the CTA and are shared by both groups.
 //
 // Operand layout (no swizzle, K-major): a matrix of R rows x K halves is stored as K/8 column
 // blocks; block j holds, for every row, the 8 halves k = 8j..8j+7 as one 16-byte unit, rows
@@ -16,20 +16,26 @@
 // 8-row x 16-byte core matrices are contiguous (128 B), the stride between 8-row groups (SBO) is
 // 128 B and the stride between the two core matrices along K of one instruction (LBO) is R*16 B.
 //
-// Tensor memory: 128 columns per CTA (columns 0..63 for the 64-wide layers, 64..79 for the 16-wide
-// ones).  At most four such CTAs share an SM: the kernel asks for enough dynamic shared memory that
-// a fifth cannot be resident, so tensor-memory allocation never has to wait.
+// One 16 KB activation region per group is enough: each layer's output overwrites the region its
+// input was read from, which is safe once the layer's commit barrier has completed (the tensor core
+// has finished reading shared memory by then).  The spherical harmonics wait in registers.
 //
-// Every wait on the commit barrier is bounded; on expiry the CTA raises an error flag, leaves the
-// tile loop, frees its tensor memory and returns.
+// Tensor memory: 64 columns per group (all 64 for the 64-wide layers, the first 16 for the 16-wide
+// ones), 128 per CTA.  Four CTAs fit an SM (4 x 52 KB shared memory, 4 x 128 = 512 columns, 32
+// warps at <= 64 registers per thread); a fifth cannot be resident, so tensor-memory allocation
+// never has to wait.
+//
+// Every wait on a commit barrier is bounded; on expiry the group raises an error flag and leaves its
+// tile loop; the CTA frees its tensor memory and returns.
 #include "srf_network.cuh"
 
 namespace srf {
 
 namespace {
 
-constexpr int kTcBlock = 128;
-constexpr uint32_t kTmemCols = 128;
+constexpr int kTcBlock = 256;                   // two groups of 128 threads
+constexpr int kGroup = 128;
+constexpr uint32_t kTmemCols = 128;               // 64 per group
 constexpr uint32_t kWaitLimit = 1u << 20;
 
 // shared-memory map (bytes)
@@ -38,11 +44,10 @@ constexpr int kSmW_D2 = kSmW_D1 + 4 * 64 * 16;    // [8][16][8]
 constexpr int kSmW_C1 = kSmW_D2 + 8 * 16 * 16;    // [4][64][8]
 constexpr int kSmW_C2 = kSmW_C1 + 4 * 64 * 16;    // [8][64][8]
 constexpr int kSmW_C3 = kSmW_C2 + 8 * 64 * 16;    // [8][16][8]
-constexpr int kSmA0 = kSmW_C3 + 8 * 16 * 16;      // [4][128][8]  hash encoding
-constexpr int kSmA1 = kSmA0 + 4 * 128 * 16;       // [4][128][8]  colour input: density out (0,1), SH (2,3)
-constexpr int kSmH = kSmA1 + 4 * 128 * 16;        // [8][128][8]  hidden activations
-constexpr int kSmBar = kSmH + 8 * 128 * 16;       // mbarrier (8 B) + tensor-memory base (4 B)
-constexpr int kSmTotal = kSmBar + 16;
+constexpr int kSmAct = kSmW_C3 + 8 * 16 * 16;     // 2 groups x [8][128][8]: the activation region
+constexpr int kActBytes = 8 * 128 * 16;
+constexpr int kSmBar = kSmAct + 2 * kActBytes;    // 2 mbarriers (16 B) + tensor-memory base (4 B)
+constexpr int kSmTotal = kSmBar + 32;
 static_assert(kSmTotal > 227 * 1024 / 5, "a fifth CTA must not fit: 5 x 128 tensor-memory columns exceed 512");
 static_assert(kSmTotal <= 227 * 1024 / 4, "four CTAs per SM are intended");
 
@@ -135,8 +140,25 @@ __device__ __forceinline__ void store_units(const uint32_t (&acc)[16], unsigned 
     *reinterpret_cast<uint4*>(image + ((size_t)(j0 + 1) * 128 + row) * 16) = u1;
 }
 
+// group-local barriers with literal ids 1 and 2 (id 0 is __syncthreads); literal ids keep the CTA's
+// barrier count at 3
+__device__ __forceinline__ void group_sync(int group) {
+    if (group == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+    else asm volatile("bar.sync 2, 128;" ::: "memory");
+}
+__device__ __forceinline__ bool group_any(int group, bool v) {
+    uint32_t r;
+    if (group == 0)
+        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.or.pred q, 1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}\n"
+                     : "=r"(r) : "r"((uint32_t)v) : "memory");
+    else
+        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.or.pred q, 2, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}\n"
+                     : "=r"(r) : "r"((uint32_t)v) : "memory");
+    return r != 0;
+}
+
 template <int F>
-__global__ void __launch_bounds__(kTcBlock)
+__global__ void __launch_bounds__(kTcBlock, 4)
 k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __half* __restrict__ wd,
                    const __half* __restrict__ wc, const float4* __restrict__ pos_dt,
                    const uint32_t* __restrict__ sample_ray, const float4* __restrict__ ray_dir_t,
@@ -144,8 +166,9 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
                    unsigned int* __restrict__ error_flags) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, warp = tid >> 5;
-    uint64_t* bar_ptr = reinterpret_cast<uint64_t*>(smem + kSmBar);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kSmBar + 8);
+    const int group = tid >> 7, row = tid & 127;
+    uint64_t* bar_ptr = reinterpret_cast<uint64_t*>(smem + kSmBar) + group;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kSmBar + 16);
     const uint32_t bar = smem_u32(bar_ptr);
 
     load_weight_image(wd, 64, 32, smem + kSmW_D1);
@@ -153,7 +176,7 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
     load_weight_image(wc, 64, 32, smem + kSmW_C1);
     load_weight_image(wc + 64 * 32, 64, 64, smem + kSmW_C2);
     load_weight_image(wc + 64 * 32 + 64 * 64, 16, 64, smem + kSmW_C3);
-    if (tid == 0) {
+    if (row == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -166,33 +189,53 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_row = tmem_base + ((uint32_t)(warp * 32) << 16);     // this warp's quarter of the lanes
+    const uint32_t tmem_group = tmem_base + (uint32_t)group * 64u;                      // this group's columns
+    const uint32_t tmem_row = tmem_group + ((uint32_t)((warp & 3) * 32) << 16);          // this warp's quarter of the lanes
 
-    const uint32_t a0 = smem_u32(smem + kSmA0), a1 = smem_u32(smem + kSmA1), ah = smem_u32(smem + kSmH);
+    unsigned char* act = smem + kSmAct + group * kActBytes;
+    const uint32_t act_addr = smem_u32(act);
     const uint32_t wD1 = smem_u32(smem + kSmW_D1), wD2 = smem_u32(smem + kSmW_D2), wC1 = smem_u32(smem + kSmW_C1),
                    wC2 = smem_u32(smem + kSmW_C2), wC3 = smem_u32(smem + kSmW_C3);
     constexpr uint32_t kIdesc64 = make_idesc(64), kIdesc16 = make_idesc(16);
     constexpr uint32_t kALbo = 128 * 16, kSbo = 128;          // A images have 128 rows
 
-    // One dense layer: K/16 instructions over an A image (128 rows) and a B image (n_out rows).
-    auto issue_layer = [&](uint32_t a_img, uint32_t b_img, uint32_t n_out, int k16, uint32_t tmem_col, uint32_t idesc) {
-        if (tid == 0) {
+    // One dense layer: K/16 instructions over the A image in the activation region and a B image (n_out rows).
+    auto issue_layer = [&](uint32_t b_img, uint32_t n_out, int k16, uint32_t idesc) {
+        if (row == 0) {
             tc_fence_after();
             for (int kk = 0; kk < k16; ++kk) {
-                const uint64_t da = make_desc(a_img + (uint32_t)kk * 2u * kALbo, kALbo, kSbo);
+                const uint64_t da = make_desc(act_addr + (uint32_t)kk * 2u * kALbo, kALbo, kSbo);
                 const uint64_t db = make_desc(b_img + (uint32_t)kk * 2u * n_out * 16u, n_out * 16u, kSbo);
-                mma_f16(tmem_base + tmem_col, da, db, idesc, kk > 0 ? 1u : 0u);
+                mma_f16(tmem_group, da, db, idesc, kk > 0 ? 1u : 0u);
             }
             mma_commit(bar);
+        }
+    };
+    // Epilogue of a 64-wide layer: my row -> ReLU -> fp16 -> 8 units of the activation region.
+    auto hidden_epilogue = [&]() {
+        uint32_t acc[16];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            tmem_ld16(tmem_row + q * 16, acc);
+            tmem_ld_wait();
+            store_units<true>(acc, act, 2 * q, row);
         }
     };
 
     uint32_t phase = 0;
     bool failed = false;
-    const uint64_t n_tiles = (n + kTcBlock - 1) / kTcBlock;
-    for (uint64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        const uint64_t s = tile * kTcBlock + tid;
-        // ---- encode: one thread per sample, written as 16-byte units of the A images ----
+    // Only the group's first warp polls the commit barrier; the other three sleep in the hardware
+    // barrier of group_any() instead of spending issue slots on a spin loop.
+    auto wait_layer = [&]() -> bool {
+        bool expired = false;
+        if ((warp & 3) == 0) expired = !mbar_wait(bar, phase);
+        phase ^= 1;
+        return !group_any(group, expired);
+    };
+    const uint64_t n_tiles = (n + kGroup - 1) / kGroup;
+    for (uint64_t tile = (uint64_t)blockIdx.x * 2 + group; tile < n_tiles; tile += (uint64_t)gridDim.x * 2) {
+        const uint64_t s = tile * kGroup + row;
+        // ---- encode: one thread per sample, written as 16-byte units of the A image ----
         float x = 0.f, y = 0.f, z = 0.f, dx = 0.5f, dy = 0.5f, dz = 0.5f;
         if (s < n) {
             if (coords7) {
@@ -210,86 +253,76 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
             hash_encode_packed<F>(net, table, x, y, z, enc);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-                *reinterpret_cast<uint4*>(smem + kSmA0 + ((size_t)j * 128 + tid) * 16) =
+                *reinterpret_cast<uint4*>(act + ((size_t)j * 128 + row) * 16) =
                     make_uint4(enc[4 * j], enc[4 * j + 1], enc[4 * j + 2], enc[4 * j + 3]);
+        }
+        uint4 sh0, sh1;                                   // spherical harmonics wait in registers
+        {
             __align__(16) __half sh[16];
             sh_encode(dx, dy, dz, sh);
-#pragma unroll
-            for (int j = 0; j < 2; ++j)
-                *reinterpret_cast<uint4*>(smem + kSmA1 + ((size_t)(2 + j) * 128 + tid) * 16) = *reinterpret_cast<const uint4*>(sh + 8 * j);
+            sh0 = *reinterpret_cast<const uint4*>(sh);
+            sh1 = *reinterpret_cast<const uint4*>(sh + 8);
         }
         fence_async_smem();
-        __syncthreads();
+        group_sync(group);
 
-        uint32_t acc[16];
         // ---- density layer 1: 32 -> 64, ReLU ----
-        issue_layer(a0, wD1, 64, 2, 0, kIdesc64);
-        failed = !mbar_wait(bar, phase); phase ^= 1;
-        if (__syncthreads_or(failed)) { failed = true; break; }
+        issue_layer(wD1, 64, 2, kIdesc64);
+        if (!wait_layer()) { failed = true; break; }
         tc_fence_after();
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            tmem_ld16(tmem_row + q * 16, acc);
-            tmem_ld_wait();
-            store_units<true>(acc, smem + kSmH, 2 * q, tid);
-        }
+        hidden_epilogue();
         tc_fence_before();
         fence_async_smem();
-        __syncthreads();
+        group_sync(group);
         // ---- density layer 2: 64 -> 16 ----
-        issue_layer(ah, wD2, 16, 4, 64, kIdesc16);
-        failed = !mbar_wait(bar, phase); phase ^= 1;
-        if (__syncthreads_or(failed)) { failed = true; break; }
+        issue_layer(wD2, 16, 4, kIdesc16);
+        if (!wait_layer()) { failed = true; break; }
         tc_fence_after();
-        tmem_ld16(tmem_row + 64, acc);
-        tmem_ld_wait();
-        store_units<false>(acc, smem + kSmA1, 0, tid);
-        const uint32_t sigma_half = pack2(__uint_as_float(acc[0]), 0.f) & 0xffffu;     // density output 0
-        tc_fence_before();
-        fence_async_smem();
-        __syncthreads();
-        // ---- colour layer 1: [density out, SH] 32 -> 64, ReLU ----
-        issue_layer(a1, wC1, 64, 2, 0, kIdesc64);
-        failed = !mbar_wait(bar, phase); phase ^= 1;
-        if (__syncthreads_or(failed)) { failed = true; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            tmem_ld16(tmem_row + q * 16, acc);
+        uint32_t sigma_half;
+        {
+            uint32_t acc[16];
+            tmem_ld16(tmem_row, acc);
             tmem_ld_wait();
-            store_units<true>(acc, smem + kSmH, 2 * q, tid);
+            store_units<false>(acc, act, 0, row);         // colour input rows 0..15 = density output
+            sigma_half = pack2(__uint_as_float(acc[0]), 0.f) & 0xffffu;
         }
+        *reinterpret_cast<uint4*>(act + ((size_t)2 * 128 + row) * 16) = sh0;   // rows 16..31 = SH
+        *reinterpret_cast<uint4*>(act + ((size_t)3 * 128 + row) * 16) = sh1;
         tc_fence_before();
         fence_async_smem();
-        __syncthreads();
-        // ---- colour layer 2: 64 -> 64, ReLU (the MMA has finished reading the hidden image when its commit arrives) ----
-        issue_layer(ah, wC2, 64, 4, 0, kIdesc64);
-        failed = !mbar_wait(bar, phase); phase ^= 1;
-        if (__syncthreads_or(failed)) { failed = true; break; }
+        group_sync(group);
+        // ---- colour layer 1: 32 -> 64, ReLU ----
+        issue_layer(wC1, 64, 2, kIdesc64);
+        if (!wait_layer()) { failed = true; break; }
         tc_fence_after();
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            tmem_ld16(tmem_row + q * 16, acc);
-            tmem_ld_wait();
-            store_units<true>(acc, smem + kSmH, 2 * q, tid);
-        }
+        hidden_epilogue();
         tc_fence_before();
         fence_async_smem();
-        __syncthreads();
+        group_sync(group);
+        // ---- colour layer 2: 64 -> 64, ReLU ----
+        issue_layer(wC2, 64, 4, kIdesc64);
+        if (!wait_layer()) { failed = true; break; }
+        tc_fence_after();
+        hidden_epilogue();
+        tc_fence_before();
+        fence_async_smem();
+        group_sync(group);
         // ---- colour layer 3: 64 -> 16 (3 used) ----
-        issue_layer(ah, wC3, 16, 4, 64, kIdesc16);
-        failed = !mbar_wait(bar, phase); phase ^= 1;
-        if (__syncthreads_or(failed)) { failed = true; break; }
+        issue_layer(wC3, 16, 4, kIdesc16);
+        if (!wait_layer()) { failed = true; break; }
         tc_fence_after();
-        tmem_ld16(tmem_row + 64, acc);
-        tmem_ld_wait();
-        if (s < n)
-            rgbsigma[s] = make_uint2(pack2(__uint_as_float(acc[0]), __uint_as_float(acc[1])),
-                                     (pack2(__uint_as_float(acc[2]), 0.f) & 0xffffu) | (sigma_half << 16));
+        {
+            uint32_t acc[16];
+            tmem_ld16(tmem_row, acc);
+            tmem_ld_wait();
+            if (s < n)
+                rgbsigma[s] = make_uint2(pack2(__uint_as_float(acc[0]), __uint_as_float(acc[1])),
+                                         (pack2(__uint_as_float(acc[2]), 0.f) & 0xffffu) | (sigma_half << 16));
+        }
         tc_fence_before();
-        __syncthreads();
+        group_sync(group);
     }
-    if (failed && tid == 0 && error_flags) atomicOr(error_flags, 2u);
+    if (failed && row == 0 && error_flags) atomicOr(error_flags, 2u);
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(kTmemCols) : "memory");
 }
@@ -307,7 +340,7 @@ void launch_field_network_tc(const NetMeta& net, const __half* table, const __ha
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const uint64_t tiles = (n + kTcBlock - 1) / kTcBlock;
+    const uint64_t tiles = (n + kTcBlock - 1) / kTcBlock;    // pairs of 128-sample tiles
     const uint64_t cap = (uint64_t)sms * 4;                  // four resident CTAs per SM
     const int grid = (int)(tiles < cap ? tiles : cap);
     if (net.n_features == 2)
