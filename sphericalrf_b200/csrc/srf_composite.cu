@@ -4,12 +4,13 @@
 // bookkeeping of compact_rays_kernel (internal/testbed.cu:423-446), shade_kernel (:448-477) and
 // CudaRenderBuffer::accumulate / tonemap (internal/utils/render_buffer.cu:46-236).
 //
-// One warp per ray.  The warp streams the ray's contiguous samples 32 at a time (coalesced 8- or
-// 16-byte loads); every lane turns its sample into (alpha, rgb) -- the exponentials and logistic
-// functions, which are the expensive part -- and then the warp replays the reference's sequential
-// recurrence  T = 1 - A; w = alpha*T; C += rgb*w; A += w  sample by sample through shuffles, so
-// the accumulated colour, the opacity and the index at which  A > 1 - threshold  stops the ray are
-// bit-identical to a scalar loop over the samples.  The last lane standing finishes the pixel.
+// Frame path: the field kernels leave (activated colour, step opacity) per sample -- the exponentials
+// and logistic functions are evaluated there, in parallel over samples -- and one thread per ray runs
+// the reference's sequential recurrence  T = 1 - A; w = alpha*T; C += rgb*w; A += w  over its
+// contiguous records, so colour, opacity and the index at which  A > 1 - threshold  stops the ray are
+// bit-identical to a scalar loop.  The same thread then finishes the pixel.
+// Stage entry srf_volume_rendering (raw fp16 network outputs in Coordinate order): one warp per ray,
+// lanes evaluate the activations of 32 samples, the recurrence is replayed through shuffles.
 #include "srf_kernels.cuh"
 
 namespace srf {
@@ -100,8 +101,6 @@ template <class Load>
 __device__ __forceinline__ RayAccum composite_ray(const DevCfg& g, const DevView& v, uint64_t lo, uint64_t hi, Load load) {
     const int lane = threadIdx.x & 31;
     RayAccum acc = {0.f, 0.f, 0.f, 0.f, 0u, false};
-    const V3 origin = mk3(v.cam[3], v.cam[7], v.cam[11]);
-    const V3 cam_fwd = mk3(v.cam[2], v.cam[6], v.cam[10]);
     for (uint64_t base = lo; base < hi && !acc.terminated; base += 32) {
         const uint64_t i = base + lane;
         float alpha = 0.f, cr = 0.f, cg = 0.f, cb = 0.f;
@@ -109,20 +108,8 @@ __device__ __forceinline__ RayAccum composite_ray(const DevCfg& g, const DevView
             float raw[4], dt;
             V3 w;
             load(i, raw, &dt, &w);
-            alpha = 1.f - srf_expf(-network_to_density(raw[3], g.density_activation) * dt);
-            cr = network_to_rgb(raw[0], g.rgb_activation);
-            cg = network_to_rgb(raw[1], g.rgb_activation);
-            cb = network_to_rgb(raw[2], g.rgb_activation);
-            if (v.render_mode == SRF_MODE_DEPTH || v.render_mode == SRF_MODE_DISTANCE) {
-                const V3 p = unwarp_position(g, w);
-                const float dx = p.x - origin.x, dy = p.y - origin.y, dz = p.z - origin.z;
-                float zz;
-                if (v.render_mode == SRF_MODE_DEPTH) zz = fmaf(cam_fwd.z, dz, fmaf(cam_fwd.y, dy, cam_fwd.x * dx)) * v.depth_scale;
-                else zz = srf_norm3f(dx, dy, dz) * v.depth_scale;
-                cr = cg = cb = zz;
-            } else if (v.render_mode == SRF_MODE_AO) {
-                cr = cg = cb = alpha;
-            }
+            const float4 q = shade_sample(g, v, raw, dt, w);
+            cr = q.x; cg = q.y; cb = q.z; alpha = q.w;
         }
         const int cnt = (int)((hi - base) < 32 ? (hi - base) : 32);
         for (int k = 0; k < cnt; ++k) {
@@ -143,55 +130,59 @@ __device__ __forceinline__ RayAccum composite_ray(const DevCfg& g, const DevView
     return acc;
 }
 
-template <bool HALF>
-__global__ void __launch_bounds__(kCompBlock)
-k_composite(const DevCfg g, const DevView v, const DevPost post, const uint64_t* __restrict__ offsets,
-            uint64_t ray_begin, uint64_t ray_end, const float4* __restrict__ pos_dt,
-            const uint2* __restrict__ rgbs_half, const float4* __restrict__ rgbs_float,
-            const uint8_t* __restrict__ ray_end_reason, float4* __restrict__ out, float4* __restrict__ accum,
-            float4* __restrict__ rgba_raw, uint32_t* __restrict__ n_composited, FrameCounters* __restrict__ counters) {
-    __shared__ unsigned long long s_comp;
-    __shared__ unsigned int s_hit;
-    if (threadIdx.x == 0) { s_comp = 0ull; s_hit = 0u; }
-    __syncthreads();
-    const int lane = threadIdx.x & 31;
-    const uint64_t r = ray_begin + (uint64_t)blockIdx.x * (kCompBlock / 32) + (threadIdx.x >> 5);
+// Frame path: one thread per ray over samples the field kernels already turned into (colour, opacity).
+// The recurrence is the reference's, statement for statement: T = 1 - A; w = alpha*T; C += c*w; A += w;
+// stop once A > 1 - threshold.  Five arithmetic instructions per sample; each thread streams its
+// ray's contiguous 16-byte records.
+constexpr int kRayBlock = 128;
+
+__global__ void __launch_bounds__(kRayBlock)
+k_composite_rays(const DevCfg g, const DevView v, const DevPost post, const uint64_t* __restrict__ offsets,
+                 uint64_t ray_begin, uint64_t ray_end, const float4* __restrict__ shaded,
+                 const uint8_t* __restrict__ ray_end_reason, float4* __restrict__ out, float4* __restrict__ accum,
+                 float4* __restrict__ rgba_raw, uint32_t* __restrict__ n_composited, FrameCounters* __restrict__ counters) {
+    const uint64_t r = ray_begin + (uint64_t)blockIdx.x * kRayBlock + threadIdx.x;
+    unsigned long long comp = 0;
+    unsigned int hits = 0;
     if (r < ray_end) {
         const uint64_t base = offsets[ray_begin];
-        const uint64_t lo = offsets[r] - base, hi = offsets[r + 1] - base;
-        const RayAccum acc = composite_ray(g, v, lo, hi, [&](uint64_t i, float* raw, float* dt, V3* w) {
-            const float4 p = pos_dt[i];
-            *dt = p.w;
-            *w = mk3(p.x, p.y, p.z);
-            if (HALF) {
-                const uint2 q = rgbs_half[i];
-                const __half2 h0 = *reinterpret_cast<const __half2*>(&q.x), h1 = *reinterpret_cast<const __half2*>(&q.y);
-                raw[0] = __low2float(h0); raw[1] = __high2float(h0); raw[2] = __low2float(h1); raw[3] = __high2float(h1);
-            } else {
-                const float4 q = rgbs_float[i];
-                raw[0] = q.x; raw[1] = q.y; raw[2] = q.z; raw[3] = q.w;
-            }
-        });
-        if (lane == 0) {
-            const uint32_t end = ray_end_reason[r];
-            // A ray reaches the hit buffer when it stops being alive (terminated, left the box, or its
-            // step size fell to 0 in empty space) and its opacity exceeds 0.001 (testbed.cu:438-445).
-            // Rays that stay alive until the reference's loop bound leave their pixel untouched.
-            const bool finished = acc.terminated || end == RAY_END_EXIT || end == RAY_END_DT0;
-            const bool hit = finished && acc.a > 0.001f;
-            const uint32_t n_steps_total = acc.terminated ? acc.n : 1u + acc.n;
-            const float rgba[4] = {acc.r, acc.g, acc.b, acc.a};
-            if (rgba_raw) rgba_raw[r] = make_float4(acc.r, acc.g, acc.b, acc.a);
-            if (n_composited) n_composited[r] = acc.n;
-            if (out || accum) finish_pixel(g, v, post, hit, rgba, n_steps_total, accum ? accum + r : nullptr, out ? out + r : nullptr);
-            atomicAdd(&s_comp, (unsigned long long)acc.n);
-            if (hit) atomicAdd(&s_hit, 1u);
+        const float4* p = shaded + (offsets[r] - base);
+        const uint64_t cnt = offsets[r + 1] - offsets[r];
+        float R = 0.f, G = 0.f, B = 0.f, A = 0.f;
+        uint32_t n = 0;
+        bool terminated = false;
+        for (uint64_t j = 0; j < cnt; ++j) {
+            const float4 q = __ldg(p + j);
+            const float T = 1.f - A;
+            const float wgt = q.w * T;
+            R = fmaf(q.x, wgt, R);
+            G = fmaf(q.y, wgt, G);
+            B = fmaf(q.z, wgt, B);
+            A += wgt;
+            ++n;
+            if (A > g.transmittance_keep) { terminated = true; break; }
         }
+        const uint32_t end = ray_end_reason[r];
+        // A ray reaches the hit buffer when it stops being alive (terminated, left the box, or its step
+        // size fell to 0 in empty space) and its opacity exceeds 0.001 (testbed.cu:438-445).  Rays that
+        // stay alive until the reference's loop bound leave their pixel untouched.
+        const bool finished = terminated || end == RAY_END_EXIT || end == RAY_END_DT0;
+        const bool hit = finished && A > 0.001f;
+        const uint32_t n_steps_total = terminated ? n : 1u + n;
+        const float rgba[4] = {R, G, B, A};
+        if (rgba_raw) rgba_raw[r] = make_float4(R, G, B, A);
+        if (n_composited) n_composited[r] = n;
+        if (out || accum) finish_pixel(g, v, post, hit, rgba, n_steps_total, accum ? accum + r : nullptr, out ? out + r : nullptr);
+        comp = n;
+        hits = hit ? 1u : 0u;
     }
-    __syncthreads();
-    if (threadIdx.x == 0 && counters) {
-        if (s_comp) atomicAdd(&counters->n_composited, s_comp);
-        if (s_hit) atomicAdd(&counters->n_hit, (unsigned long long)s_hit);
+    for (int o = 16; o > 0; o >>= 1) {
+        comp += __shfl_down_sync(0xffffffffu, comp, o);
+        hits += __shfl_down_sync(0xffffffffu, hits, o);
+    }
+    if ((threadIdx.x & 31) == 0 && counters) {
+        if (comp) atomicAdd(&counters->n_composited, comp);
+        if (hits) atomicAdd(&counters->n_hit, (unsigned long long)hits);
     }
 }
 
@@ -219,18 +210,14 @@ k_composite_coords(const DevCfg g, const DevView v, const uint64_t* __restrict__
 }  // namespace
 
 void launch_composite(const DevCfg& g, const DevView& v, const DevPost& post, const uint64_t* offsets,
-                      uint64_t ray_begin, uint64_t ray_end, const float4* pos_dt, const uint2* rgbs_half,
-                      const float4* rgbs_float, const uint8_t* ray_end_reason, float4* out, float4* accum,
-                      float4* rgba_raw, uint32_t* n_composited, FrameCounters* counters, cudaStream_t stream) {
+                      uint64_t ray_begin, uint64_t ray_end, const float4* shaded, const uint8_t* ray_end_reason,
+                      float4* out, float4* accum, float4* rgba_raw, uint32_t* n_composited, FrameCounters* counters,
+                      cudaStream_t stream) {
     if (ray_end <= ray_begin) return;
     const uint64_t n = ray_end - ray_begin;
-    const unsigned int nb = (unsigned int)((n + kCompBlock / 32 - 1) / (kCompBlock / 32));
-    if (rgbs_half)
-        k_composite<true><<<nb, kCompBlock, 0, stream>>>(g, v, post, offsets, ray_begin, ray_end, pos_dt, rgbs_half,
-                                                         rgbs_float, ray_end_reason, out, accum, rgba_raw, n_composited, counters);
-    else
-        k_composite<false><<<nb, kCompBlock, 0, stream>>>(g, v, post, offsets, ray_begin, ray_end, pos_dt, rgbs_half,
-                                                          rgbs_float, ray_end_reason, out, accum, rgba_raw, n_composited, counters);
+    const unsigned int nb = (unsigned int)((n + kRayBlock - 1) / kRayBlock);
+    k_composite_rays<<<nb, kRayBlock, 0, stream>>>(g, v, post, offsets, ray_begin, ray_end, shaded, ray_end_reason, out, accum,
+                                                   rgba_raw, n_composited, counters);
 }
 
 void launch_composite_coords(const DevCfg& g, const DevView& v, const uint64_t* offsets, uint64_t n_rays,

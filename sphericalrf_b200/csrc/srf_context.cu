@@ -290,8 +290,7 @@ srf_status ensure_sample_buffers(srf_ctx* ctx, uint64_t n_samples) {
     srf_status st;
     if ((st = ensure(ctx, ctx->pos_dt, n_samples * sizeof(float4))) != SRF_OK) return st;
     if ((st = ensure(ctx, ctx->sample_ray, n_samples * sizeof(uint32_t))) != SRF_OK) return st;
-    const size_t per = ctx->cfg.field_type == SRF_FIELD_BLOBS ? sizeof(float4) : sizeof(uint2);
-    if ((st = ensure(ctx, ctx->rgbs, n_samples * per)) != SRF_OK) return st;
+    if ((st = ensure(ctx, ctx->rgbs, n_samples * sizeof(float4))) != SRF_OK) return st;   // shaded samples
     return SRF_OK;
 }
 
@@ -651,10 +650,10 @@ srf_status srf_network_inference(srf_ctx* ctx, const float* d_coords, uint64_t n
     DeviceGuard guard(ctx->device);
     if (ctx->use_tcgen05)
         launch_field_network_tc(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, nullptr, nullptr, nullptr, d_coords, n,
-                                (uint2*)d_rgbsigma, &ctx->d_counters->error_flags, (cudaStream_t)stream);
+                                (uint2*)d_rgbsigma, nullptr, nullptr, nullptr, &ctx->d_counters->error_flags, (cudaStream_t)stream);
     else
         launch_field_network(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, nullptr, nullptr, nullptr, d_coords, n,
-                             (uint2*)d_rgbsigma, (cudaStream_t)stream);
+                             (uint2*)d_rgbsigma, nullptr, nullptr, nullptr, (cudaStream_t)stream);
     SRF_CK(ctx, cudaGetLastError());
     return SRF_OK;
 }
@@ -740,18 +739,17 @@ srf_status srf_render_frame(srf_ctx* ctx, const srf_view_t* view, const srf_post
                         nullptr, nullptr, ctx->d_counters, s);
         if (tm) cudaEventRecord(ctx->ev[3], s);
         if (blobs)
-            launch_field_blobs(ctx->g, ctx->blobs, ctx->n_blobs, ctx->cmap, (const float4*)ctx->pos_dt.p, n_s, (float4*)ctx->rgbs.p, s);
+            launch_field_blobs(ctx->g, v, ctx->blobs, ctx->n_blobs, ctx->cmap, (const float4*)ctx->pos_dt.p, n_s, (float4*)ctx->rgbs.p, s);
         else if (ctx->use_tcgen05)
             launch_field_network_tc(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, (const float4*)ctx->pos_dt.p,
-                                    (const uint32_t*)ctx->sample_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, n_s,
-                                    (uint2*)ctx->rgbs.p, &ctx->d_counters->error_flags, s);
+                                    (const uint32_t*)ctx->sample_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, n_s, nullptr,
+                                    (float4*)ctx->rgbs.p, &ctx->g, &v, &ctx->d_counters->error_flags, s);
         else
             launch_field_network(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, (const float4*)ctx->pos_dt.p,
-                                 (const uint32_t*)ctx->sample_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, n_s,
-                                 (uint2*)ctx->rgbs.p, s);
+                                 (const uint32_t*)ctx->sample_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, n_s, nullptr,
+                                 (float4*)ctx->rgbs.p, &ctx->g, &v, s);
         if (tm) cudaEventRecord(ctx->ev[4], s);
-        launch_composite(ctx->g, v, dp, (const uint64_t*)ctx->offsets.p, r0, r1, (const float4*)ctx->pos_dt.p,
-                         blobs ? nullptr : (const uint2*)ctx->rgbs.p, blobs ? (const float4*)ctx->rgbs.p : nullptr,
+        launch_composite(ctx->g, v, dp, (const uint64_t*)ctx->offsets.p, r0, r1, (const float4*)ctx->rgbs.p,
                          (const uint8_t*)ctx->ray_end.p, (float4*)d_out, (float4*)d_accum, (float4*)d_rgba_raw, nullptr,
                          ctx->d_counters, s);
         if (tm) {

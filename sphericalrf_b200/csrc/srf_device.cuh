@@ -434,4 +434,25 @@ __device__ __forceinline__ float linear_to_srgb(float l) {
     return l < 0.0031308f ? 12.92f * l : 1.055f * srf_powf(l, 0.41666f) - 0.055f;
 }
 
+// What the compositor needs from one sample: the activated colour and the opacity of the step
+// (volume_rendering_kernel, internal/render/ray_marcher.cu:236-265).  raw = (r, g, b, sigma) as the
+// field returned them; w = warped position (for the depth modes).
+__device__ __forceinline__ float4 shade_sample(const DevCfg& g, const DevView& v, const float (&raw)[4], float dt, const V3& w) {
+    const float alpha = 1.f - srf_expf(-network_to_density(raw[3], g.density_activation) * dt);
+    float cr = network_to_rgb(raw[0], g.rgb_activation);
+    float cg = network_to_rgb(raw[1], g.rgb_activation);
+    float cb = network_to_rgb(raw[2], g.rgb_activation);
+    if (v.render_mode == SRF_MODE_DEPTH || v.render_mode == SRF_MODE_DISTANCE) {
+        const V3 p = unwarp_position(g, w);
+        const float dx = p.x - v.cam[3], dy = p.y - v.cam[7], dz = p.z - v.cam[11];
+        float zz;
+        if (v.render_mode == SRF_MODE_DEPTH) zz = fmaf(v.cam[10], dz, fmaf(v.cam[6], dy, v.cam[2] * dx)) * v.depth_scale;
+        else zz = srf_norm3f(dx, dy, dz) * v.depth_scale;
+        cr = cg = cb = zz;
+    } else if (v.render_mode == SRF_MODE_AO) {
+        cr = cg = cb = alpha;
+    }
+    return make_float4(cr, cg, cb, alpha);
+}
+
 }  // namespace srf

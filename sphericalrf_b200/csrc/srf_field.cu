@@ -13,6 +13,7 @@
 // the published algorithm (Mueller et al. 2022): fp16 parameters and activations, fp32
 // accumulation, one rounding to fp16 per layer; trilinear interpolation with fp32 weights in
 // corner order 0..7 (bit d of the corner index selects the upper neighbour along axis d).
+#include <cstring>
 #include "srf_network.cuh"
 
 namespace srf {
@@ -24,7 +25,7 @@ __global__ void __launch_bounds__(kFieldBlock)
 k_field_network(const NetMeta net, const __half* __restrict__ table, const __half* __restrict__ wd, const __half* __restrict__ wc,
                 const float4* __restrict__ pos_dt, const uint32_t* __restrict__ sample_ray,
                 const float4* __restrict__ ray_dir_t, const float* __restrict__ coords7, uint64_t n,
-                uint2* __restrict__ rgbsigma) {
+                uint2* __restrict__ rgbsigma, float4* __restrict__ shaded, const DevCfg cfg, const DevView view) {
     __shared__ __align__(16) __half sW[kWeightHalves];
     __shared__ __align__(16) __half sRows[kFieldBlock * kRowLd];
     load_weights(wd, wc, sW, true);
@@ -116,10 +117,22 @@ k_field_network(const NetMeta net, const __half* __restrict__ table, const __hal
                 const uint64_t base = tile * kFieldBlock + warp * 32 + mt * 16;
                 const uint64_t s0 = base + g, s1 = base + g + 8;
                 const uint32_t sg0 = sigma_bits[mt] & 0xffffu, sg1 = sigma_bits[mt] >> 16;
-                if (s0 < n) rgbsigma[s0] = make_uint2(pack_half2(c3[mt][0][0], c3[mt][0][1]),
-                                                      (pack_half2(b_lo, 0.f) & 0xffffu) | (sg0 << 16));
-                if (s1 < n) rgbsigma[s1] = make_uint2(pack_half2(c3[mt][0][2], c3[mt][0][3]),
-                                                      (pack_half2(b_hi, 0.f) & 0xffffu) | (sg1 << 16));
+                const uint2 o0 = make_uint2(pack_half2(c3[mt][0][0], c3[mt][0][1]), (pack_half2(b_lo, 0.f) & 0xffffu) | (sg0 << 16));
+                const uint2 o1 = make_uint2(pack_half2(c3[mt][0][2], c3[mt][0][3]), (pack_half2(b_hi, 0.f) & 0xffffu) | (sg1 << 16));
+                const uint64_t ss[2] = {s0, s1};
+                const uint2 oo[2] = {o0, o1};
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    if (ss[e] >= n) continue;
+                    if (shaded) {
+                        const __half2 h0 = *reinterpret_cast<const __half2*>(&oo[e].x), h1 = *reinterpret_cast<const __half2*>(&oo[e].y);
+                        const float raw[4] = {__low2float(h0), __high2float(h0), __low2float(h1), __high2float(h1)};
+                        const float4 p = pos_dt[ss[e]];
+                        shaded[ss[e]] = shade_sample(cfg, view, raw, p.w, mk3(p.x, p.y, p.z));
+                    } else {
+                        rgbsigma[ss[e]] = oo[e];
+                    }
+                }
             }
         }
         __syncwarp();
@@ -179,7 +192,7 @@ k_field_density(const NetMeta net, const __half* __restrict__ table, const __hal
 
 // Analytic stand-in scene, fp32, one thread per sample.
 __global__ void __launch_bounds__(256)
-k_field_blobs(const DevCfg g, const float* __restrict__ blobs, uint32_t n_blobs, const float* __restrict__ cmap,
+k_field_blobs(const DevCfg g, const DevView v, const float* __restrict__ blobs, uint32_t n_blobs, const float* __restrict__ cmap,
               const float4* __restrict__ pos_dt, uint64_t n, float4* __restrict__ out) {
     extern __shared__ float s_blobs[];
     for (uint32_t i = threadIdx.x; i < n_blobs * 5; i += blockDim.x) s_blobs[i] = blobs[i];
@@ -197,12 +210,9 @@ k_field_blobs(const DevCfg g, const float* __restrict__ blobs, uint32_t n_blobs,
         sigma = fmaf(q[4], srf_expf(d2 * inv), sigma);
     }
     const float px = x.x - 0.5f, py = x.y - 0.5f, pz = x.z - 0.5f;
-    float4 r;
-    r.x = fmaf(cmap[2], pz, fmaf(cmap[1], py, cmap[0] * px));
-    r.y = fmaf(cmap[5], pz, fmaf(cmap[4], py, cmap[3] * px));
-    r.z = fmaf(cmap[8], pz, fmaf(cmap[7], py, cmap[6] * px));
-    r.w = sigma;
-    out[i] = r;
+    const float raw[4] = {fmaf(cmap[2], pz, fmaf(cmap[1], py, cmap[0] * px)), fmaf(cmap[5], pz, fmaf(cmap[4], py, cmap[3] * px)),
+                          fmaf(cmap[8], pz, fmaf(cmap[7], py, cmap[6] * px)), sigma};
+    out[i] = shade_sample(g, v, raw, p.w, mk3(p.x, p.y, p.z));
 }
 
 int field_grid(uint64_t n) {
@@ -218,13 +228,18 @@ int field_grid(uint64_t n) {
 
 void launch_field_network(const NetMeta& net, const __half* table, const __half* w_density, const __half* w_rgb,
                           const float4* pos_dt, const uint32_t* sample_ray, const float4* ray_dir_t,
-                          const float* coords7, uint64_t n, uint2* rgbsigma, cudaStream_t stream) {
+                          const float* coords7, uint64_t n, uint2* rgbsigma, float4* shaded, const DevCfg* g,
+                          const DevView* v, cudaStream_t stream) {
     if (n == 0) return;
     const int grid = field_grid(n);
+    DevCfg g0; DevView v0;
+    memset(&g0, 0, sizeof(g0)); memset(&v0, 0, sizeof(v0));
+    if (g) g0 = *g;
+    if (v) v0 = *v;
     if (net.n_features == 2)
-        k_field_network<2><<<grid, kFieldBlock, 0, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma);
+        k_field_network<2><<<grid, kFieldBlock, 0, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0);
     else
-        k_field_network<4><<<grid, kFieldBlock, 0, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma);
+        k_field_network<4><<<grid, kFieldBlock, 0, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0);
 }
 
 void launch_field_density(const NetMeta& net, const __half* table, const __half* w_density, const float* positions,
@@ -237,11 +252,11 @@ void launch_field_density(const NetMeta& net, const __half* table, const __half*
         k_field_density<4><<<grid, kFieldBlock, 0, stream>>>(net, table, w_density, positions, stride, n, out16);
 }
 
-void launch_field_blobs(const DevCfg& g, const float* blobs, uint32_t n_blobs, const float* color_map,
-                        const float4* pos_dt, uint64_t n, float4* rgbsigma, cudaStream_t stream) {
+void launch_field_blobs(const DevCfg& g, const DevView& v, const float* blobs, uint32_t n_blobs, const float* color_map,
+                        const float4* pos_dt, uint64_t n, float4* shaded, cudaStream_t stream) {
     if (n == 0) return;
     k_field_blobs<<<(unsigned int)((n + 255) / 256), 256, n_blobs * 5 * sizeof(float), stream>>>(
-        g, blobs, n_blobs, color_map, pos_dt, n, rgbsigma);
+        g, v, blobs, n_blobs, color_map, pos_dt, n, shaded);
 }
 
 }  // namespace srf

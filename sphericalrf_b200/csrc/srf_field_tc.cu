@@ -27,6 +27,7 @@
 //
 // Every wait on a commit barrier is bounded; on expiry the group raises an error flag and leaves its
 // tile loop; the CTA frees its tensor memory and returns.
+#include <cstring>
 #include "srf_network.cuh"
 
 namespace srf {
@@ -163,6 +164,7 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
                    const __half* __restrict__ wc, const float4* __restrict__ pos_dt,
                    const uint32_t* __restrict__ sample_ray, const float4* __restrict__ ray_dir_t,
                    const float* __restrict__ coords7, uint64_t n, uint2* __restrict__ rgbsigma,
+                   float4* __restrict__ shaded, const DevCfg g, const DevView v,
                    unsigned int* __restrict__ error_flags) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, warp = tid >> 5;
@@ -315,9 +317,19 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
             uint32_t acc[16];
             tmem_ld16(tmem_row, acc);
             tmem_ld_wait();
-            if (s < n)
-                rgbsigma[s] = make_uint2(pack2(__uint_as_float(acc[0]), __uint_as_float(acc[1])),
-                                         (pack2(__uint_as_float(acc[2]), 0.f) & 0xffffu) | (sigma_half << 16));
+            if (s < n) {
+                const uint32_t rg = pack2(__uint_as_float(acc[0]), __uint_as_float(acc[1]));
+                const uint32_t bs = (pack2(__uint_as_float(acc[2]), 0.f) & 0xffffu) | (sigma_half << 16);
+                if (shaded) {
+                    // frame path: activations evaluated here, on the fp16-rounded network outputs
+                    const __half2 h0 = *reinterpret_cast<const __half2*>(&rg), h1 = *reinterpret_cast<const __half2*>(&bs);
+                    const float raw[4] = {__low2float(h0), __high2float(h0), __low2float(h1), __high2float(h1)};
+                    const float4 p = pos_dt[s];                      // re-read (L2) instead of holding four registers
+                    shaded[s] = shade_sample(g, v, raw, p.w, mk3(p.x, p.y, p.z));
+                } else {
+                    rgbsigma[s] = make_uint2(rg, bs);
+                }
+            }
         }
         tc_fence_before();
         group_sync(group);
@@ -331,8 +343,8 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
 
 void launch_field_network_tc(const NetMeta& net, const __half* table, const __half* w_density, const __half* w_rgb,
                              const float4* pos_dt, const uint32_t* sample_ray, const float4* ray_dir_t,
-                             const float* coords7, uint64_t n, uint2* rgbsigma, unsigned int* error_flags,
-                             cudaStream_t stream) {
+                             const float* coords7, uint64_t n, uint2* rgbsigma, float4* shaded, const DevCfg* g,
+                             const DevView* v, unsigned int* error_flags, cudaStream_t stream) {
     if (n == 0) return;
     // per device and cheap: set on every launch rather than cached per process
     cudaFuncSetAttribute(k_field_network_tc<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmTotal);
@@ -343,10 +355,14 @@ void launch_field_network_tc(const NetMeta& net, const __half* table, const __ha
     const uint64_t tiles = (n + kTcBlock - 1) / kTcBlock;    // pairs of 128-sample tiles
     const uint64_t cap = (uint64_t)sms * 4;                  // four resident CTAs per SM
     const int grid = (int)(tiles < cap ? tiles : cap);
+    DevCfg g0; DevView v0;
+    memset(&g0, 0, sizeof(g0)); memset(&v0, 0, sizeof(v0));
+    if (g) g0 = *g;
+    if (v) v0 = *v;
     if (net.n_features == 2)
-        k_field_network_tc<2><<<grid, kTcBlock, kSmTotal, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, error_flags);
+        k_field_network_tc<2><<<grid, kTcBlock, kSmTotal, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0, error_flags);
     else
-        k_field_network_tc<4><<<grid, kTcBlock, kSmTotal, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, error_flags);
+        k_field_network_tc<4><<<grid, kTcBlock, kSmTotal, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0, error_flags);
 }
 
 }  // namespace srf

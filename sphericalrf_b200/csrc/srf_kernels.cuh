@@ -62,19 +62,23 @@ void launch_generate_rays(const DevCfg& g, const DevView& v, const uint8_t* bits
 //   dirs come either from ray_dir_t[sample_ray[i]] (compact layout) or from coords7 (Coordinate records).
 void launch_field_network(const NetMeta& net, const __half* table, const __half* w_density, const __half* w_rgb,
                           const float4* pos_dt, const uint32_t* sample_ray, const float4* ray_dir_t,
-                          const float* coords7, uint64_t n, uint2* rgbsigma, cudaStream_t stream);
+                          const float* coords7, uint64_t n, uint2* rgbsigma, float4* shaded, const DevCfg* g,
+                          const DevView* v, cudaStream_t stream);
 //   the same on tcgen05 tensor cores with TMEM accumulators (srf_field_tc.cu); error_flags bit 1 reports an
 //   expired wait on the MMA commit barrier.
+//   Output: either rgbsigma (4 raw halves per sample, the reference's network output) or, on the frame path,
+//   shaded (activated colour and step opacity, 4 floats per sample; needs g, v and pos_dt for dt).
 void launch_field_network_tc(const NetMeta& net, const __half* table, const __half* w_density, const __half* w_rgb,
                              const float4* pos_dt, const uint32_t* sample_ray, const float4* ray_dir_t,
-                             const float* coords7, uint64_t n, uint2* rgbsigma, unsigned int* error_flags,
-                             cudaStream_t stream);
+                             const float* coords7, uint64_t n, uint2* rgbsigma, float4* shaded, const DevCfg* g,
+                             const DevView* v, unsigned int* error_flags, cudaStream_t stream);
 //   density only: positions (3 floats, stride given in floats) -> 16 halves per position.
 void launch_field_density(const NetMeta& net, const __half* table, const __half* w_density, const float* positions,
                           uint32_t stride, uint64_t n, __half* out16, cudaStream_t stream);
 //   analytic blob field in fp32 -> (r,g,b logits, sigma), 4 floats per sample.
-void launch_field_blobs(const DevCfg& g, const float* blobs, uint32_t n_blobs, const float* color_map,
-                        const float4* pos_dt, uint64_t n, float4* rgbsigma, cudaStream_t stream);
+//   writes shaded samples (activated colour, step opacity).
+void launch_field_blobs(const DevCfg& g, const DevView& v, const float* blobs, uint32_t n_blobs, const float* color_map,
+                        const float4* pos_dt, uint64_t n, float4* shaded, cudaStream_t stream);
 
 struct DevPost {
     float exposure_scale;      // 2^exposure
@@ -83,11 +87,12 @@ struct DevPost {
 };
 
 // Compositing of rays [ray_begin, ray_end) over the compact layout, followed by shade, accumulate and
-// tonemap of the ray's pixel.  Exactly one of rgbs_half / rgbs_float is non-null.  Any output may be null.
+// tonemap of the ray's pixel.  shaded: per sample (activated r, g, b, step opacity) as the frame-path field
+// kernels write it.  Any output may be null.
 void launch_composite(const DevCfg& g, const DevView& v, const DevPost& post, const uint64_t* offsets,
-                      uint64_t ray_begin, uint64_t ray_end, const float4* pos_dt, const uint2* rgbs_half,
-                      const float4* rgbs_float, const uint8_t* ray_end_reason, float4* out, float4* accum,
-                      float4* rgba_raw, uint32_t* n_composited, FrameCounters* counters, cudaStream_t stream);
+                      uint64_t ray_begin, uint64_t ray_end, const float4* shaded, const uint8_t* ray_end_reason,
+                      float4* out, float4* accum, float4* rgba_raw, uint32_t* n_composited, FrameCounters* counters,
+                      cudaStream_t stream);
 
 // Compositing over Coordinate records (stage entry srf_volume_rendering): no post stage.
 void launch_composite_coords(const DevCfg& g, const DevView& v, const uint64_t* offsets, uint64_t n_rays,
