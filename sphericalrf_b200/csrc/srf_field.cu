@@ -28,6 +28,8 @@ k_field_network(const NetMeta net, const __half* __restrict__ table, const __hal
                 uint2* __restrict__ rgbsigma, float4* __restrict__ shaded, const DevCfg cfg, const DevView view) {
     __shared__ __align__(16) __half sW[kWeightHalves];
     __shared__ __align__(16) __half sRows[kFieldBlock * kRowLd];
+    __shared__ EncMeta enc_meta;
+    prepare_enc_meta(net, &enc_meta);
     load_weights(wd, wc, sW, true);
     __syncthreads();
 
@@ -51,7 +53,7 @@ k_field_network(const NetMeta net, const __half* __restrict__ table, const __hal
                 dx = (d.x + 1.f) * 0.5f; dy = (d.y + 1.f) * 0.5f; dz = (d.z + 1.f) * 0.5f;   // warp_direction
             }
         }
-        hash_encode<F>(net, table, x, y, z, my_row);
+        hash_encode<F>(&enc_meta, table, x, y, z, my_row);
         sh_encode(dx, dy, dz, my_row + 32);
         __syncwarp();
 
@@ -146,6 +148,8 @@ k_field_density(const NetMeta net, const __half* __restrict__ table, const __hal
                 uint32_t stride, uint64_t n, __half* __restrict__ out16) {
     __shared__ __align__(16) __half sW[kOffC1];
     __shared__ __align__(16) __half sRows[kFieldBlock * kRowLd];
+    __shared__ EncMeta enc_meta;
+    prepare_enc_meta(net, &enc_meta);
     load_weights(wd, nullptr, sW, false);
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
@@ -156,7 +160,7 @@ k_field_density(const NetMeta net, const __half* __restrict__ table, const __hal
         const uint64_t s = tile * kFieldBlock + threadIdx.x;
         float x = 0.f, y = 0.f, z = 0.f;
         if (s < n) { const float* p = positions + s * stride; x = p[0]; y = p[1]; z = p[2]; }
-        hash_encode<F>(net, table, x, y, z, my_row);
+        hash_encode<F>(&enc_meta, table, x, y, z, my_row);
         __syncwarp();
         uint32_t a_in[2][2][4];
         {

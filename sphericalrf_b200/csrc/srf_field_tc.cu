@@ -48,7 +48,8 @@ constexpr int kSmW_C3 = kSmW_C2 + 8 * 64 * 16;    // [8][16][8]
 constexpr int kSmAct = kSmW_C3 + 8 * 16 * 16;     // 2 groups x [8][128][8]: the activation region
 constexpr int kActBytes = 8 * 128 * 16;
 constexpr int kSmBar = kSmAct + 2 * kActBytes;    // 2 mbarriers (16 B) + tensor-memory base (4 B)
-constexpr int kSmTotal = kSmBar + 32;
+constexpr int kSmEnc = kSmBar + 32;               // per-level constants of the encoding
+constexpr int kSmTotal = kSmEnc + (int)sizeof(EncMeta);
 static_assert(kSmTotal > 227 * 1024 / 5, "a fifth CTA must not fit: 5 x 128 tensor-memory columns exceed 512");
 static_assert(kSmTotal <= 227 * 1024 / 4, "four CTAs per SM are intended");
 
@@ -173,6 +174,8 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kSmBar + 16);
     const uint32_t bar = smem_u32(bar_ptr);
 
+    EncMeta* enc_meta = reinterpret_cast<EncMeta*>(smem + kSmEnc);
+    prepare_enc_meta(net, enc_meta);
     load_weight_image(wd, 64, 32, smem + kSmW_D1);
     load_weight_image(wd + 64 * 32, 16, 64, smem + kSmW_D2);
     load_weight_image(wc, 64, 32, smem + kSmW_C1);
@@ -252,7 +255,7 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
         }
         {
             uint32_t enc[16];
-            hash_encode_packed<F>(net, table, x, y, z, enc);
+            hash_encode_packed<F>(enc_meta, table, x, y, z, enc);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
                 *reinterpret_cast<uint4*>(act + ((size_t)j * 128 + row) * 16) =

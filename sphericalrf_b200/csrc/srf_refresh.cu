@@ -54,6 +54,8 @@ k_refresh_sample(const DevCfg g, const NetMeta net, const __half* __restrict__ t
                  uint32_t step, Pcg rng0, float thresh, uint32_t aabb_scale) {
     __shared__ __align__(16) float sW1[64 * 32];
     __shared__ float sW2[64];
+    __shared__ EncMeta enc_meta;
+    prepare_enc_meta(net, &enc_meta);
     for (int i = threadIdx.x; i < 64 * 32; i += blockDim.x) sW1[i] = __half2float(wd[i]);
     for (int i = threadIdx.x; i < 64; i += blockDim.x) sW2[i] = __half2float(wd[64 * 32 + i]);   // row 0 of layer 2
     __syncthreads();
@@ -96,7 +98,7 @@ k_refresh_sample(const DevCfg g, const NetMeta net, const __half* __restrict__ t
     }
 
     __half enc[32];
-    hash_encode<F>(net, table, pos.x, pos.y, pos.z, enc);
+    hash_encode<F>(&enc_meta, table, pos.x, pos.y, pos.z, enc);
     float x[32];
 #pragma unroll
     for (int k = 0; k < 32; ++k) x[k] = __half2float(enc[k]);
