@@ -245,7 +245,7 @@ def run_ours(args):
             dist.destroy_process_group()
         return
     peak, peak_kind = _peaks()
-    launches_per_frame = 4 + 3 * n_batches           # count, 3 scan kernels, then emit/field/composite per batch
+    launches_per_frame = 3 * n_batches               # march, field, composite per batch of rays
     achieved = ALG_BYTES_PER_SAMPLE * n_samples / max(n_batches, 1) / (t_field / max(n_batches, 1) * 1e-3) / 1e9 if t_field > 0 else 0.0
     line = {
         "metric": "render throughput", "value": value, "unit": "Mrays/s", "n_gpus": world, "steps": args.steps,

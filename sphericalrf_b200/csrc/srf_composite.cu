@@ -136,8 +136,11 @@ __device__ __forceinline__ RayAccum composite_ray(const DevCfg& g, const DevView
 // ray's contiguous 16-byte records.
 constexpr int kRayBlock = 128;
 
+template <bool PAGED>
 __global__ void __launch_bounds__(kRayBlock)
 k_composite_rays(const DevCfg g, const DevView v, const DevPost post, const uint64_t* __restrict__ offsets,
+                 const uint32_t* __restrict__ ray_head, const uint32_t* __restrict__ ray_count,
+                 const uint32_t* __restrict__ chunk_next,
                  uint64_t ray_begin, uint64_t ray_end, const float4* __restrict__ shaded,
                  const uint8_t* __restrict__ ray_end_reason, float4* __restrict__ out, float4* __restrict__ accum,
                  float4* __restrict__ rgba_raw, uint32_t* __restrict__ n_composited, FrameCounters* __restrict__ counters) {
@@ -145,14 +148,10 @@ k_composite_rays(const DevCfg g, const DevView v, const DevPost post, const uint
     unsigned long long comp = 0;
     unsigned int hits = 0;
     if (r < ray_end) {
-        const uint64_t base = offsets[ray_begin];
-        const float4* p = shaded + (offsets[r] - base);
-        const uint64_t cnt = offsets[r + 1] - offsets[r];
         float R = 0.f, G = 0.f, B = 0.f, A = 0.f;
         uint32_t n = 0;
         bool terminated = false;
-        for (uint64_t j = 0; j < cnt; ++j) {
-            const float4 q = __ldg(p + j);
+        auto take = [&](const float4 q) {
             const float T = 1.f - A;
             const float wgt = q.w * T;
             R = fmaf(q.x, wgt, R);
@@ -160,7 +159,24 @@ k_composite_rays(const DevCfg g, const DevView v, const DevPost post, const uint
             B = fmaf(q.z, wgt, B);
             A += wgt;
             ++n;
-            if (A > g.transmittance_keep) { terminated = true; break; }
+            return A > g.transmittance_keep;
+        };
+        if (PAGED) {
+            uint32_t left = ray_count[r], c = ray_head[r];
+            while (left && !terminated) {
+                const float4* p = shaded + (uint64_t)c * kChunkSamples;
+                const uint32_t m = left < kChunkSamples ? left : kChunkSamples;
+                for (uint32_t j = 0; j < m; ++j)
+                    if (take(__ldg(p + j))) { terminated = true; break; }
+                left -= m;
+                c = chunk_next[c];
+            }
+        } else {
+            const uint64_t base = offsets[ray_begin];
+            const float4* p = shaded + (offsets[r] - base);
+            const uint64_t cnt = offsets[r + 1] - offsets[r];
+            for (uint64_t j = 0; j < cnt; ++j)
+                if (take(__ldg(p + j))) { terminated = true; break; }
         }
         const uint32_t end = ray_end_reason[r];
         // A ray reaches the hit buffer when it stops being alive (terminated, left the box, or its step
@@ -216,8 +232,19 @@ void launch_composite(const DevCfg& g, const DevView& v, const DevPost& post, co
     if (ray_end <= ray_begin) return;
     const uint64_t n = ray_end - ray_begin;
     const unsigned int nb = (unsigned int)((n + kRayBlock - 1) / kRayBlock);
-    k_composite_rays<<<nb, kRayBlock, 0, stream>>>(g, v, post, offsets, ray_begin, ray_end, shaded, ray_end_reason, out, accum,
-                                                   rgba_raw, n_composited, counters);
+    k_composite_rays<false><<<nb, kRayBlock, 0, stream>>>(g, v, post, offsets, nullptr, nullptr, nullptr, ray_begin, ray_end, shaded,
+                                                          ray_end_reason, out, accum, rgba_raw, n_composited, counters);
+}
+
+void launch_composite_paged(const DevCfg& g, const DevView& v, const DevPost& post, uint64_t ray_begin, uint64_t ray_end,
+                            const uint32_t* ray_head, const uint32_t* ray_count, const uint32_t* chunk_next,
+                            const float4* pool_shaded, const uint8_t* ray_end_reason, float4* out, float4* accum,
+                            float4* rgba_raw, uint32_t* n_composited, FrameCounters* counters, cudaStream_t stream) {
+    if (ray_end <= ray_begin) return;
+    const uint64_t n = ray_end - ray_begin;
+    const unsigned int nb = (unsigned int)((n + kRayBlock - 1) / kRayBlock);
+    k_composite_rays<true><<<nb, kRayBlock, 0, stream>>>(g, v, post, nullptr, ray_head, ray_count, chunk_next, ray_begin, ray_end,
+                                                         pool_shaded, ray_end_reason, out, accum, rgba_raw, n_composited, counters);
 }
 
 void launch_composite_coords(const DevCfg& g, const DevView& v, const uint64_t* offsets, uint64_t n_rays,

@@ -3,10 +3,12 @@
 // (internal/testbed.cu:479-606).
 //
 // Frame loop.  The reference alternates compaction, <= 8 samples per ray, the network and
-// compositing under host control, reading a counter back every iteration.  Here a frame is:
-// count pass -> exclusive scan -> ONE read-back (the sample total and a coarse offset table) ->
-// per batch of rays { emit -> field -> composite+output }.  Batches exist only to bound the
-// sample scratch; a frame whose samples fit the scratch is a single batch.
+// compositing under host control, reading a counter back every iteration.  Here a frame is, per
+// batch of rays: single-pass march into a paged sample pool -> field over the pool -> per-ray
+// compositing + output stage.  Nothing is read back: the field kernel takes the number of chunks the
+// sampler used from device memory.  Batches exist only to bound the pool (every ray of a batch is
+// given room for the most samples its step-size law allows).  The count -> scan -> emit kernels serve
+// the stage entry points and the parity tap, which need the compact ray-major layout.
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
@@ -25,7 +27,7 @@ namespace {
 thread_local std::string g_create_error;
 
 constexpr uint64_t kCoarse = 4096;                    // rays per entry of the coarse offset table
-constexpr uint64_t kAutoSampleCapacity = 256ull << 20;  // default upper bound of the sample scratch
+constexpr uint64_t kAutoSampleCapacity = 512ull << 20;  // default upper bound of the sample pool (32 B per slot)
 
 struct DevBuf {
     void* p = nullptr;
@@ -61,6 +63,8 @@ struct srf_ctx {
     // per-frame scratch
     DevBuf ray_dir_t, ray_end, counts, offsets, scan_scratch;
     DevBuf pos_dt, sample_ray, rgbs;
+    DevBuf pool_pos, pool_shaded, chunk_ray, chunk_next, ray_head;   // paged frame path
+    uint32_t* d_chunk_cursor = nullptr;
     DevBuf img_out, img_accum;
     FrameCounters* d_counters = nullptr;
     FrameCounters* h_counters = nullptr;     // pinned
@@ -210,6 +214,31 @@ void resolve(const srf_config_t& c, DevCfg* g, float* min_thick) {
     g->train_in_linear_color = c.train_in_linear_color;
     g->field_type = c.field_type;
     *min_thick = c.min_optical_thickness;
+}
+
+// Upper bound of the samples one ray can emit, from the step-size law alone (every sample is a march
+// step): used to size the sample pool per ray so that the single-pass sampler can never run out of chunks.
+uint32_t ray_sample_bound(const srf_config_t& c, const DevCfg& g) {
+    const double cap = g.sample_cap;
+    double b = cap;
+    const double ds = 1.0 / (double)c.maximum_marching_steps;
+    switch (c.sampling_type) {
+    case SRF_SAMPLING_ORIGINAL:       // dt >= min_step; the path inside the cube is at most sqrt(3) * edge
+        if (g.min_step > 0.f) b = 1.7320508 * (double)g.box_diag / (double)g.min_step + 16.0;
+        break;
+    case SRF_SAMPLING_DISPARITY: {    // 1/t falls from <= 1/0.05 by ds*(1/near - 1/far) per step, then one jump to far
+        const double delta = ds * ((double)g.g_near - (double)g.g_far);
+        if (delta > 0.0) b = 20.0 / delta * 1.001 + 16.0;
+    } break;
+    case SRF_SAMPLING_LOG: {          // log t grows from >= log 0.05 by ds*(log far - log near) per step up to log far
+        const double delta = ds * ((double)g.g_far - (double)g.g_near);
+        if (delta > 0.0 && c.far_distance > 0.05f) b = (std::log((double)c.far_distance) - std::log(0.05)) / delta * 1.001 + 16.0;
+    } break;
+    default: break;
+    }
+    if (!(b < cap)) b = cap;
+    if (b < 1.0) b = 1.0;
+    return (uint32_t)std::ceil(b);
 }
 
 uint64_t shard_rows_total(const srf_view_t& v) {
@@ -403,6 +432,7 @@ srf_status srf_create(const srf_config_t* cfg, int device, srf_ctx** out) {
         CK_CREATE(cudaMalloc((void**)&ctx->w_rgb, (64 * 32 + 64 * 64 + 16 * 64) * sizeof(__half)));
     }
     CK_CREATE(cudaMalloc((void**)&ctx->d_counters, sizeof(FrameCounters)));
+    CK_CREATE(cudaMalloc((void**)&ctx->d_chunk_cursor, sizeof(uint32_t)));
     CK_CREATE(cudaMallocHost((void**)&ctx->h_counters, sizeof(FrameCounters)));
     for (int i = 0; i < 8; ++i) CK_CREATE(cudaEventCreate(&ctx->ev[i]));
 #undef CK_CREATE
@@ -419,7 +449,8 @@ void srf_destroy(srf_ctx* ctx) {
     void* ptrs[] = {ctx->grid, ctx->grid_current, ctx->partial_a, ctx->partial_b, ctx->mean, ctx->bits, ctx->table,
                     ctx->w_density, ctx->w_rgb, ctx->blobs, ctx->cmap, ctx->d_counters, ctx->ray_dir_t.p, ctx->ray_end.p,
                     ctx->counts.p, ctx->offsets.p, ctx->scan_scratch.p, ctx->pos_dt.p, ctx->sample_ray.p, ctx->rgbs.p,
-                    ctx->img_out.p, ctx->img_accum.p};
+                    ctx->img_out.p, ctx->img_accum.p, ctx->pool_pos.p, ctx->pool_shaded.p, ctx->chunk_ray.p, ctx->chunk_next.p,
+                    ctx->ray_head.p, ctx->d_chunk_cursor};
     for (void* p : ptrs) if (p) cudaFree(p);
     if (ctx->h_counters) cudaFreeHost(ctx->h_counters);
     if (ctx->h_coarse) cudaFreeHost(ctx->h_coarse);
@@ -706,59 +737,62 @@ srf_status srf_render_frame(srf_ctx* ctx, const srf_view_t* view, const srf_post
         *acc += ms;
     };
 
-    if (tm) cudaEventRecord(ctx->ev[0], s);
-    if ((st = count_and_scan(ctx, v, s)) != SRF_OK) return st;
-    if (tm) cudaEventRecord(ctx->ev[1], s);
-    uint64_t total = 0;
-    if ((st = read_coarse_offsets(ctx, v.n_rays, s, &total)) != SRF_OK) return st;
-    if (tm) lap(0, 1, &ms_sampler);
-    if (d_n_samples) SRF_CK(ctx, cudaMemcpyAsync(d_n_samples, ctx->counts.p, v.n_rays * sizeof(uint32_t), cudaMemcpyDeviceToDevice, s));
-
-    // batches of whole coarse groups whose samples fit the scratch
-    const uint64_t cap_limit = ctx->reserve_samples ? ctx->reserve_samples : kAutoSampleCapacity;
-    const size_t n_groups = (size_t)((v.n_rays + kCoarse - 1) / kCoarse);
-    auto group_begin = [&](size_t k) { return k < n_groups ? ctx->h_coarse[k] : total; };   // offsets[k*kCoarse]
-    uint64_t largest_group = 0;
-    for (size_t k = 0; k < n_groups; ++k) largest_group = std::max(largest_group, group_begin(k + 1) - group_begin(k));
-    if (largest_group > cap_limit && ctx->reserve_samples)
-        return fail(ctx, SRF_ERR_CAPACITY, "srf_reserve limit is smaller than the samples of one group of 4096 rays");
-    const uint64_t capacity = std::max(std::min(total, cap_limit), largest_group);
-    if ((st = ensure_sample_buffers(ctx, std::max<uint64_t>(capacity, 1))) != SRF_OK) return st;
+    // Sample pool: every ray of a batch is given room for the most samples its step-size law allows, so the
+    // single-pass sampler cannot run out of chunks and nothing has to be read back before the field runs.
+    const uint32_t bound = ray_sample_bound(ctx->cfg, ctx->g);
+    const uint64_t per_ray_slots = ((uint64_t)bound + kChunkSamples - 1) / kChunkSamples * kChunkSamples + kChunkSamples;
+    const uint64_t limit = ctx->reserve_samples ? ctx->reserve_samples : kAutoSampleCapacity;
+    uint64_t rays_per_batch = limit / per_ray_slots;
+    if (rays_per_batch == 0) return fail(ctx, SRF_ERR_CAPACITY, "srf_reserve limit is smaller than the samples one ray may emit");
+    if (rays_per_batch >= v.n_rays) rays_per_batch = v.n_rays;
+    else if (rays_per_batch > 128) rays_per_batch -= rays_per_batch % 128;
+    const uint64_t pool_slots = rays_per_batch * per_ray_slots;
+    if (pool_slots / kChunkSamples >= 0xffffffffull) return fail(ctx, SRF_ERR_CAPACITY, "sample pool exceeds 2^32 chunks");
+    const uint32_t pool_chunks = (uint32_t)(pool_slots / kChunkSamples);
+    if ((st = ensure(ctx, ctx->ray_dir_t, v.n_rays * sizeof(float4))) != SRF_OK) return st;
+    if ((st = ensure(ctx, ctx->ray_end, v.n_rays)) != SRF_OK) return st;
+    if ((st = ensure(ctx, ctx->counts, v.n_rays * sizeof(uint32_t))) != SRF_OK) return st;
+    if ((st = ensure(ctx, ctx->ray_head, v.n_rays * sizeof(uint32_t))) != SRF_OK) return st;
+    if ((st = ensure(ctx, ctx->pool_pos, pool_slots * sizeof(float4))) != SRF_OK) return st;
+    if ((st = ensure(ctx, ctx->pool_shaded, pool_slots * sizeof(float4))) != SRF_OK) return st;
+    if ((st = ensure(ctx, ctx->chunk_ray, (size_t)pool_chunks * sizeof(uint32_t))) != SRF_OK) return st;
+    if ((st = ensure(ctx, ctx->chunk_next, (size_t)pool_chunks * sizeof(uint32_t))) != SRF_OK) return st;
+    SRF_CK(ctx, cudaMemsetAsync(ctx->d_counters, 0, sizeof(FrameCounters), s));
 
     const bool blobs = ctx->cfg.field_type == SRF_FIELD_BLOBS;
+    const uint8_t* bits = ctx->cfg.use_grid ? ctx->bits : nullptr;
     uint32_t n_batches = 0;
-    size_t k0 = 0;
-    while (k0 < n_groups) {
-        size_t k1 = k0 + 1;
-        while (k1 < n_groups && group_begin(k1 + 1) - group_begin(k0) <= capacity) ++k1;
-        const uint64_t r0 = (uint64_t)k0 * kCoarse, r1 = std::min<uint64_t>((uint64_t)k1 * kCoarse, v.n_rays);
-        const uint64_t n_s = group_begin(k1) - group_begin(k0);
+    for (uint64_t r0 = 0; r0 < v.n_rays; r0 += rays_per_batch) {
+        const uint64_t r1 = std::min<uint64_t>(r0 + rays_per_batch, v.n_rays);
+        SRF_CK(ctx, cudaMemsetAsync(ctx->d_chunk_cursor, 0, sizeof(uint32_t), s));
         if (tm) cudaEventRecord(ctx->ev[2], s);
-        launch_ray_emit(ctx->g, v, ctx->cfg.use_grid ? ctx->bits : nullptr, (const float4*)ctx->ray_dir_t.p,
-                        (const uint64_t*)ctx->offsets.p, r0, r1, (float4*)ctx->pos_dt.p, (uint32_t*)ctx->sample_ray.p, nullptr,
-                        nullptr, nullptr, ctx->d_counters, s);
+        launch_march_paged(ctx->g, v, bits, r0, r1, (float4*)ctx->pool_pos.p, (uint32_t*)ctx->chunk_ray.p, (uint32_t*)ctx->chunk_next.p,
+                           pool_chunks, ctx->d_chunk_cursor, (float4*)ctx->ray_dir_t.p, (uint8_t*)ctx->ray_end.p,
+                           (uint32_t*)ctx->counts.p, (uint32_t*)ctx->ray_head.p, ctx->d_counters, s);
         if (tm) cudaEventRecord(ctx->ev[3], s);
         if (blobs)
-            launch_field_blobs(ctx->g, v, ctx->blobs, ctx->n_blobs, ctx->cmap, (const float4*)ctx->pos_dt.p, n_s, (float4*)ctx->rgbs.p, s);
+            launch_field_blobs(ctx->g, v, ctx->blobs, ctx->n_blobs, ctx->cmap, (const float4*)ctx->pool_pos.p, 0,
+                               (float4*)ctx->pool_shaded.p, s, ctx->d_chunk_cursor);
         else if (ctx->use_tcgen05)
-            launch_field_network_tc(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, (const float4*)ctx->pos_dt.p,
-                                    (const uint32_t*)ctx->sample_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, n_s, nullptr,
-                                    (float4*)ctx->rgbs.p, &ctx->g, &v, &ctx->d_counters->error_flags, s);
+            launch_field_network_tc(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, (const float4*)ctx->pool_pos.p,
+                                    (const uint32_t*)ctx->chunk_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, 0, nullptr,
+                                    (float4*)ctx->pool_shaded.p, &ctx->g, &v, &ctx->d_counters->error_flags, s,
+                                    ctx->d_chunk_cursor, kChunkShift);
         else
-            launch_field_network(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, (const float4*)ctx->pos_dt.p,
-                                 (const uint32_t*)ctx->sample_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, n_s, nullptr,
-                                 (float4*)ctx->rgbs.p, &ctx->g, &v, s);
+            launch_field_network(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, (const float4*)ctx->pool_pos.p,
+                                 (const uint32_t*)ctx->chunk_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, 0, nullptr,
+                                 (float4*)ctx->pool_shaded.p, &ctx->g, &v, s, ctx->d_chunk_cursor, kChunkShift);
         if (tm) cudaEventRecord(ctx->ev[4], s);
-        launch_composite(ctx->g, v, dp, (const uint64_t*)ctx->offsets.p, r0, r1, (const float4*)ctx->rgbs.p,
-                         (const uint8_t*)ctx->ray_end.p, (float4*)d_out, (float4*)d_accum, (float4*)d_rgba_raw, nullptr,
-                         ctx->d_counters, s);
+        launch_composite_paged(ctx->g, v, dp, r0, r1, (const uint32_t*)ctx->ray_head.p, (const uint32_t*)ctx->counts.p,
+                               (const uint32_t*)ctx->chunk_next.p, (const float4*)ctx->pool_shaded.p, (const uint8_t*)ctx->ray_end.p,
+                               (float4*)d_out, (float4*)d_accum, (float4*)d_rgba_raw, nullptr, ctx->d_counters, s);
         if (tm) {
             cudaEventRecord(ctx->ev[5], s);
             lap(2, 3, &ms_sampler); lap(3, 4, &ms_field); lap(4, 5, &ms_comp);
         }
         ++n_batches;
-        k0 = k1;
     }
+    if (d_n_samples) SRF_CK(ctx, cudaMemcpyAsync(d_n_samples, ctx->counts.p, v.n_rays * sizeof(uint32_t), cudaMemcpyDeviceToDevice, s));
     SRF_CK(ctx, cudaGetLastError());
     if (stats) {
         SRF_CK(ctx, cudaMemcpyAsync(ctx->h_counters, ctx->d_counters, sizeof(FrameCounters), cudaMemcpyDeviceToHost, s));
@@ -774,6 +808,7 @@ srf_status srf_render_frame(srf_ctx* ctx, const srf_view_t* view, const srf_post
         stats->ms_sampler = ms_sampler; stats->ms_field = ms_field; stats->ms_composite = ms_comp; stats->ms_post = 0.f;
         if (stats->error_flags & 1u) return fail(ctx, SRF_ERR_TIMEOUT, "a ray hit the march loop's iteration bound");
         if (stats->error_flags & 2u) return fail(ctx, SRF_ERR_TIMEOUT, "a wait on the tensor-core commit barrier expired");
+        if (stats->error_flags & 4u) return fail(ctx, SRF_ERR_CAPACITY, "the sample pool ran out of chunks");
     }
     return SRF_OK;
 }

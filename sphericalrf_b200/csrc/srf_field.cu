@@ -25,7 +25,9 @@ __global__ void __launch_bounds__(kFieldBlock)
 k_field_network(const NetMeta net, const __half* __restrict__ table, const __half* __restrict__ wd, const __half* __restrict__ wc,
                 const float4* __restrict__ pos_dt, const uint32_t* __restrict__ sample_ray,
                 const float4* __restrict__ ray_dir_t, const float* __restrict__ coords7, uint64_t n,
-                uint2* __restrict__ rgbsigma, float4* __restrict__ shaded, const DevCfg cfg, const DevView view) {
+                uint2* __restrict__ rgbsigma, float4* __restrict__ shaded, const DevCfg cfg, const DevView view,
+                const uint32_t* __restrict__ n_chunks_dev, uint32_t ray_shift) {
+    if (n_chunks_dev) n = (uint64_t)(*n_chunks_dev) * kChunkSamples;
     __shared__ __align__(16) __half sW[kWeightHalves];
     __shared__ __align__(16) __half sRows[kFieldBlock * kRowLd];
     __shared__ EncMeta enc_meta;
@@ -48,7 +50,7 @@ k_field_network(const NetMeta net, const __half* __restrict__ table, const __hal
                 x = c[0]; y = c[1]; z = c[2]; dx = c[4]; dy = c[5]; dz = c[6];
             } else {
                 const float4 p = pos_dt[s];
-                const float4 d = ray_dir_t[sample_ray[s]];
+                const float4 d = ray_dir_t[sample_ray[s >> ray_shift]];
                 x = p.x; y = p.y; z = p.z;
                 dx = (d.x + 1.f) * 0.5f; dy = (d.y + 1.f) * 0.5f; dz = (d.z + 1.f) * 0.5f;   // warp_direction
             }
@@ -197,12 +199,12 @@ k_field_density(const NetMeta net, const __half* __restrict__ table, const __hal
 // Analytic stand-in scene, fp32, one thread per sample.
 __global__ void __launch_bounds__(256)
 k_field_blobs(const DevCfg g, const DevView v, const float* __restrict__ blobs, uint32_t n_blobs, const float* __restrict__ cmap,
-              const float4* __restrict__ pos_dt, uint64_t n, float4* __restrict__ out) {
+              const float4* __restrict__ pos_dt, uint64_t n, float4* __restrict__ out, const uint32_t* __restrict__ n_chunks_dev) {
     extern __shared__ float s_blobs[];
     for (uint32_t i = threadIdx.x; i < n_blobs * 5; i += blockDim.x) s_blobs[i] = blobs[i];
     __syncthreads();
-    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
+    if (n_chunks_dev) n = (uint64_t)(*n_chunks_dev) * kChunkSamples;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
     const float4 p = pos_dt[i];
     const V3 x = unwarp_position(g, mk3(p.x, p.y, p.z));
     float sigma = 0.f;
@@ -217,6 +219,7 @@ k_field_blobs(const DevCfg g, const DevView v, const float* __restrict__ blobs, 
     const float raw[4] = {fmaf(cmap[2], pz, fmaf(cmap[1], py, cmap[0] * px)), fmaf(cmap[5], pz, fmaf(cmap[4], py, cmap[3] * px)),
                           fmaf(cmap[8], pz, fmaf(cmap[7], py, cmap[6] * px)), sigma};
     out[i] = shade_sample(g, v, raw, p.w, mk3(p.x, p.y, p.z));
+    }
 }
 
 int field_grid(uint64_t n) {
@@ -233,17 +236,17 @@ int field_grid(uint64_t n) {
 void launch_field_network(const NetMeta& net, const __half* table, const __half* w_density, const __half* w_rgb,
                           const float4* pos_dt, const uint32_t* sample_ray, const float4* ray_dir_t,
                           const float* coords7, uint64_t n, uint2* rgbsigma, float4* shaded, const DevCfg* g,
-                          const DevView* v, cudaStream_t stream) {
-    if (n == 0) return;
-    const int grid = field_grid(n);
+                          const DevView* v, cudaStream_t stream, const uint32_t* n_chunks_dev, uint32_t ray_shift) {
+    if (n == 0 && !n_chunks_dev) return;
+    const int grid = field_grid(n_chunks_dev ? ~0ull >> 8 : n);
     DevCfg g0; DevView v0;
     memset(&g0, 0, sizeof(g0)); memset(&v0, 0, sizeof(v0));
     if (g) g0 = *g;
     if (v) v0 = *v;
     if (net.n_features == 2)
-        k_field_network<2><<<grid, kFieldBlock, 0, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0);
+        k_field_network<2><<<grid, kFieldBlock, 0, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0, n_chunks_dev, ray_shift);
     else
-        k_field_network<4><<<grid, kFieldBlock, 0, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0);
+        k_field_network<4><<<grid, kFieldBlock, 0, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0, n_chunks_dev, ray_shift);
 }
 
 void launch_field_density(const NetMeta& net, const __half* table, const __half* w_density, const float* positions,
@@ -257,10 +260,15 @@ void launch_field_density(const NetMeta& net, const __half* table, const __half*
 }
 
 void launch_field_blobs(const DevCfg& g, const DevView& v, const float* blobs, uint32_t n_blobs, const float* color_map,
-                        const float4* pos_dt, uint64_t n, float4* shaded, cudaStream_t stream) {
-    if (n == 0) return;
-    k_field_blobs<<<(unsigned int)((n + 255) / 256), 256, n_blobs * 5 * sizeof(float), stream>>>(
-        g, v, blobs, n_blobs, color_map, pos_dt, n, shaded);
+                        const float4* pos_dt, uint64_t n, float4* shaded, cudaStream_t stream, const uint32_t* n_chunks_dev) {
+    if (n == 0 && !n_chunks_dev) return;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const uint64_t want = n_chunks_dev ? ~0ull >> 8 : (n + 255) / 256;
+    const uint64_t cap = (uint64_t)sms * 16;
+    k_field_blobs<<<(unsigned int)(want < cap ? want : cap), 256, n_blobs * 5 * sizeof(float), stream>>>(
+        g, v, blobs, n_blobs, color_map, pos_dt, n, shaded, n_chunks_dev);
 }
 
 }  // namespace srf

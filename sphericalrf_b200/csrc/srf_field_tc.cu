@@ -166,7 +166,8 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
                    const uint32_t* __restrict__ sample_ray, const float4* __restrict__ ray_dir_t,
                    const float* __restrict__ coords7, uint64_t n, uint2* __restrict__ rgbsigma,
                    float4* __restrict__ shaded, const DevCfg g, const DevView v,
-                   unsigned int* __restrict__ error_flags) {
+                   unsigned int* __restrict__ error_flags, const uint32_t* __restrict__ n_chunks_dev, uint32_t ray_shift) {
+    if (n_chunks_dev) n = (uint64_t)(*n_chunks_dev) * kChunkSamples;        // frame path: the sampler's chunk count
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, warp = tid >> 5;
     const int group = tid >> 7, row = tid & 127;
@@ -248,7 +249,7 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
                 x = c[0]; y = c[1]; z = c[2]; dx = c[4]; dy = c[5]; dz = c[6];
             } else {
                 const float4 p = pos_dt[s];
-                const float4 d = ray_dir_t[sample_ray[s]];
+                const float4 d = ray_dir_t[sample_ray[s >> ray_shift]];
                 x = p.x; y = p.y; z = p.z;
                 dx = (d.x + 1.f) * 0.5f; dy = (d.y + 1.f) * 0.5f; dz = (d.z + 1.f) * 0.5f;   // warp_direction
             }
@@ -347,8 +348,9 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
 void launch_field_network_tc(const NetMeta& net, const __half* table, const __half* w_density, const __half* w_rgb,
                              const float4* pos_dt, const uint32_t* sample_ray, const float4* ray_dir_t,
                              const float* coords7, uint64_t n, uint2* rgbsigma, float4* shaded, const DevCfg* g,
-                             const DevView* v, unsigned int* error_flags, cudaStream_t stream) {
-    if (n == 0) return;
+                             const DevView* v, unsigned int* error_flags, cudaStream_t stream,
+                             const uint32_t* n_chunks_dev, uint32_t ray_shift) {
+    if (n == 0 && !n_chunks_dev) return;
     // per device and cheap: set on every launch rather than cached per process
     cudaFuncSetAttribute(k_field_network_tc<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmTotal);
     cudaFuncSetAttribute(k_field_network_tc<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmTotal);
@@ -357,15 +359,15 @@ void launch_field_network_tc(const NetMeta& net, const __half* table, const __ha
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const uint64_t tiles = (n + kTcBlock - 1) / kTcBlock;    // pairs of 128-sample tiles
     const uint64_t cap = (uint64_t)sms * 4;                  // four resident CTAs per SM
-    const int grid = (int)(tiles < cap ? tiles : cap);
+    const int grid = n_chunks_dev ? (int)cap : (int)(tiles < cap ? tiles : cap);
     DevCfg g0; DevView v0;
     memset(&g0, 0, sizeof(g0)); memset(&v0, 0, sizeof(v0));
     if (g) g0 = *g;
     if (v) v0 = *v;
     if (net.n_features == 2)
-        k_field_network_tc<2><<<grid, kTcBlock, kSmTotal, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0, error_flags);
+        k_field_network_tc<2><<<grid, kTcBlock, kSmTotal, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0, error_flags, n_chunks_dev, ray_shift);
     else
-        k_field_network_tc<4><<<grid, kTcBlock, kSmTotal, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0, error_flags);
+        k_field_network_tc<4><<<grid, kTcBlock, kSmTotal, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0, error_flags, n_chunks_dev, ray_shift);
 }
 
 }  // namespace srf

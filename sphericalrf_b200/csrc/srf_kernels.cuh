@@ -53,6 +53,16 @@ void launch_ray_emit(const DevCfg& g, const DevView& v, const uint8_t* bits, con
                      uint32_t* sample_ray, float* coords7, uint32_t* ordinal, uint32_t* cell,
                      FrameCounters* counters, cudaStream_t stream);
 
+// Frame path: single-pass paged sampler.  Samples of a ray live in a linked list of chunks of
+// kChunkSamples records taken from a pool; see srf_sampler.cu.
+constexpr uint32_t kChunkSamples = 16;
+constexpr uint32_t kChunkShift = 4;
+constexpr uint32_t kNoChunk = 0xffffffffu;
+void launch_march_paged(const DevCfg& g, const DevView& v, const uint8_t* bits, uint64_t ray_begin, uint64_t ray_end,
+                        float4* pool_pos_dt, uint32_t* chunk_ray, uint32_t* chunk_next, uint32_t pool_chunks,
+                        uint32_t* chunk_cursor, float4* ray_dir_t, uint8_t* ray_end_out, uint32_t* ray_count,
+                        uint32_t* ray_head, FrameCounters* counters, cudaStream_t stream);
+
 // Rays only (generate_rays_from_camera_matrix): direction, t at the first occupied step, alive, pixel.
 void launch_generate_rays(const DevCfg& g, const DevView& v, const uint8_t* bits, float* dir, float* t,
                           uint8_t* alive, uint32_t* pixel, cudaStream_t stream);
@@ -63,7 +73,8 @@ void launch_generate_rays(const DevCfg& g, const DevView& v, const uint8_t* bits
 void launch_field_network(const NetMeta& net, const __half* table, const __half* w_density, const __half* w_rgb,
                           const float4* pos_dt, const uint32_t* sample_ray, const float4* ray_dir_t,
                           const float* coords7, uint64_t n, uint2* rgbsigma, float4* shaded, const DevCfg* g,
-                          const DevView* v, cudaStream_t stream);
+                          const DevView* v, cudaStream_t stream, const uint32_t* n_chunks_dev = nullptr,
+                          uint32_t ray_shift = 0);
 //   the same on tcgen05 tensor cores with TMEM accumulators (srf_field_tc.cu); error_flags bit 1 reports an
 //   expired wait on the MMA commit barrier.
 //   Output: either rgbsigma (4 raw halves per sample, the reference's network output) or, on the frame path,
@@ -71,14 +82,18 @@ void launch_field_network(const NetMeta& net, const __half* table, const __half*
 void launch_field_network_tc(const NetMeta& net, const __half* table, const __half* w_density, const __half* w_rgb,
                              const float4* pos_dt, const uint32_t* sample_ray, const float4* ray_dir_t,
                              const float* coords7, uint64_t n, uint2* rgbsigma, float4* shaded, const DevCfg* g,
-                             const DevView* v, unsigned int* error_flags, cudaStream_t stream);
+                             const DevView* v, unsigned int* error_flags, cudaStream_t stream,
+                             const uint32_t* n_chunks_dev = nullptr, uint32_t ray_shift = 0);
+//   n_chunks_dev (frame path): the number of samples is *n_chunks_dev * kChunkSamples, read on the device, and
+//   the ray of sample s is sample_ray[s >> ray_shift] (one entry per chunk).
 //   density only: positions (3 floats, stride given in floats) -> 16 halves per position.
 void launch_field_density(const NetMeta& net, const __half* table, const __half* w_density, const float* positions,
                           uint32_t stride, uint64_t n, __half* out16, cudaStream_t stream);
 //   analytic blob field in fp32 -> (r,g,b logits, sigma), 4 floats per sample.
 //   writes shaded samples (activated colour, step opacity).
 void launch_field_blobs(const DevCfg& g, const DevView& v, const float* blobs, uint32_t n_blobs, const float* color_map,
-                        const float4* pos_dt, uint64_t n, float4* shaded, cudaStream_t stream);
+                        const float4* pos_dt, uint64_t n, float4* shaded, cudaStream_t stream,
+                        const uint32_t* n_chunks_dev = nullptr);
 
 struct DevPost {
     float exposure_scale;      // 2^exposure
@@ -93,6 +108,12 @@ void launch_composite(const DevCfg& g, const DevView& v, const DevPost& post, co
                       uint64_t ray_begin, uint64_t ray_end, const float4* shaded, const uint8_t* ray_end_reason,
                       float4* out, float4* accum, float4* rgba_raw, uint32_t* n_composited, FrameCounters* counters,
                       cudaStream_t stream);
+
+// The same over per-ray chunk lists (frame path).
+void launch_composite_paged(const DevCfg& g, const DevView& v, const DevPost& post, uint64_t ray_begin, uint64_t ray_end,
+                            const uint32_t* ray_head, const uint32_t* ray_count, const uint32_t* chunk_next,
+                            const float4* pool_shaded, const uint8_t* ray_end_reason, float4* out, float4* accum,
+                            float4* rgba_raw, uint32_t* n_composited, FrameCounters* counters, cudaStream_t stream);
 
 // Compositing over Coordinate records (stage entry srf_volume_rendering): no post stage.
 void launch_composite_coords(const DevCfg& g, const DevView& v, const uint64_t* offsets, uint64_t n_rays,

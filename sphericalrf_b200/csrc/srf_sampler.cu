@@ -6,7 +6,11 @@
 // 8 samples per ray per host iteration, each ray is marched to its end in one kernel: a count
 // pass sizes a compact per-ray-contiguous sample buffer, an exclusive scan places the rays, an
 // emit pass fills it.
+#include <cooperative_groups.h>
+
 #include "srf_kernels.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace srf {
 
@@ -84,6 +88,67 @@ k_ray_emit(const DevCfg g, const DevView v, const uint8_t* __restrict__ bits, co
         ++slot;
         return slot < slot_end;     // never writes past the slots the count pass reserved
     });
+}
+
+// Single-pass sampler of the frame path.  Each thread marches its ray once and appends the live
+// samples to the ray's own list of fixed-size chunks (kChunkSamples records) taken from a pool.  Chunks
+// are handed out by one atomicAdd per group of lanes that need one at the same time (the lanes of a
+// warp march neighbouring pixels in near lockstep, so they usually run out of room together).  There is
+// no counting pass, no scan and no read-back: the field kernel later walks the pool densely, the
+// compositor walks each ray's chunk list.
+__global__ void __launch_bounds__(kBlock)
+k_march_paged(const DevCfg g, const DevView v, const uint8_t* __restrict__ bits, uint64_t ray_begin, uint64_t ray_end,
+              float4* __restrict__ pool_pos_dt, uint32_t* __restrict__ chunk_ray, uint32_t* __restrict__ chunk_next,
+              uint32_t pool_chunks, uint32_t* __restrict__ chunk_cursor, float4* __restrict__ ray_dir_t,
+              uint8_t* __restrict__ ray_end_out, uint32_t* __restrict__ ray_count, uint32_t* __restrict__ ray_head,
+              FrameCounters* __restrict__ counters) {
+    const uint64_t i = ray_begin + (uint64_t)blockIdx.x * kBlock + threadIdx.x;
+    unsigned long long alive = 0, steps = 0, samples = 0;
+    unsigned int err = 0;
+    if (i < ray_end) {
+        const uint32_t pixel = shard_ray_pixel(v, i);
+        const RayInit r = init_ray(g, v, pixel);
+        uint32_t n = 0, end = RAY_END_BORN_DEAD, n_steps = 0, head = kNoChunk;
+        if (r.alive) {
+            uint32_t chunk = kNoChunk, fill = kChunkSamples;
+            end = march_ray(g, bits, r.o, r.d, r.t, &n_steps, [&](const V3& w, float dt, uint32_t, uint32_t, float) {
+                if (fill == kChunkSamples) {
+                    const cg::coalesced_group lanes = cg::coalesced_threads();
+                    uint32_t base = 0;
+                    if (lanes.thread_rank() == 0) base = atomicAdd(chunk_cursor, lanes.size());
+                    const uint32_t c = lanes.shfl(base, 0) + lanes.thread_rank();
+                    if (c >= pool_chunks) { err = 4u; return false; }      // the pool is sized so that this cannot happen
+                    chunk_ray[c] = (uint32_t)i;
+                    chunk_next[c] = kNoChunk;
+                    if (chunk == kNoChunk) head = c; else chunk_next[chunk] = c;
+                    chunk = c;
+                    fill = 0;
+                }
+                pool_pos_dt[(uint64_t)chunk * kChunkSamples + fill] = make_float4(w.x, w.y, w.z, dt);
+                ++fill;
+                ++n;
+                return true;
+            });
+            alive = 1;
+            if (end == RAY_END_LIMIT) err |= 1u;
+        }
+        ray_dir_t[i] = make_float4(r.d.x, r.d.y, r.d.z, r.t);
+        ray_end_out[i] = (uint8_t)end;
+        ray_count[i] = n;
+        ray_head[i] = head;
+        steps = n_steps;
+        samples = n;
+    }
+    alive = warp_sum_u64(alive);
+    steps = warp_sum_u64(steps);
+    samples = warp_sum_u64(samples);
+    for (int o = 16; o > 0; o >>= 1) err |= __shfl_down_sync(0xffffffffu, err, o);
+    if ((threadIdx.x & 31) == 0) {
+        if (alive) atomicAdd(&counters->n_alive, alive);
+        if (steps) atomicAdd(&counters->n_march_steps, steps);
+        if (samples) atomicAdd(&counters->n_samples, samples);
+        if (err) atomicOr(&counters->error_flags, err);
+    }
 }
 
 __global__ void __launch_bounds__(kBlock)
@@ -231,6 +296,16 @@ void launch_ray_emit(const DevCfg& g, const DevView& v, const uint8_t* bits, con
     else
         k_ray_emit<false><<<nb, kBlock, 0, stream>>>(g, v, bits, ray_dir_t, offsets, ray_begin, ray_end, pos_dt,
                                                      sample_ray, coords7, ordinal, cell);
+}
+
+void launch_march_paged(const DevCfg& g, const DevView& v, const uint8_t* bits, uint64_t ray_begin, uint64_t ray_end,
+                        float4* pool_pos_dt, uint32_t* chunk_ray, uint32_t* chunk_next, uint32_t pool_chunks,
+                        uint32_t* chunk_cursor, float4* ray_dir_t, uint8_t* ray_end_out, uint32_t* ray_count,
+                        uint32_t* ray_head, FrameCounters* counters, cudaStream_t stream) {
+    if (ray_end <= ray_begin) return;
+    k_march_paged<<<blocks_for(ray_end - ray_begin, kBlock), kBlock, 0, stream>>>(
+        g, v, bits, ray_begin, ray_end, pool_pos_dt, chunk_ray, chunk_next, pool_chunks, chunk_cursor, ray_dir_t, ray_end_out,
+        ray_count, ray_head, counters);
 }
 
 void launch_generate_rays(const DevCfg& g, const DevView& v, const uint8_t* bits, float* dir, float* t,
