@@ -266,6 +266,23 @@ def run_ours(args):
                      "mlp_tflops": ALG_FLOP_PER_SAMPLE * n_samples / (t_field * 1e-3) / 1e12 if t_field > 0 else 0.0},
         "stage_ms": {"sampler": t_sampler, "field": t_field, "composite_output": t_comp},
     }
+    if world == 1:
+        # density-grid refresh (Testbed::train_prep_nerf): 16 consecutive refreshes of the 128^3 grid, all-cells mode
+        r.refresh_reset(3001)
+        for _ in range(2):
+            r.refresh_grid(0)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(16):
+            r.refresh_grid(0)
+        e1.record()
+        torch.cuda.synchronize()
+        ms_refresh = e0.elapsed_time(e1) / 16
+        cells = cfg.grid_size ** 3
+        line["refresh"] = {"ms_per_refresh": ms_refresh, "cells": cells, "refreshes_per_s": 1e3 / ms_refresh,
+                           "algorithmic_gbs": cells * 532.125 / (ms_refresh * 1e-3) / 1e9,
+                           "algorithmic_tflops": cells * 4224.0 / (ms_refresh * 1e-3) / 1e12}
     if world == 1 and not args.no_cpu_baseline:
         v, cores, desc, _ = cpu_reference_sample(sc, target_seconds=15.0)
         line["cpu_baseline"] = {"value": v, "unit": "Mrays/s", "cores": cores, "kind": "port", "sample": desc}
