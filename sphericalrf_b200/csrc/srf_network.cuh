@@ -89,15 +89,17 @@ __device__ __forceinline__ void level_finish(const LevelCell& c, const uint32_t 
     }
 }
 
-// Encodes one position into 32 halves, returned as 16 packed pairs (pair i = features 2i, 2i+1).
-// `m` lives in shared memory (prepare_enc_meta).
+// Encodes levels [l_begin, l_end) of one position into the packed pairs out[l*F/2 ...] (pair i = features
+// 2i, 2i+1 of the 32-half encoding).  `m` lives in shared memory (prepare_enc_meta).  Callers that want to
+// interleave the encoding with other work call it on successive level ranges.
 template <int F>
-__device__ __forceinline__ void hash_encode_packed(const EncMeta* m, const __half* __restrict__ table, float x, float y,
-                                                   float z, uint32_t (&out)[16]) {
+__device__ __forceinline__ void hash_encode_range(const EncMeta* m, const __half* __restrict__ table, float x, float y,
+                                                  float z, int l_begin, int l_end, uint32_t (&out)[16]) {
     const uint32_t* table32 = reinterpret_cast<const uint32_t*>(table);
-    const int n_dense = m->n_dense, n_levels = m->n_levels;
+    const int n_dense = m->n_dense;
+    const int dense_end = l_end < n_dense ? l_end : n_dense;
 #pragma unroll 1
-    for (int l = 0; l < n_dense; ++l) {
+    for (int l = l_begin; l < dense_end; ++l) {
         const EncLevel L = m->level[l];
         const uint32_t* base = table32 + (size_t)L.offset * (F / 2);
         const LevelCell c = level_cell(L.scale, x, y, z);
@@ -118,7 +120,7 @@ __device__ __forceinline__ void hash_encode_packed(const EncMeta* m, const __hal
         level_finish<F>(c, raw, l, out);
     }
 #pragma unroll 2
-    for (int l = n_dense; l < n_levels; ++l) {
+    for (int l = l_begin > n_dense ? l_begin : n_dense; l < l_end; ++l) {
         const float scale = m->level[l].scale;
         const uint32_t mask = m->level[l].size - 1u;
         const uint32_t* base = table32 + (size_t)m->level[l].offset * (F / 2);
@@ -135,6 +137,13 @@ __device__ __forceinline__ void hash_encode_packed(const EncMeta* m, const __hal
         }
         level_finish<F>(c, raw, l, out);
     }
+}
+
+// Encodes one position into 32 halves, returned as 16 packed pairs.
+template <int F>
+__device__ __forceinline__ void hash_encode_packed(const EncMeta* m, const __half* __restrict__ table, float x, float y,
+                                                   float z, uint32_t (&out)[16]) {
+    hash_encode_range<F>(m, table, x, y, z, 0, m->n_levels, out);
 }
 
 // Same, written as 32 consecutive halves.
