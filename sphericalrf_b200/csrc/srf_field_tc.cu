@@ -132,9 +132,9 @@ __device__ __forceinline__ void store_units(const uint32_t (&acc)[16], unsigned 
     uint32_t h[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
-        __half2 v = __floats2half2_rn(__uint_as_float(acc[2 * k]), __uint_as_float(acc[2 * k + 1]));
-        if (RELU) v = __hmax2(v, __float2half2_rn(0.f));     // ReLU commutes with the rounding
-        h[k] = *reinterpret_cast<const uint32_t*>(&v);
+        const float lo = __uint_as_float(acc[2 * k]), hi = __uint_as_float(acc[2 * k + 1]);
+        if (RELU) asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(h[k]) : "f"(hi), "f"(lo));   // round and clamp at 0 in one instruction
+        else h[k] = pack2(lo, hi);
     }
     const uint4 u0 = make_uint4(h[0], h[1], h[2], h[3]);
     const uint4 u1 = make_uint4(h[4], h[5], h[6], h[7]);
