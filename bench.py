@@ -260,8 +260,11 @@ def run_ours(args):
         "e2e": {"value": e2e_value, "unit": "Mrays/s", "h2d_bytes_per_step": int(C.sizeof(abi.View) + C.sizeof(abi.Post)) * n_views,
                 "d2h_bytes_per_step": int(HEIGHT * WIDTH * 16 * n_views)},
         "gpu_launches": int(launches_per_frame * n_views * args.steps),
-        "roofline": {"kernel": "k_field_network (hash-grid gather + MLPs)", "bound": "hbm", "achieved": achieved, "peak": peak,
-                     "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+        "roofline": {"kernel": "k_field_network_tc (hash-grid gather + tcgen05 MLPs + shading)", "bound": "hbm", "achieved": achieved, "peak": peak,
+                     "unit": "GB/s", "frac": achieved / peak,
+                     # DRAM bytes of one launch: 33.7 B/sample from the ncu capture of a 108 M-sample launch
+                     # (profiles/field_network_tcgen05_config1_320x208.md), scaled by this launch's samples
+                     "traffic": 33.7 * n_samples / max(n_batches, 1), "peak_kind": peak_kind,
                      "ms_per_launch": t_field / max(n_batches, 1), "launches_per_frame": int(n_batches),
                      "mlp_tflops": ALG_FLOP_PER_SAMPLE * n_samples / (t_field * 1e-3) / 1e12 if t_field > 0 else 0.0},
         "stage_ms": {"sampler": t_sampler, "field": t_field, "composite_output": t_comp},
