@@ -91,10 +91,38 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+WORKLOAD = "1"          # BASELINE configuration: "1" (the benchmark), "0O", "0D", "4": other configurations, for the record
+WORKLOAD_NAMES = {
+    "1": "config1 full inference frame {w}x{h}, fp16 network, 128^3 bitfield",
+    "0O": "config0-O sampler+compositing, analytic blob field fp32, Original sampling, {w}x{h}",
+    "0D": "config0-D sampler+compositing, analytic blob field fp32, Disparity sampling, {w}x{h}",
+    "4": "config4 dense inward-facing scene, fp16 network, Original sampling, 2048-sample cap, {w}x{h}",
+}
+
+
 def build_scene():
     from sphericalrf_b200 import abi, synth
-    sc = synth.scene_config1(grid_size=128, width=WIDTH, height=HEIGHT)
-    return sc
+    if WORKLOAD == "1":
+        return synth.scene_config1(grid_size=128, width=WIDTH, height=HEIGHT)
+    if WORKLOAD in ("0O", "0D"):
+        return synth.scene_config0(WORKLOAD[1], 128, WIDTH, HEIGHT)
+    if WORKLOAD == "4":
+        return synth.scene_config4(128, WIDTH, HEIGHT)
+    raise SystemExit(f"unknown workload {WORKLOAD}")
+
+
+def workload_name():
+    return WORKLOAD_NAMES[WORKLOAD].format(w=WIDTH, h=HEIGHT)
+
+
+def upload_scene(r, sc):
+    from sphericalrf_b200 import abi
+    if sc["cfg"].field_type == abi.FIELD_NETWORK:
+        r.upload_network(sc["hash_table"], sc["density_mlp"], sc["rgb_mlp"])
+    else:
+        r.upload_blobs(sc["blobs"], sc["color_map"])
+    r.upload_density_grid(sc["grid"])
+    r.update_grid_bitfield()
 
 
 def cpu_reference_sample(sc, target_seconds=15.0):
@@ -103,7 +131,7 @@ def cpu_reference_sample(sc, target_seconds=15.0):
     from sphericalrf_b200 import abi, synth
     cfg = sc["cfg"]
     bits = synth.bitfield_from_grid(cfg, sc["grid"])
-    orc = srf_oracle.Oracle(cfg, bits, sc["hash_table"], sc["density_mlp"], sc["rgb_mlp"])
+    orc = srf_oracle.Oracle(cfg, bits, sc.get("hash_table"), sc.get("density_mlp"), sc.get("rgb_mlp"), sc.get("blobs"), sc.get("color_map"))
     b2, _ = orc.update_grid_bitfield(sc["grid"])
     orc.bitfield = b2
     view = abi.make_view(sc["cameras"][0], WIDTH, HEIGHT, sc["rfl"])
@@ -138,7 +166,7 @@ def run_reference(args):
         "impl": "reference", "metric": "render throughput", "value": value, "unit": "Mrays/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t_tot / max(1, args.steps), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": "config1 full inference frame 1245x825, fp16 network, 128^3 bitfield", "rays_per_frame": WIDTH * HEIGHT},
+        "config": {"workload": workload_name(), "rays_per_frame": WIDTH * HEIGHT},
         "cpu_baseline": {"value": value, "unit": "Mrays/s", "cores": cores, "kind": "port", "sample": desc},
         "e2e": {"value": value, "unit": "Mrays/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -166,9 +194,7 @@ def run_ours(args):
     sc = build_scene()
     cfg = sc["cfg"]
     r = Renderer(cfg, local_rank)
-    r.upload_network(sc["hash_table"], sc["density_mlp"], sc["rgb_mlp"])
-    r.upload_density_grid(sc["grid"])
-    r.update_grid_bitfield()
+    upload_scene(r, sc)
     post = abi.default_post()
     view = abi.make_view(sc["cameras"][0], WIDTH, HEIGHT, sc["rfl"], shard_rows=8, shard_count=world, shard_rank=rank)
     n_local = r.n_rays(view)
@@ -247,11 +273,20 @@ def run_ours(args):
     peak, peak_kind = _peaks()
     launches_per_frame = 3 * n_batches               # march, field, composite per batch of rays
     achieved = ALG_BYTES_PER_SAMPLE * n_samples / max(n_batches, 1) / (t_field / max(n_batches, 1) * 1e-3) / 1e9 if t_field > 0 else 0.0
+    roof_kernel = "k_field_network_tc (hash-grid gather + tcgen05 MLPs + shading)"
+    roof_ms = t_field / max(n_batches, 1)
+    roof_traffic = 33.7 * n_samples / max(n_batches, 1)
+    if cfg.field_type != abi.FIELD_NETWORK:
+        # sampler + compositing configurations: the sampler is the kernel of interest (28 B/sample + 80 B/ray)
+        roof_kernel = "k_march_paged (single-pass sampler)"
+        roof_ms = t_sampler / max(n_batches, 1)
+        achieved = (28.0 * n_samples + 80.0 * n_local) / (t_sampler * 1e-3) / 1e9 if t_sampler > 0 else 0.0
+        roof_traffic = 16.1 * n_samples / max(n_batches, 1)
     line = {
         "metric": "render throughput", "value": value, "unit": "Mrays/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
-        "config": {"workload": f"config1 full inference frame {WIDTH}x{HEIGHT}, fp16 network, 128^3 bitfield",
+        "config": {"workload": workload_name(),
                    "frames_per_step": n_views, "rays_per_frame": WIDTH * HEIGHT, "samples_per_frame_shard": int(n_samples),
                    "partition": f"rows in blocks of 8 round-robin over {world} rank(s), gather to rank 0",
                    "l2": "per-frame working set (sample buffers) far larger than L2; no flush needed"},
@@ -260,16 +295,16 @@ def run_ours(args):
         "e2e": {"value": e2e_value, "unit": "Mrays/s", "h2d_bytes_per_step": int(C.sizeof(abi.View) + C.sizeof(abi.Post)) * n_views,
                 "d2h_bytes_per_step": int(HEIGHT * WIDTH * 16 * n_views)},
         "gpu_launches": int(launches_per_frame * n_views * args.steps),
-        "roofline": {"kernel": "k_field_network_tc (hash-grid gather + tcgen05 MLPs + shading)", "bound": "hbm", "achieved": achieved, "peak": peak,
+        "roofline": {"kernel": roof_kernel, "bound": "hbm", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak,
                      # DRAM bytes of one launch: 33.7 B/sample from the ncu capture of a 108 M-sample launch
                      # (profiles/field_network_tcgen05_config1_320x208.md), scaled by this launch's samples
-                     "traffic": 33.7 * n_samples / max(n_batches, 1), "peak_kind": peak_kind,
-                     "ms_per_launch": t_field / max(n_batches, 1), "launches_per_frame": int(n_batches),
+                     "traffic": roof_traffic, "peak_kind": peak_kind,
+                     "ms_per_launch": roof_ms, "launches_per_frame": int(n_batches),
                      "mlp_tflops": ALG_FLOP_PER_SAMPLE * n_samples / (t_field * 1e-3) / 1e12 if t_field > 0 else 0.0},
         "stage_ms": {"sampler": t_sampler, "field": t_field, "composite_output": t_comp},
     }
-    if world == 1:
+    if world == 1 and cfg.field_type == abi.FIELD_NETWORK:
         # density-grid refresh (Testbed::train_prep_nerf): 16 consecutive refreshes of the 128^3 grid, all-cells mode
         r.refresh_reset(3001)
         for _ in range(2):
@@ -301,11 +336,17 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="1", choices=sorted(WORKLOAD_NAMES), help="BASELINE configuration; the benchmark is 1")
     ap.add_argument("--res", default=None, help="WxH: a smaller image of the same scene, for profiler captures only "
                                                 "(the benchmark number is the default 1245x825)")
     args = ap.parse_args()
+    global WIDTH, HEIGHT, WORKLOAD
+    WORKLOAD = args.workload
+    if WORKLOAD in ("0O", "0D"):
+        WIDTH, HEIGHT = 800, 800
+    elif WORKLOAD == "4":
+        WIDTH, HEIGHT = 3840, 2160
     if args.res:
-        global WIDTH, HEIGHT
         WIDTH, HEIGHT = (int(x) for x in args.res.lower().split("x"))
     if args.impl == "reference":
         run_reference(args)
