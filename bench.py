@@ -200,15 +200,32 @@ def run_ours(args):
     n_local = r.n_rays(view)
     rays_per_step = WIDTH * HEIGHT * n_views
 
-    from sphericalrf_b200.sharding import TileGather
+    from sphericalrf_b200.sharding import PeerImage, TileGather
     tg = TileGather(WIDTH, HEIGHT, n_views, 4, 8, dev)
     assert tg.n_local == n_local
     out = tg.tiles
     accum = torch.zeros((tg.n_pad, 4), dtype=torch.float32, device=dev)
+    # N > 1: the output stage stores pixels straight into rank 0's image over NVLink (peer stores); NCCL gather of
+    # tiles is the fallback when symmetric memory cannot be set up
+    peer, gather_kind = None, "none"
+    if world > 1:
+        gather_kind = "nccl gather of tiles"
+        if args.gather == "peer":
+            try:
+                peer = PeerImage(WIDTH, HEIGHT, n_views, dev)
+                gather_kind = "peer stores into rank 0's image (fused into the output stage) + barrier"
+            except Exception as e:          # noqa: BLE001
+                if rank == 0:
+                    print(f"symmetric memory unavailable ({type(e).__name__}: {e}); using the NCCL gather", file=sys.stderr)
     host_img = torch.zeros((n_views, HEIGHT, WIDTH, 4), dtype=torch.float32).pin_memory() if rank == 0 else None
     stats = abi.FrameStats()
 
     def step_device():
+        if peer is not None:
+            for k in range(n_views):
+                r.render_frame_scatter_device(view, post, peer.root[k], accum)
+            peer.barrier()
+            return
         for k in range(n_views):
             r.render_frame_device(view, post, out[k], accum, None, None, None, None)
         if world > 1:
@@ -222,7 +239,7 @@ def run_ours(args):
         else:
             step_device()
             if rank == 0:
-                host_img.view(n_views, HEIGHT * WIDTH, 4).copy_(tg.image, non_blocking=True)
+                host_img.view(n_views, HEIGHT * WIDTH, 4).copy_(peer.local if peer is not None else tg.image, non_blocking=True)
                 torch.cuda.current_stream().synchronize()
 
     def timed(fn, steps, warmup, sample_clocks=False):
@@ -288,7 +305,7 @@ def run_ours(args):
         "dtype": "f16", "data": "synthetic",
         "config": {"workload": workload_name(),
                    "frames_per_step": n_views, "rays_per_frame": WIDTH * HEIGHT, "samples_per_frame_shard": int(n_samples),
-                   "partition": f"rows in blocks of 8 round-robin over {world} rank(s), gather to rank 0",
+                   "partition": f"rows in blocks of 8 round-robin over {world} rank(s)", "gather": gather_kind,
                    "l2": "per-frame working set (sample buffers) far larger than L2; no flush needed"},
         "frames_per_s": n_views / (ms_step * 1e-3),
         "clocks": clocks,
@@ -336,6 +353,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"], help="N > 1: how tiles reach rank 0")
     ap.add_argument("--workload", default="1", choices=sorted(WORKLOAD_NAMES), help="BASELINE configuration; the benchmark is 1")
     ap.add_argument("--res", default=None, help="WxH: a smaller image of the same scene, for profiler captures only "
                                                 "(the benchmark number is the default 1245x825)")

@@ -247,6 +247,15 @@ srf_status srf_render_frame(srf_ctx* ctx, const srf_view_t* view, const srf_post
                             float* d_out, float* d_accum, float* d_rgba_raw, uint32_t* d_n_samples,
                             srf_frame_stats_t* stats, void* stream);
 
+/* The same frame with the output stage fused into the gather of a sharded render: the pixel of every ray
+   of the shard is stored at its position in a whole-image buffer d_image float[height*width*4], which may
+   live on another GPU of the box (a peer-mapped pointer: plain stores over NVLink, no collective).  Pixels
+   outside the shard are not touched.  d_accum stays local and shard-indexed.  Replaces shade_kernel's
+   scatter `frame_buffer[payload.idx] = ...` (internal/testbed.cu:476) across GPUs; the caller orders the
+   stores against the consumer (a barrier or stream event after the call). */
+srf_status srf_render_frame_scatter(srf_ctx* ctx, const srf_view_t* view, const srf_post_t* post, float* d_image,
+                                    float* d_accum, srf_frame_stats_t* stats, void* stream);
+
 /* Testbed::render (internal/python_api.cu:17-41): spp passes of srf_render_frame and the copy
    to a host image h_image float[height*width*4] (whole image; shard_count must be 1).
    Synchronises. */

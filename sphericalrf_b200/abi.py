@@ -169,6 +169,7 @@ SYMBOLS = {
     "srf_network_density": (C.c_int, [_ctx, _vp, C.c_uint64, _vp, _vp]),
     "srf_volume_rendering": (C.c_int, [_ctx, _P(View), _vp, C.c_uint64, _vp, _vp, _vp, _vp, _vp]),
     "srf_render_frame": (C.c_int, [_ctx, _P(View), _P(Post), _vp, _vp, _vp, _vp, _P(FrameStats), _vp]),
+    "srf_render_frame_scatter": (C.c_int, [_ctx, _P(View), _P(Post), _vp, _vp, _P(FrameStats), _vp]),
     "srf_render": (C.c_int, [_ctx, _P(View), _P(Post), C.c_uint32, _vp, _P(FrameStats)]),
     "srf_dump_samples": (C.c_int, [_ctx, _P(View), C.c_uint64, C.c_uint64, C.c_uint64, _vp, _vp, _vp, _vp,
                                    _P(C.c_uint64)]),

@@ -188,7 +188,9 @@ k_composite_rays(const DevCfg g, const DevView v, const DevPost post, const uint
         const float rgba[4] = {R, G, B, A};
         if (rgba_raw) rgba_raw[r] = make_float4(R, G, B, A);
         if (n_composited) n_composited[r] = n;
-        if (out || accum) finish_pixel(g, v, post, hit, rgba, n_steps_total, accum ? accum + r : nullptr, out ? out + r : nullptr);
+        if (out || accum)
+            finish_pixel(g, v, post, hit, rgba, n_steps_total, accum ? accum + r : nullptr,
+                         out ? out + (v.out_by_pixel ? (uint64_t)shard_ray_pixel(v, r) : r) : nullptr);
         comp = n;
         hits = hit ? 1u : 0u;
     }

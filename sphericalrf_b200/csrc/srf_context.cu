@@ -715,13 +715,15 @@ srf_status srf_volume_rendering(srf_ctx* ctx, const srf_view_t* view, const uint
 }
 
 // ---- frames -------------------------------------------------------------------------------------------
-srf_status srf_render_frame(srf_ctx* ctx, const srf_view_t* view, const srf_post_t* post, float* d_out, float* d_accum,
-                            float* d_rgba_raw, uint32_t* d_n_samples, srf_frame_stats_t* stats, void* stream) {
+static srf_status render_frame_impl(srf_ctx* ctx, const srf_view_t* view, const srf_post_t* post, float* d_out, float* d_accum,
+                                    float* d_rgba_raw, uint32_t* d_n_samples, srf_frame_stats_t* stats, void* stream,
+                                    int out_by_pixel) {
     if (!ctx) return SRF_ERR_ARG;
     srf_status st = check_ready(ctx);
     if (st != SRF_OK) return st;
     DevView v;
     if ((st = make_view(ctx, view, &v)) != SRF_OK) return st;
+    v.out_by_pixel = out_by_pixel;
     DevPost dp;
     make_post(post, &dp);
     DeviceGuard guard(ctx->device);
@@ -811,6 +813,17 @@ srf_status srf_render_frame(srf_ctx* ctx, const srf_view_t* view, const srf_post
         if (stats->error_flags & 4u) return fail(ctx, SRF_ERR_CAPACITY, "the sample pool ran out of chunks");
     }
     return SRF_OK;
+}
+
+srf_status srf_render_frame(srf_ctx* ctx, const srf_view_t* view, const srf_post_t* post, float* d_out, float* d_accum,
+                            float* d_rgba_raw, uint32_t* d_n_samples, srf_frame_stats_t* stats, void* stream) {
+    return render_frame_impl(ctx, view, post, d_out, d_accum, d_rgba_raw, d_n_samples, stats, stream, 0);
+}
+
+srf_status srf_render_frame_scatter(srf_ctx* ctx, const srf_view_t* view, const srf_post_t* post, float* d_image,
+                                    float* d_accum, srf_frame_stats_t* stats, void* stream) {
+    if (!d_image) return fail(ctx, SRF_ERR_ARG, "d_image is NULL");
+    return render_frame_impl(ctx, view, post, d_image, d_accum, nullptr, nullptr, stats, stream, 1);
 }
 
 srf_status srf_render(srf_ctx* ctx, const srf_view_t* view, const srf_post_t* post, uint32_t spp, float* h_image,

@@ -45,6 +45,7 @@ struct DevView {
     float depth_scale;
     uint32_t shard_rows, shard_count, shard_rank;
     uint64_t n_rays;
+    int out_by_pixel;                        // output stage writes out[pixel] (whole-image buffer) instead of out[shard ray]
 };
 
 struct V3 { float x, y, z; };

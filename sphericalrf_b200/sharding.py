@@ -6,6 +6,13 @@ layout srf_render_frame writes) and rank 0 gathers the tiles and scatters them b
 order.  The per-ray arithmetic does not depend on the partition, so the assembled image is
 byte-identical to the single-rank image.  The only exchange step is this gather; weights, grid
 and bitfield are replicated.
+
+Two ways to move the tiles:
+  PeerImage  -- the output stage of the render kernel stores every pixel directly at its position in
+                rank 0's image over NVLink (srf_render_frame_scatter on a peer-mapped buffer from torch's
+                symmetric memory), followed by one barrier: no staging tile, no collective, no un-interleave;
+  TileGather -- NCCL/gloo `gather` of padded tiles + scatter into image order on rank 0 (works everywhere,
+                used by the CPU tests).
 """
 from __future__ import annotations
 
@@ -63,3 +70,25 @@ class TileGather:
             for r in range(self.world):
                 self.image[:, self._pix[r]] = self._recv[r][:, : self.counts[r]]
         return self.image
+
+
+class PeerImage:
+    """n_views whole images on rank 0 that every rank's output stage writes into with plain peer stores.
+
+    Every rank allocates the same symmetric buffer (the rendezvous is symmetric); only rank 0's copy
+    receives pixels.  `root` is this rank's view of rank 0's buffer; `barrier()` orders all ranks' stores
+    before rank 0 reads `local`.  NVLink multicast objects are not used (plain stores only)."""
+
+    def __init__(self, width: int, height: int, n_views: int, device, group=None):
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        shape = (n_views, height * width, 4)
+        self.local = symm_mem.empty(shape, dtype=torch.float32, device=torch.device(device))
+        self.local.zero_()
+        self.handle = symm_mem.rendezvous(self.local, self.group)
+        self.root = self.handle.get_buffer(0, shape, torch.float32)
+
+    def barrier(self):
+        self.handle.barrier()

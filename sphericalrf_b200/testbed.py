@@ -116,6 +116,13 @@ class Renderer:
         self._ck(self.lib.srf_render_frame(self.ctx, C.byref(view), C.byref(post), p(out), p(accum), p(rgba_raw),
                                            p(n_samples), None if stats is None else C.byref(stats), stream))
 
+    def render_frame_scatter_device(self, view, post, image, accum, stats=None, stream=None):
+        """Writes the shard's pixels at their positions of the whole-image tensor `image` (H*W, 4), which may be
+        a peer GPU's buffer; `accum` is the local shard-indexed accumulate buffer."""
+        self._ck(self.lib.srf_render_frame_scatter(self.ctx, C.byref(view), C.byref(post), C.c_void_p(image.data_ptr()),
+                                                   None if accum is None else C.c_void_p(accum.data_ptr()),
+                                                   None if stats is None else C.byref(stats), stream))
+
     def render_frame(self, view, post, accum=None, want_raw=False, want_counts=False, want_stats=False):
         """Convenience path for tests: allocates device buffers with torch, returns numpy arrays."""
         import torch

@@ -308,3 +308,28 @@ def test_errors_are_reported_not_faked(built_lib):
     with pytest.raises(abi.SrfError) as e:
         r.render_frame(sc["view"], abi.default_post())
     assert e.value.status == abi.ERR_ARG
+
+
+def test_scatter_output_equals_compact_output(built_lib):
+    """srf_render_frame_scatter: three shards write straight into one whole-image buffer; byte-equal to the
+    single-shard frame, pixels of other shards untouched by each call."""
+    import torch
+    sc = small_scene(kind="net", width=24, height=21)
+    r = make_renderer(sc)
+    post = abi.default_post()
+    whole = r.render_frame(sc["view"], post)["out"]
+    dev = torch.device("cuda", 0)
+    image = torch.full((21 * 24, 4), -7.0, dtype=torch.float32, device=dev)
+    for rank in range(3):
+        v = abi.View.from_buffer_copy(sc["view"])
+        v.shard_count, v.shard_rank, v.shard_rows = 3, rank, 4
+        accum = torch.zeros((r.n_rays(v), 4), dtype=torch.float32, device=dev)
+        before = image.clone()
+        r.render_frame_scatter_device(v, post, image, accum)
+        torch.cuda.synchronize()
+        rows = [y for y in range(21) if (y // 4) % 3 == rank]
+        mask = torch.zeros(21, dtype=torch.bool)
+        mask[rows] = True
+        mask = mask.repeat_interleave(24).to(dev)
+        assert torch.equal(image[~mask], before[~mask])
+    assert np.array_equal(image.cpu().numpy().view(np.uint32), whole.view(np.uint32))
