@@ -52,6 +52,9 @@ struct srf_ctx {
     float* partial_b = nullptr;
     float* mean = nullptr;
     uint8_t* bits = nullptr;
+    uint32_t* skip_shell = nullptr;          // summaries of the bitfield for the sampler (see march_ray)
+    uint32_t* skip_yz = nullptr;
+    bool skip_capable = false;
     __half* table = nullptr;
     __half* w_density = nullptr;
     __half* w_rgb = nullptr;
@@ -424,6 +427,21 @@ srf_status srf_create(const srf_config_t* cfg, int device, srf_ctx** out) {
     CK_CREATE(cudaMemset(ctx->grid, 0, total * sizeof(float)));
     CK_CREATE(cudaMemset(ctx->bits, 0, total / 8));
     CK_CREATE(cudaMemset(ctx->mean, 0, sizeof(float)));
+    // staged empty-space tests apply to the configuration every shipped config uses: sinusoidal ("ERP") warp,
+    // one cascade, grid laid out in warped space
+    ctx->skip_capable = cfg->use_grid && cfg->num_cascades == 1 &&
+                        (cfg->warping_type == SRF_WARP_ERP || cfg->warping_type == SRF_WARP_SINUSOIDAL) &&
+                        (cfg->grid_distribution_type == SRF_GRID_WARPED_EXP || cfg->grid_distribution_type == SRF_GRID_WARPED_RECIPROCAL);
+    if (const char* e = getenv("SRF_B200_SKIP_TABLES")) if (std::string(e) == "0") ctx->skip_capable = false;
+    if (ctx->skip_capable) {
+        const size_t N = cfg->grid_size;
+        CK_CREATE(cudaMalloc((void**)&ctx->skip_shell, ((N + 31) / 32) * sizeof(uint32_t)));
+        CK_CREATE(cudaMalloc((void**)&ctx->skip_yz, ((N * N + 31) / 32) * sizeof(uint32_t)));
+        CK_CREATE(cudaMemset(ctx->skip_shell, 0, ((N + 31) / 32) * sizeof(uint32_t)));
+        CK_CREATE(cudaMemset(ctx->skip_yz, 0, ((N * N + 31) / 32) * sizeof(uint32_t)));
+        ctx->g.skip_shell = ctx->skip_shell;
+        ctx->g.skip_yz = ctx->skip_yz;
+    }
     if (cfg->field_type == SRF_FIELD_NETWORK) {
         build_net_meta(*cfg, &ctx->net);
         ctx->n_table_entries = table_entries(ctx->net);
@@ -447,7 +465,7 @@ void srf_destroy(srf_ctx* ctx) {
     if (!ctx) return;
     DeviceGuard guard(ctx->device);
     void* ptrs[] = {ctx->grid, ctx->grid_current, ctx->partial_a, ctx->partial_b, ctx->mean, ctx->bits, ctx->table,
-                    ctx->w_density, ctx->w_rgb, ctx->blobs, ctx->cmap, ctx->d_counters, ctx->ray_dir_t.p, ctx->ray_end.p,
+                    ctx->w_density, ctx->w_rgb, ctx->skip_shell, ctx->skip_yz, ctx->blobs, ctx->cmap, ctx->d_counters, ctx->ray_dir_t.p, ctx->ray_end.p,
                     ctx->counts.p, ctx->offsets.p, ctx->scan_scratch.p, ctx->pos_dt.p, ctx->sample_ray.p, ctx->rgbs.p,
                     ctx->img_out.p, ctx->img_accum.p, ctx->pool_pos.p, ctx->pool_shaded.p, ctx->chunk_ray.p, ctx->chunk_next.p,
                     ctx->ray_head.p, ctx->d_chunk_cursor};
@@ -530,6 +548,7 @@ srf_status srf_upload_bitfield(srf_ctx* ctx, const uint8_t* h, size_t n, void* s
     if (n != (size_t)ctx->g.cells * ctx->g.n_cascades / 8) return fail(ctx, SRF_ERR_ARG, "bitfield size mismatch");
     DeviceGuard guard(ctx->device);
     SRF_CK(ctx, cudaMemcpyAsync(ctx->bits, h, n, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    if (ctx->skip_capable) launch_build_skip_tables(ctx->g, ctx->bits, ctx->skip_shell, ctx->skip_yz, (cudaStream_t)stream);
     SRF_CK(ctx, cudaStreamSynchronize((cudaStream_t)stream));
     return SRF_OK;
 }
@@ -556,6 +575,7 @@ srf_status srf_update_grid_bitfield(srf_ctx* ctx, void* stream) {
     const uint32_t total = ctx->g.cells * ctx->g.n_cascades;
     launch_decay_and_mean(ctx->grid, ctx->grid_current, total, ctx->g.cells, 0.f, 0, ctx->partial_a, ctx->partial_b, ctx->mean, s);
     launch_grid_to_bitfield(ctx->g, ctx->grid, ctx->bits, ctx->mean, ctx->min_optical_thickness, s);
+    if (ctx->skip_capable) launch_build_skip_tables(ctx->g, ctx->bits, ctx->skip_shell, ctx->skip_yz, s);
     SRF_CK(ctx, cudaGetLastError());
     return SRF_OK;
 }
@@ -605,6 +625,7 @@ srf_status srf_refresh_grid(srf_ctx* ctx, uint32_t training_step, void* stream) 
                           ctx->partial_b, ctx->mean, s);
     ++ctx->refresh_step;                                                            // :1060
     launch_grid_to_bitfield(ctx->g, ctx->grid, ctx->bits, ctx->mean, ctx->min_optical_thickness, s);
+    if (ctx->skip_capable) launch_build_skip_tables(ctx->g, ctx->bits, ctx->skip_shell, ctx->skip_yz, s);
     SRF_CK(ctx, cudaGetLastError());
     return SRF_OK;
 }

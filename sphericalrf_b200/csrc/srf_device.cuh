@@ -30,6 +30,9 @@ struct DevCfg {
     // compositing
     float transmittance_keep;                // 1 - transmittance_threshold
     int density_activation, rgb_activation, train_in_linear_color, field_type;
+    // exact empty-space tests in front of the full lookup (sinusoidal warp, one cascade): see march_ray
+    const uint32_t* skip_shell;              // bit z: some occupied cell has radial index z
+    const uint32_t* skip_yz;                 // bit z*N + y: some occupied cell has radial index z and latitude index y
 };
 
 // Per-call view constants.
@@ -385,13 +388,47 @@ __device__ __forceinline__ uint32_t march_ray(const DevCfg& g, const uint8_t* __
         const V3 pos = mk3(fmaf(d.x, t, o.x), fmaf(d.y, t, o.y), fmaf(d.z, t, o.z));
         if (!box_contains(g, pos)) { end = RAY_END_EXIT; ++ordinal; break; }
         const float dt = calc_dt(g, t);
-        const V3 w = warp_position(g, pos);
+        V3 w;
         bool occ = true;
         uint32_t idx = 0;
-        if (g.use_grid) {
-            const uint32_t level = level_from_pos(g, pos, w);
-            idx = cascaded_grid_idx_at(g, pos, w, level) + level * g.cells;
-            occ = (__ldg(bits + (idx >> 3)) >> (idx & 7u)) & 1u;
+        if (g.skip_shell) {
+            // Staged evaluation of warp_sinusoidal + cascaded_grid_idx_at for one cascade: the radial cell
+            // index needs only |p|, the latitude index only asin; a 1-D and a 2-D summary of the bitfield
+            // tell whether any occupied cell has these indices.  Every expression is the one the full path
+            // evaluates, so the decision (and the sample, when there is one) is bit-identical to it; the
+            // atan2 / cos / fp64 part -- most of a step's cost -- runs only where it can matter.
+            const uint32_t N = g.grid_size;
+            const float fn = (float)N, s1 = 1.0f;
+            const int hi = (int)N - 1;
+            const V3 p = mk3(pos.x - 0.5f, pos.y - 0.5f, pos.z - 0.5f);
+            float p_mag = srf_norm3f(p.x, p.y, p.z);
+            const float p_mag_inv = 1.f / p_mag;
+            p_mag = (p_mag <= 1.f) ? p_mag : (2.f - p_mag_inv);
+            w.z = p_mag * 0.5f;
+            const uint32_t iz = (uint32_t)min(max(srf_f2i_rz(((w.z - 0.5f) * s1 + 0.5f) * fn), 0), hi);
+            occ = (__ldg(g.skip_shell + (iz >> 5)) >> (iz & 31u)) & 1u;
+            if (occ) {
+                const float phi = srf_asinf(p.z * p_mag_inv);
+                w.y = (float)fma((double)phi, SRF_INV_PI, 0.5);
+                const uint32_t iy = (uint32_t)min(max(srf_f2i_rz(((w.y - 0.5f) * s1 + 0.5f) * fn), 0), hi);
+                const uint32_t yz = iz * N + iy;
+                occ = (__ldg(g.skip_yz + (yz >> 5)) >> (yz & 31u)) & 1u;
+                if (occ) {
+                    const float theta = srf_atan2f(p.y, p.x);
+                    const double tx = (double)(theta * srf_cosf(phi)) * SRF_INV_PI;
+                    w.x = (float)fma(tx, 0.5, 0.5);
+                    const uint32_t ix = (uint32_t)min(max(srf_f2i_rz(((w.x - 0.5f) * s1 + 0.5f) * fn), 0), hi);
+                    idx = morton3D(ix, iy, iz);
+                    occ = (__ldg(bits + (idx >> 3)) >> (idx & 7u)) & 1u;
+                }
+            }
+        } else {
+            w = warp_position(g, pos);
+            if (g.use_grid) {
+                const uint32_t level = level_from_pos(g, pos, w);
+                idx = cascaded_grid_idx_at(g, pos, w, level) + level * g.cells;
+                occ = (__ldg(bits + (idx >> 3)) >> (idx & 7u)) & 1u;
+            }
         }
         if (occ) {
             if (dt == 0.f) { end = RAY_END_STUCK; ++ordinal; break; }

@@ -132,6 +132,9 @@ void launch_decay_and_mean(float* grid, const float* grid_current, uint32_t tota
 void launch_grid_to_bitfield(const DevCfg& g, const float* grid, uint8_t* bits, const float* mean,
                              float min_optical_thickness, cudaStream_t stream);
 
+// Summaries of the bitfield used by the sampler's staged empty-space tests (N/32 and N*N/32 words).
+void launch_build_skip_tables(const DevCfg& g, const uint8_t* bits, uint32_t* shell, uint32_t* yz, cudaStream_t stream);
+
 void launch_eval_math(int op, const float* a, const float* b, float* out, size_t n, cudaStream_t stream);
 
 }  // namespace srf

@@ -202,7 +202,34 @@ __global__ void k_bitfield_max_pool(uint32_t n_elements, uint32_t n_grid_size, c
     next_level[morton3D(x, y, z)] |= bits;
 }
 
+// Summaries of the level-0 bitfield for the sampler's staged empty-space tests: which radial indices z, and
+// which (z, y) index pairs, have at least one occupied cell.
+__global__ void k_build_skip_tables(const uint8_t* __restrict__ bits, uint32_t n_bytes, uint32_t n_grid_size,
+                                    uint32_t* __restrict__ shell, uint32_t* __restrict__ yz) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_bytes) return;
+    const uint32_t b = bits[i];
+    if (!b) return;
+    for (uint32_t j = 0; j < 8; ++j) {
+        if (!((b >> j) & 1u)) continue;
+        const uint32_t m = i * 8u + j;
+        const uint32_t y = morton3D_invert(m >> 1), z = morton3D_invert(m >> 2);
+        const uint32_t sb = 1u << (z & 31u);
+        if (!(shell[z >> 5] & sb)) atomicOr(shell + (z >> 5), sb);          // mostly already set: read first
+        const uint32_t k = z * n_grid_size + y, kb = 1u << (k & 31u);
+        if (!(yz[k >> 5] & kb)) atomicOr(yz + (k >> 5), kb);
+    }
+}
+
 }  // namespace
+
+void launch_build_skip_tables(const DevCfg& g, const uint8_t* bits, uint32_t* shell, uint32_t* yz, cudaStream_t stream) {
+    const uint32_t N = g.grid_size;
+    cudaMemsetAsync(shell, 0, ((N + 31) / 32) * sizeof(uint32_t), stream);
+    cudaMemsetAsync(yz, 0, ((size_t)N * N + 31) / 32 * sizeof(uint32_t), stream);
+    const uint32_t n_bytes = g.cells / 8;
+    k_build_skip_tables<<<(n_bytes + 255) / 256, 256, 0, stream>>>(bits, n_bytes, N, shell, yz);
+}
 
 void launch_refresh_sample(const DevCfg& g, const NetMeta& net, const __half* table, const __half* w_density,
                            const float* grid, float* grid_current, uint32_t n_elements, uint32_t step, RefreshRng rng,

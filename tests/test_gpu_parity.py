@@ -333,3 +333,33 @@ def test_scatter_output_equals_compact_output(built_lib):
         mask = mask.repeat_interleave(24).to(dev)
         assert torch.equal(image[~mask], before[~mask])
     assert np.array_equal(image.cpu().numpy().view(np.uint32), whole.view(np.uint32))
+
+
+@pytest.mark.parametrize("sampling", ["Disparity", "Original"])
+@pytest.mark.parametrize("fill", [0.002, 0.05])
+def test_staged_empty_space_tests_change_nothing(built_lib, oracle_mod, monkeypatch, sampling, fill):
+    """The sampler's 1-D / 2-D summaries of the bitfield only skip work: on a sparse random bitfield the sample
+    list is the oracle's, and the one a context built without the summaries produces."""
+    from sphericalrf_b200.testbed import Renderer
+    sc = small_scene(kind="blobs", sampling=sampling, radius=0.5 if sampling == "Disparity" else 4.0, grid_size=64)
+    rng = np.random.Generator(np.random.PCG64(11))
+    n_cells = 64 ** 3
+    bits = np.packbits(rng.random(n_cells) < fill, bitorder="little")
+    view = sc["view"]
+    outs = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("SRF_B200_SKIP_TABLES", flag)
+        r = Renderer(sc["cfg"], 0)
+        r.upload_blobs(sc["blobs"], sc["color_map"])
+        r.upload_bitfield(bits)
+        outs.append(r.dump_samples(view, 0, r.n_rays(view), 1 << 22))
+        frame = r.render_frame(view, abi.default_post())["out"]
+        outs[-1] = outs[-1] + (frame,)
+    for a, b in zip(outs[0], outs[1]):
+        assert np.array_equal(a.view(np.uint32) if a.dtype == np.float32 else a, b.view(np.uint32) if b.dtype == np.float32 else b)
+    orc = make_oracle(oracle_mod, sc, bits)
+    oc, opd, oo, ocell, _ = orc.march(view, 0, orc.n_rays(view), 1 << 22)
+    gc, gpd, go, gcell, _ = outs[0]
+    assert np.array_equal(oc, gc) and np.array_equal(oo, go) and np.array_equal(ocell, gcell)
+    assert _bits_equal(opd, gpd)
+    assert oc.sum() > 0
