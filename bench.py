@@ -192,6 +192,12 @@ def run_ours(args):
     n_views = world                                  # frames per step
 
     sc = build_scene()
+    if world > 1:
+        # replication at load: rank 0's parameters, grid and scene arrays go to every rank (NCCL broadcast)
+        from sphericalrf_b200.sharding import broadcast_arrays
+        import numpy as np
+        names = [k for k, v in sc.items() if isinstance(v, np.ndarray)]
+        sc.update(broadcast_arrays({k: sc[k] for k in names} if rank == 0 else None, src=0, device=dev))
     cfg = sc["cfg"]
     r = Renderer(cfg, local_rank)
     upload_scene(r, sc)

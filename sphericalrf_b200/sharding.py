@@ -92,3 +92,37 @@ class PeerImage:
 
     def barrier(self):
         self.handle.barrier()
+
+
+def broadcast_arrays(arrays, src: int = 0, device="cpu", group=None):
+    """Replication at load time: rank `src` holds a dict name -> numpy array (hash table, MLP weights, density
+    grid, ...); every rank returns the same dict.  One broadcast of the directory (names, dtypes, shapes)
+    and one per array; other ranks pass None."""
+    import numpy as np
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return arrays
+    rank = dist.get_rank(group)
+    directory = [None]
+    if rank == src:
+        directory = [[(k, str(np.asarray(v).dtype), tuple(np.asarray(v).shape)) for k, v in arrays.items()]]
+    dist.broadcast_object_list(directory, src=src, group=group)
+    out = {}
+    for name, dtype, shape in directory[0]:
+        nbytes = int(np.prod(shape, dtype=np.int64)) * np.dtype(dtype).itemsize
+        if rank == src:
+            t = torch.from_numpy(np.ascontiguousarray(arrays[name]).reshape(-1).view(np.uint8).copy()).to(device)
+        else:
+            t = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        dist.broadcast(t, src=src, group=group)
+        out[name] = t.cpu().numpy().view(np.dtype(dtype)).reshape(shape)
+    return out
+
+
+def reduce_counters(stats: dict, dst: int = 0, device="cpu", group=None):
+    """Sum of per-rank frame counters (rays, march steps, samples, ...) on rank `dst`; other ranks get None."""
+    keys = sorted(k for k, v in stats.items() if isinstance(v, int))
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return {k: stats[k] for k in keys}
+    t = torch.tensor([stats[k] for k in keys], dtype=torch.int64, device=device)
+    dist.reduce(t, dst=dst, op=dist.ReduceOp.SUM, group=group)
+    return dict(zip(keys, t.tolist())) if dist.get_rank(group) == dst else None

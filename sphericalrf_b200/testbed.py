@@ -275,6 +275,11 @@ class Testbed:
         p = Path(config_path)
         if not str(config_path) or not p.exists():
             raise RuntimeError("The model config must exist.")
+        if p.suffix.lower() == ".msgpack":
+            from .snapshot import _msgpack
+            with open(p, "rb") as f:
+                self.load_model_config_dict(_msgpack().unpackb(f.read(), raw=False, strict_map_key=False))
+            return
         if p.suffix.lower() != ".json":
             raise RuntimeError("The model config must be a .json or .msgpack file.")
         with open(p) as f:
@@ -298,6 +303,20 @@ class Testbed:
         self.renderer.update_grid_bitfield()
         self.scene_scale = float(scene_scale)
         self.scene_offset = np.asarray(scene_offset, np.float32)
+
+    def load_snapshot(self, snapshot_path: str):
+        """Testbed::load_snapshot (internal/testbed.cu:151-171): configuration, scene scale and offset, density
+        grid (+ update_grid_bitfield) and network parameters from one .msgpack file."""
+        from . import snapshot
+        self.load_model_config(snapshot_path)
+        if "snapshot" not in self.model_config:
+            raise RuntimeError("ERROR in loading snapshot.")
+        snap = snapshot.read_snapshot(snapshot_path)
+        want = snapshot.table_entries(self.cfg)
+        if snap["hash_table"].size != want:
+            raise RuntimeError(f"snapshot holds {snap['hash_table'].size} hash-grid parameters, the configuration needs {want}")
+        self.load_parameters(snap["hash_table"], snap["density_mlp"], snap["rgb_mlp"], snap["density_grid"],
+                             snap["scene_scale"], snap["scene_offset"])
 
     # -- camera (internal/testbed.h:73-89, internal/utils/common_device.h:105-141) --
     @property

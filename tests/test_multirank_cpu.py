@@ -57,3 +57,35 @@ def test_two_rank_gather_equals_whole_frame(tmp_path, oracle_mod):
         v.spp_index = k
         whole = orc.render_frame(v, abi.default_post())["out"]
         assert got[k].tobytes() == whole.tobytes()
+
+
+def _replicate_worker(rank, world, port, tmp):
+    sys.path.insert(0, str(ROOT))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from sphericalrf_b200.sharding import broadcast_arrays, reduce_counters
+    arrays = None
+    if rank == 0:
+        rng = np.random.Generator(np.random.PCG64(5))
+        arrays = {"hash_table": rng.standard_normal(1000).astype(np.float16), "density_grid": rng.random((8, 8, 8)).astype(np.float32),
+                  "bitfield": rng.integers(0, 256, 64, dtype=np.uint8)}
+    got = broadcast_arrays(arrays, src=0)
+    np.savez(os.path.join(tmp, f"rank{rank}.npz"), **got)
+    total = reduce_counters({"n_rays": 10 + rank, "n_samples": 1000 * (rank + 1), "ms": 1.5}, dst=0)
+    if rank == 0:
+        assert total == {"n_rays": 21, "n_samples": 3000}
+    else:
+        assert total is None
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_load_time_replication_and_counter_reduction(tmp_path):
+    import socket
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    mp.spawn(_replicate_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    a, b = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
+    assert sorted(a.files) == sorted(b.files) == ["bitfield", "density_grid", "hash_table"]
+    for k in a.files:
+        assert a[k].dtype == b[k].dtype and a[k].shape == b[k].shape and a[k].tobytes() == b[k].tobytes()
+    assert a["density_grid"].shape == (8, 8, 8) and a["hash_table"].dtype == np.float16
