@@ -234,6 +234,49 @@ srf_status srf_volume_rendering(srf_ctx* ctx, const srf_view_t* view, const uint
                                 uint64_t n_rays, const float* d_coords, const uint16_t* d_rgbsigma,
                                 float* d_rgba, uint32_t* d_n_composited, void* stream);
 
+/* ---- training-side sampler ---------------------------------------------------------------- */
+
+/* The Dataset fields the sampler's training-side kernels read (OccupancySampler::init and
+   sample_coords_from_dataset, internal/sampler/occupancy_sampler.cu:946-978,1090-1143).  All pointers are
+   device pointers and have the reference's buffer layouts, so its own GPUMemory buffers can be passed as
+   they are. */
+typedef struct srf_train_views_t {
+    uint32_t n_images;
+    int32_t  width, height;                 /* image_resolution */
+    float    focal_length[2];               /* in pixels */
+    float    principal_point[2];            /* relative */
+    const float*    d_xforms;               /* n_images x 12 floats: 3x4 camera matrices, column-major
+                                               (Eigen::Matrix<float,3,4>'s default storage) */
+    const uint16_t* d_images;               /* fp16 rgba, n_images * height * width * 4 (may be NULL for srf_sampler_init) */
+    const uint16_t* d_sampling_probability; /* fp16, n_images * height * width; NULL = every pixel eligible */
+} srf_train_views_t;
+
+/* OccupancySampler::init (occupancy_sampler.cu:946-978): restarts the refresh counter and RNG stream (as
+   srf_refresh_reset) and initialises the density grid: with a grid, `init_grid_with_mask` and the NGP warp,
+   mark_untrained_density_grid (:12-102) writes 0 into cells some training view sees and -1 into the others;
+   in every other case the grid is cleared.  The bitfield is not touched (the reference rebuilds it at the next
+   refresh).  `views` may be NULL when no mask is asked for. */
+srf_status srf_sampler_init(srf_ctx* ctx, const srf_train_views_t* views, int init_grid_with_mask,
+                            uint64_t rng_seed, void* stream);
+
+/* OccupancySampler::sample_coords_from_dataset / generate_training_samples_nerf (occupancy_sampler.cu:513-689,
+   1090-1143): for each of n_rays training rays pick image and pixel (PCG32 state `rng_state`/`rng_inc`, stream
+   position i*8 for ray i), march the ray and emit its occupied samples (at most maximum_marching_steps) as
+   Coordinate records into one variable-length buffer.
+     d_ray_counter[1]      rays kept                    d_numsteps_counter[1]  samples of all rays with samples,
+     d_rays[kept*6]        origin, direction                                   including rays that found no room
+     d_rays_rgba[kept*4]   the pixel's rgba             d_numsteps[kept*2]     per kept ray: sample count, base
+     d_coords[n_coords*7]  samples, ray after ray
+   A ray is kept when it has samples and base + count <= n_coords, where base is the number of samples of all
+   earlier rays (kept or not).  The reference takes base and the ray slot from atomic counters, so its order
+   depends on scheduling; this entry returns the order of a serial execution (ray 0, 1, 2, ...), reproducibly.
+   The counters are set, not added to.  Totals must stay below 2^32. */
+srf_status srf_sample_training_rays(srf_ctx* ctx, const srf_train_views_t* views, uint32_t n_rays,
+                                    uint32_t n_rays_shift, uint32_t n_coords, uint64_t rng_state, uint64_t rng_inc,
+                                    int snap_to_pixel_centers, uint32_t* d_ray_counter, uint32_t* d_numsteps_counter,
+                                    float* d_rays, float* d_rays_rgba, uint32_t* d_numsteps, float* d_coords,
+                                    void* stream);
+
 /* ---- whole frames ------------------------------------------------------------------------ */
 
 /* Testbed::render_frame (internal/testbed.cu:479-606) for one sample-per-pixel pass of one

@@ -802,6 +802,143 @@ int srfo_warp_position(const srf_config_t* cfg, const float* pos, float* out, si
 
 uint64_t srfo_shard_ray_count(const srf_view_t* view) { return shard_rows_total(*view) * view->width; }
 
+/* mark_untrained_density_grid (occupancy_sampler.cu:12-102).  views holds HOST pointers here.
+   grid_out: cells * cascades floats: 0 where some training view sees the cell, -1 elsewhere. */
+int srfo_mark_untrained(const srf_config_t* cfg, const srf_train_views_t* tv, float* grid_out) {
+    const Cfg g = resolve(cfg);
+    const uint32_t N = cfg->grid_size, nc = cfg->num_cascades;
+    const int64_t n = (int64_t)g.cells * nc;
+    const float fn = (float)N, fa = (float)cfg->aabb_scale;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) {
+        const uint32_t level = (uint32_t)(i / g.cells), pos_idx = (uint32_t)(i % g.cells);   /* :29-30 */
+        const uint32_t x = morton3D_invert(pos_idx >> 0), y = morton3D_invert(pos_idx >> 1), z = morton3D_invert(pos_idx >> 2);
+        V3 pos = v3(((float)x + 0.5f) / fn - 0.5f, ((float)y + 0.5f) / fn - 0.5f, ((float)z + 0.5f) / fn - 0.5f);   /* :37 */
+        const int down = -(int)(nc - level - 1);
+        const float fl = (float)(nc - level);
+        float s;
+        switch (cfg->grid_distribution_type) {
+        case SRF_GRID_WARPED_EXP:                                    /* :40-45 */
+            s = scalbnf(1.0f, down);
+            pos = v3(pos.x * s + 0.5f, pos.y * s + 0.5f, pos.z * s + 0.5f);
+            pos = unwarp_position(g, pos);
+            break;
+        case SRF_GRID_WARPED_RECIPROCAL:                             /* :46-51 */
+            pos = v3(pos.x / fl + 0.5f, pos.y / fl + 0.5f, pos.z / fl + 0.5f);
+            pos = unwarp_position(g, pos);
+            break;
+        case SRF_GRID_METRIC_EXP:                                    /* :52-54, falls through (no break) */
+            s = scalbnf(fa, down);
+            pos = v3(pos.x * s + 0.5f, pos.y * s + 0.5f, pos.z * s + 0.5f);
+            /* fallthrough */
+        case SRF_GRID_METRIC_RECIPROCAL:                             /* :55-57 */
+            s = fa / fl;
+            pos = v3(pos.x * s + 0.5f, pos.y * s + 0.5f, pos.z * s + 0.5f);
+            break;
+        default: break;
+        }
+        const float half_resx = (float)tv->width * 0.5f, half_resy = (float)tv->height * 0.5f;   /* :61-62 */
+        float voxel_radius = 0.5f * 1.73205080757f * fa / fn;        /* :63 */
+        if (cfg->grid_distribution_type == SRF_GRID_WARPED_EXP || cfg->grid_distribution_type == SRF_GRID_METRIC_EXP)
+            voxel_radius *= scalbnf(1.0f, down);                     /* :66-69,74-76 */
+        else
+            voxel_radius /= fl;                                      /* :70-73,77-79 */
+        bool seen = false;
+        for (uint32_t j = 0; j < tv->n_images && !seen; ++j) {       /* :84-99 */
+            const float* m = tv->d_xforms + (size_t)j * 12;          /* column-major 3x4 */
+            const V3 ploc = v3(pos.x - m[9], pos.y - m[10], pos.z - m[11]);
+            const float cx = fmaf(ploc.z, m[2], fmaf(ploc.y, m[1], ploc.x * m[0]));   /* [E] dot */
+            const float cy = fmaf(ploc.z, m[5], fmaf(ploc.y, m[4], ploc.x * m[3]));
+            const float cz = fmaf(ploc.z, m[8], fmaf(ploc.y, m[7], ploc.x * m[6]));
+            if (cz > 0.f)
+                seen = fabsf(cx) - voxel_radius < cz / tv->focal_length[0] * half_resx &&
+                       fabsf(cy) - voxel_radius < cz / tv->focal_length[1] * half_resy;
+        }
+        grid_out[i] = seen ? 0.f : -1.f;                             /* :101 */
+    }
+    return 0;
+}
+
+/* generate_training_samples_nerf (occupancy_sampler.cu:513-689) executed serially, ray 0 first: the atomic
+   counters of the reference then hand out bases and ray slots in ray order.  views holds HOST pointers.
+   Output capacities: rays n_rays*6, rgba n_rays*4, numsteps n_rays*2, coords n_coords*7. */
+int srfo_sample_training_rays(const srf_config_t* cfg, const srf_train_views_t* tv, const uint8_t* bitfield,
+                              uint32_t n_rays, uint32_t n_rays_shift, uint32_t n_coords, const srfo_rng_t* rng0,
+                              int snap, uint32_t* ray_counter, uint32_t* numsteps_counter, float* rays_out,
+                              float* rays_rgba, uint32_t* numsteps_out, float* coords_out) {
+    const Cfg g = resolve(cfg);
+    const uint32_t n_max_steps = cfg->maximum_marching_steps;
+    *ray_counter = 0;
+    *numsteps_counter = 0;
+    const float rw = (float)tv->width, rh = (float)tv->height;
+    for (uint32_t i = 0; i < n_rays; ++i) {
+        const uint32_t img = (((n_rays_shift + i) * tv->n_images) / n_rays) % tv->n_images;   /* :544 */
+        srfo_rng_t rng = *rng0;
+        pcg_advance(rng, (uint64_t)(uint32_t)(i * 8u));              /* :551 */
+        float xx = pcg_next_float(rng);                              /* :552, random_val.cuh:21-23 */
+        float yy = pcg_next_float(rng);
+        if (snap) {                                                  /* :553-555 */
+            xx = ((float)std::min(std::max(srf_f2i_rz(xx * rw), 0), tv->width - 1) + 0.5f) / rw;
+            yy = ((float)std::min(std::max(srf_f2i_rz(yy * rh), 0), tv->height - 1) + 0.5f) / rh;
+        }
+        const int px = std::max(std::min(srf_f2i_rz(xx * rw), tv->width - 1), 0);   /* common_device.h:191-197 */
+        const int py = std::max(std::min(srf_f2i_rz(yy * rh), tv->height - 1), 0);
+        const uint64_t pixel = (uint64_t)(int64_t)(px + py * tv->width) + (uint64_t)img * (uint64_t)tv->width * (uint64_t)tv->height;
+        if (tv->d_sampling_probability && h2f(tv->d_sampling_probability[pixel]) <= 0.f) continue;   /* :570-571 */
+        const float* m = tv->d_xforms + (size_t)img * 12;
+        const V3 o = v3(m[9], m[10], m[11]);                         /* :576 */
+        const float dx = (xx - tv->principal_point[0]) * rw / tv->focal_length[0];   /* :577-581 */
+        const float dy = (yy - tv->principal_point[1]) * rh / tv->focal_length[1];
+        const float rx = fmaf(m[6], 1.0f, fmaf(m[3], dy, m[0] * dx));                /* :582 [E] */
+        const float ry = fmaf(m[7], 1.0f, fmaf(m[4], dy, m[1] * dx));
+        const float rz = fmaf(m[8], 1.0f, fmaf(m[5], dy, m[2] * dx));
+        const float nrm = srf_norm3f(rx, ry, rz);
+        const V3 d = v3(rx / nrm, ry / nrm, rz / nrm);
+        const float t0 = fmaxf(box_ray_tmin(g.box, o, d), cfg->near_distance);       /* :585-587 */
+        const float startt = fmaf(pcg_next_float(rng), calc_dt(g, t0), t0);          /* :596-597 */
+        /* the march of :602-628 (count) and :652-688 (emit): `emit` false = count only */
+        auto march = [&](uint32_t limit, float* coords) {
+            uint32_t j = 0;
+            float t = startt;
+            const V3 wd = v3((d.x + 1.f) * 0.5f, (d.y + 1.f) * 0.5f, (d.z + 1.f) * 0.5f);   /* warp_direction */
+            for (uint32_t it = 0; it < (1u << 24) && j < limit; ++it) {
+                const V3 pos = v3(fmaf(d.x, t, o.x), fmaf(d.y, t, o.y), fmaf(d.z, t, o.z));
+                if (!box_contains(g.box, pos)) break;
+                const float dt = calc_dt(g, t);
+                const V3 w = warp_position(g, pos);
+                bool occ = true;
+                if (cfg->use_grid) {
+                    const uint32_t level = level_from_pos(g, pos, w);
+                    occ = occupied_at(g, bitfield, cascaded_grid_idx_at(g, pos, w, level), level);
+                }
+                if (occ) {
+                    if (coords) {
+                        float* c = coords + (size_t)j * 7;
+                        c[0] = w.x; c[1] = w.y; c[2] = w.z; c[3] = dt; c[4] = wd.x; c[5] = wd.y; c[6] = wd.z;
+                    }
+                    ++j;
+                }
+                t += dt;
+                if (dt == 0.f) break;
+            }
+            return j;
+        };
+        const uint32_t numsteps = march(n_max_steps, nullptr);
+        if (numsteps == 0) continue;                                 /* :630-632 */
+        const uint32_t base = *numsteps_counter;                     /* :634 atomicAdd */
+        *numsteps_counter += numsteps;
+        if ((uint64_t)base + numsteps > n_coords) continue;          /* :635-637 */
+        const uint32_t ray_idx = (*ray_counter)++;                   /* :642 */
+        float* ro = rays_out + (size_t)ray_idx * 6;
+        ro[0] = o.x; ro[1] = o.y; ro[2] = o.z; ro[3] = d.x; ro[4] = d.y; ro[5] = d.z;
+        for (int k = 0; k < 4; ++k) rays_rgba[(size_t)ray_idx * 4 + k] = h2f(tv->d_images[pixel * 4 + k]);   /* :645 */
+        numsteps_out[ray_idx * 2 + 0] = numsteps;
+        numsteps_out[ray_idx * 2 + 1] = base;
+        march(numsteps, coords_out + (size_t)base * 7);
+    }
+    return 0;
+}
+
 /* OccupancySampler::generate_rays_from_camera_matrix (occupancy_sampler.cu:1145-1188). */
 int srfo_generate_rays(const srf_config_t* cfg, const srf_view_t* view, const uint8_t* bitfield,
                        float* dir, float* t_out, uint8_t* alive, uint32_t* pixel) {

@@ -46,6 +46,13 @@ int srfo_march(const srf_config_t* cfg, const srf_view_t* view, const uint8_t* b
                float* pos_dt, uint32_t* ordinal, uint32_t* cell, uint64_t* n_total,
                uint64_t* n_march_steps);
 
+/* Training-side sampler; `views` carries HOST pointers in the oracle. */
+int srfo_mark_untrained(const srf_config_t* cfg, const srf_train_views_t* views, float* grid_out);
+int srfo_sample_training_rays(const srf_config_t* cfg, const srf_train_views_t* views, const uint8_t* bitfield,
+                              uint32_t n_rays, uint32_t n_rays_shift, uint32_t n_coords, const srfo_rng_t* rng,
+                              int snap_to_pixel_centers, uint32_t* ray_counter, uint32_t* numsteps_counter,
+                              float* rays_out, float* rays_rgba, uint32_t* numsteps_out, float* coords_out);
+
 int srfo_network_inference(const srf_config_t* cfg, const srfo_model_t* model, const float* coords,
                            uint64_t n, uint16_t* rgbsigma);
 int srfo_network_density(const srf_config_t* cfg, const srfo_model_t* model, const float* positions,

@@ -172,3 +172,43 @@ def hashgrid_layout(cfg):
 
 def num_threads():
     return int(lib().srfo_num_threads())
+
+
+def _host_views(views: dict):
+    """srf_train_views_t with host pointers from dict(n_images, width, height, focal_length, principal_point,
+    xforms (n,12) float32 column-major, images (n,H,W,4) float16 or None, sampling_probability (n,H,W) float16 or
+    None).  Returns (struct, keep-alive list)."""
+    keep = [np.ascontiguousarray(views["xforms"], np.float32),
+            None if views.get("images") is None else np.ascontiguousarray(views["images"], np.float16),
+            None if views.get("sampling_probability") is None else np.ascontiguousarray(views["sampling_probability"], np.float16)]
+    tv = abi.TrainViews()
+    tv.n_images, tv.width, tv.height = int(views["n_images"]), int(views["width"]), int(views["height"])
+    tv.focal_length[:] = [float(x) for x in views["focal_length"]]
+    tv.principal_point[:] = [float(x) for x in views["principal_point"]]
+    tv.d_xforms = keep[0].ctypes.data
+    tv.d_images = None if keep[1] is None else keep[1].ctypes.data
+    tv.d_sampling_probability = None if keep[2] is None else keep[2].ctypes.data
+    return tv, keep
+
+
+def mark_untrained(cfg: abi.Config, views: dict):
+    tv, keep = _host_views(views)
+    grid = np.zeros(cfg.grid_size ** 3 * cfg.num_cascades, np.float32)
+    rc = lib().srfo_mark_untrained(C.byref(cfg), C.byref(tv), _p(grid))
+    assert rc == 0
+    return grid
+
+
+def sample_training_rays(cfg: abi.Config, views: dict, bitfield, n_rays, n_rays_shift, n_coords, rng: Rng, snap=True):
+    """Returns dict(n_rays, n_samples_total, rays (k,6), rgba (k,4), numsteps (k,2), coords (n_coords,7))."""
+    tv, keep = _host_views(views)
+    bits = None if bitfield is None else np.ascontiguousarray(bitfield, np.uint8)
+    rc_, nc_ = C.c_uint32(0), C.c_uint32(0)
+    rays = np.zeros((n_rays, 6), np.float32); rgba = np.zeros((n_rays, 4), np.float32)
+    numsteps = np.zeros((n_rays, 2), np.uint32); coords = np.zeros((n_coords, 7), np.float32)
+    rc = lib().srfo_sample_training_rays(C.byref(cfg), C.byref(tv), _p(bits), C.c_uint32(n_rays), C.c_uint32(n_rays_shift),
+                                         C.c_uint32(n_coords), C.byref(rng), C.c_int(1 if snap else 0), C.byref(rc_),
+                                         C.byref(nc_), _p(rays), _p(rgba), _p(numsteps), _p(coords))
+    assert rc == 0
+    k = rc_.value
+    return dict(n_rays=k, n_samples_total=nc_.value, rays=rays[:k], rgba=rgba[:k], numsteps=numsteps[:k], coords=coords)

@@ -61,6 +61,14 @@ class Post(C.Structure):
     ]
 
 
+class TrainViews(C.Structure):
+    _fields_ = [
+        ("n_images", C.c_uint32), ("width", C.c_int32), ("height", C.c_int32),
+        ("focal_length", C.c_float * 2), ("principal_point", C.c_float * 2),
+        ("d_xforms", C.c_void_p), ("d_images", C.c_void_p), ("d_sampling_probability", C.c_void_p),
+    ]
+
+
 class FrameStats(C.Structure):
     _fields_ = [
         ("n_rays", C.c_uint64), ("n_rays_alive", C.c_uint64), ("n_march_steps", C.c_uint64),
@@ -174,6 +182,9 @@ SYMBOLS = {
     "srf_dump_samples": (C.c_int, [_ctx, _P(View), C.c_uint64, C.c_uint64, C.c_uint64, _vp, _vp, _vp, _vp,
                                    _P(C.c_uint64)]),
     "srf_reserve": (C.c_int, [_ctx, C.c_uint64]),
+    "srf_sampler_init": (C.c_int, [_ctx, _P(TrainViews), C.c_int, C.c_uint64, _vp]),
+    "srf_sample_training_rays": (C.c_int, [_ctx, _P(TrainViews), C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint64, C.c_uint64,
+                                           C.c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "srf_sample_offsets_static": (C.c_int, [C.c_int, _vp, C.c_uint64, _vp, _vp, C.c_char_p, C.c_size_t]),
     "srf_eval_math": (C.c_int, [C.c_int, C.c_int, _vp, _vp, _vp, C.c_size_t]),
 }

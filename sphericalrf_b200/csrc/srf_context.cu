@@ -64,6 +64,7 @@ struct srf_ctx {
     uint32_t n_blobs = 0;
 
     // per-frame scratch
+    DevBuf train_flags, train_rank;
     DevBuf ray_dir_t, ray_end, counts, offsets, scan_scratch;
     DevBuf pos_dt, sample_ray, rgbs;
     DevBuf pool_pos, pool_shaded, chunk_ray, chunk_next, ray_head;   // paged frame path
@@ -465,7 +466,7 @@ void srf_destroy(srf_ctx* ctx) {
     if (!ctx) return;
     DeviceGuard guard(ctx->device);
     void* ptrs[] = {ctx->grid, ctx->grid_current, ctx->partial_a, ctx->partial_b, ctx->mean, ctx->bits, ctx->table,
-                    ctx->w_density, ctx->w_rgb, ctx->skip_shell, ctx->skip_yz, ctx->blobs, ctx->cmap, ctx->d_counters, ctx->ray_dir_t.p, ctx->ray_end.p,
+                    ctx->w_density, ctx->w_rgb, ctx->skip_shell, ctx->skip_yz, ctx->train_flags.p, ctx->train_rank.p, ctx->blobs, ctx->cmap, ctx->d_counters, ctx->ray_dir_t.p, ctx->ray_end.p,
                     ctx->counts.p, ctx->offsets.p, ctx->scan_scratch.p, ctx->pos_dt.p, ctx->sample_ray.p, ctx->rgbs.p,
                     ctx->img_out.p, ctx->img_accum.p, ctx->pool_pos.p, ctx->pool_shaded.p, ctx->chunk_ray.p, ctx->chunk_next.p,
                     ctx->ray_head.p, ctx->d_chunk_cursor};
@@ -626,6 +627,73 @@ srf_status srf_refresh_grid(srf_ctx* ctx, uint32_t training_step, void* stream) 
     ++ctx->refresh_step;                                                            // :1060
     launch_grid_to_bitfield(ctx->g, ctx->grid, ctx->bits, ctx->mean, ctx->min_optical_thickness, s);
     if (ctx->skip_capable) launch_build_skip_tables(ctx->g, ctx->bits, ctx->skip_shell, ctx->skip_yz, s);
+    SRF_CK(ctx, cudaGetLastError());
+    return SRF_OK;
+}
+
+// ---- training-side sampler -------------------------------------------------------------------------
+
+static srf_status make_train_views(srf_ctx* ctx, const srf_train_views_t* in, bool need_images, TrainViews* tv) {
+    if (!in) return fail(ctx, SRF_ERR_ARG, "training views are required");
+    if (in->n_images == 0 || in->width <= 0 || in->height <= 0) return fail(ctx, SRF_ERR_ARG, "training views: empty image set");
+    if (!(in->focal_length[0] > 0.f) || !(in->focal_length[1] > 0.f)) return fail(ctx, SRF_ERR_ARG, "training views: focal length must be positive");
+    if (!in->d_xforms) return fail(ctx, SRF_ERR_ARG, "training views: camera matrices missing");
+    if (need_images && !in->d_images) return fail(ctx, SRF_ERR_ARG, "training views: images missing");
+    tv->n_images = in->n_images; tv->width = in->width; tv->height = in->height;
+    tv->focal_x = in->focal_length[0]; tv->focal_y = in->focal_length[1];
+    tv->pp_x = in->principal_point[0]; tv->pp_y = in->principal_point[1];
+    tv->xforms = in->d_xforms;
+    tv->images = reinterpret_cast<const __half*>(in->d_images);
+    tv->sampling_probability = reinterpret_cast<const __half*>(in->d_sampling_probability);
+    return SRF_OK;
+}
+
+srf_status srf_sampler_init(srf_ctx* ctx, const srf_train_views_t* views, int init_grid_with_mask, uint64_t rng_seed, void* stream) {
+    if (!ctx) return SRF_ERR_ARG;
+    DeviceGuard guard(ctx->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    srf_refresh_reset(ctx, rng_seed);
+    const size_t total = (size_t)ctx->g.cells * ctx->g.n_cascades;
+    if (ctx->cfg.use_grid && init_grid_with_mask && ctx->cfg.warping_type == SRF_WARP_NGP) {
+        TrainViews tv;
+        srf_status st = make_train_views(ctx, views, false, &tv);
+        if (st != SRF_OK) return st;
+        launch_mark_untrained(ctx->g, ctx->cfg.aabb_scale, tv, ctx->grid, s);
+        SRF_CK(ctx, cudaGetLastError());
+    } else {
+        SRF_CK(ctx, cudaMemsetAsync(ctx->grid, 0, total * sizeof(float), s));
+    }
+    return SRF_OK;
+}
+
+srf_status srf_sample_training_rays(srf_ctx* ctx, const srf_train_views_t* views, uint32_t n_rays, uint32_t n_rays_shift,
+                                    uint32_t n_coords, uint64_t rng_state, uint64_t rng_inc, int snap_to_pixel_centers,
+                                    uint32_t* d_ray_counter, uint32_t* d_numsteps_counter, float* d_rays, float* d_rays_rgba,
+                                    uint32_t* d_numsteps, float* d_coords, void* stream) {
+    if (!ctx || !d_ray_counter || !d_numsteps_counter || !d_rays || !d_rays_rgba || !d_numsteps || !d_coords) return SRF_ERR_ARG;
+    if (n_rays == 0) return fail(ctx, SRF_ERR_ARG, "n_rays must be positive");
+    TrainViews tv;
+    srf_status st = make_train_views(ctx, views, true, &tv);
+    if (st != SRF_OK) return st;
+    DeviceGuard guard(ctx->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    if ((st = ensure(ctx, ctx->counts, (size_t)n_rays * sizeof(uint32_t))) != SRF_OK) return st;
+    if ((st = ensure(ctx, ctx->train_flags, (size_t)n_rays * sizeof(uint32_t))) != SRF_OK) return st;
+    if ((st = ensure(ctx, ctx->offsets, ((size_t)n_rays + 1) * sizeof(uint64_t))) != SRF_OK) return st;
+    if ((st = ensure(ctx, ctx->train_rank, ((size_t)n_rays + 1) * sizeof(uint64_t))) != SRF_OK) return st;
+    if ((st = ensure(ctx, ctx->scan_scratch, scan_scratch_bytes(n_rays))) != SRF_OK) return st;
+    uint32_t* counts = (uint32_t*)ctx->counts.p;
+    uint32_t* flags = (uint32_t*)ctx->train_flags.p;
+    uint64_t* offsets = (uint64_t*)ctx->offsets.p;
+    uint64_t* rank = (uint64_t*)ctx->train_rank.p;
+    const RefreshRng rng = {rng_state, rng_inc};
+    launch_train_count(ctx->g, tv, ctx->bits, n_rays, n_rays_shift, ctx->cfg.maximum_marching_steps, rng, snap_to_pixel_centers,
+                       counts, flags, s);
+    launch_scan(counts, n_rays, offsets, ctx->scan_scratch.p, s);
+    launch_scan(flags, n_rays, rank, ctx->scan_scratch.p, s);
+    SRF_CK(ctx, cudaMemsetAsync(d_ray_counter, 0, sizeof(uint32_t), s));
+    launch_train_emit(ctx->g, tv, ctx->bits, n_rays, n_rays_shift, n_coords, rng, snap_to_pixel_centers, counts, offsets, rank,
+                      d_ray_counter, d_numsteps_counter, d_rays, d_rays_rgba, d_numsteps, d_coords, s);
     SRF_CK(ctx, cudaGetLastError());
     return SRF_OK;
 }

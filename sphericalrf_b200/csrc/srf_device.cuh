@@ -347,6 +347,30 @@ __device__ __forceinline__ uint32_t cascaded_grid_idx_at(const DevCfg& g, const 
     return morton3D((uint32_t)ix, (uint32_t)iy, (uint32_t)iz);
 }
 
+// ---- PCG32 (the generator behind the reference's default_rng_t) ------------------------------------
+struct Pcg { uint64_t state, inc; };
+constexpr uint64_t kPcgMult = 0x5851f42d4c957f2dULL;
+__device__ __forceinline__ uint32_t pcg_next_uint(Pcg& r) {
+    const uint64_t old = r.state;
+    r.state = old * kPcgMult + r.inc;
+    const uint32_t xorshifted = (uint32_t)(((old >> 18u) ^ old) >> 27u);
+    const uint32_t rot = (uint32_t)(old >> 59u);
+    return (xorshifted >> rot) | (xorshifted << ((~rot + 1u) & 31));
+}
+__device__ __forceinline__ float pcg_next_float(Pcg& r) {
+    return __uint_as_float((pcg_next_uint(r) >> 9) | 0x3f800000u) - 1.0f;
+}
+__device__ __forceinline__ void pcg_advance(Pcg& r, uint64_t delta) {
+    uint64_t cur_mult = kPcgMult, cur_plus = r.inc, acc_mult = 1u, acc_plus = 0u;
+    while (delta > 0) {
+        if (delta & 1) { acc_mult *= cur_mult; acc_plus = acc_plus * cur_mult + cur_plus; }
+        cur_plus = (cur_mult + 1) * cur_plus;
+        cur_mult *= cur_mult;
+        delta >>= 1;
+    }
+    r.state = acc_mult * r.state + acc_plus;
+}
+
 // ---- one ray ---------------------------------------------------------------------------------------
 enum RayEnd : uint32_t {
     RAY_END_EXIT = 0,       // left the box
@@ -376,6 +400,60 @@ __device__ __forceinline__ RayInit init_ray(const DevCfg& g, const DevView& v, u
     return r;
 }
 
+// One march step's occupancy lookup: warped position *w, Morton cell index *idx (+ level * cells), and
+// whether the cell's bit is set (warp_position + level_from_pos + density_grid_occupied_at,
+// occupancy_sampler.cu:786-788).  Without a grid every step counts as occupied.  When the lookup says
+// "empty", *w and *idx may be partly unset: callers use them only for occupied steps.
+__device__ __forceinline__ bool grid_lookup(const DevCfg& g, const uint8_t* __restrict__ bits, const V3& pos, V3* w_out,
+                                            uint32_t* idx_out) {
+    V3 w;
+    bool occ = true;
+    uint32_t idx = 0;
+    if (g.skip_shell) {
+        // Staged evaluation of warp_sinusoidal + cascaded_grid_idx_at for one cascade: the radial cell
+        // index needs only |p|, the latitude index only asin; a 1-D and a 2-D summary of the bitfield
+        // tell whether any occupied cell has these indices.  Every expression is the one the full path
+        // evaluates, so the decision (and the sample, when there is one) is bit-identical to it; the
+        // atan2 / cos / fp64 part -- most of a step's cost -- runs only where it can matter.
+        const uint32_t N = g.grid_size;
+        const float fn = (float)N, s1 = 1.0f;
+        const int hi = (int)N - 1;
+        const V3 p = mk3(pos.x - 0.5f, pos.y - 0.5f, pos.z - 0.5f);
+        float p_mag = srf_norm3f(p.x, p.y, p.z);
+        const float p_mag_inv = 1.f / p_mag;
+        p_mag = (p_mag <= 1.f) ? p_mag : (2.f - p_mag_inv);
+        w.z = p_mag * 0.5f;
+        w.x = w.y = 0.f;
+        const uint32_t iz = (uint32_t)min(max(srf_f2i_rz(((w.z - 0.5f) * s1 + 0.5f) * fn), 0), hi);
+        occ = (__ldg(g.skip_shell + (iz >> 5)) >> (iz & 31u)) & 1u;
+        if (occ) {
+            const float phi = srf_asinf(p.z * p_mag_inv);
+            w.y = (float)fma((double)phi, SRF_INV_PI, 0.5);
+            const uint32_t iy = (uint32_t)min(max(srf_f2i_rz(((w.y - 0.5f) * s1 + 0.5f) * fn), 0), hi);
+            const uint32_t yz = iz * N + iy;
+            occ = (__ldg(g.skip_yz + (yz >> 5)) >> (yz & 31u)) & 1u;
+            if (occ) {
+                const float theta = srf_atan2f(p.y, p.x);
+                const double tx = (double)(theta * srf_cosf(phi)) * SRF_INV_PI;
+                w.x = (float)fma(tx, 0.5, 0.5);
+                const uint32_t ix = (uint32_t)min(max(srf_f2i_rz(((w.x - 0.5f) * s1 + 0.5f) * fn), 0), hi);
+                idx = morton3D(ix, iy, iz);
+                occ = (__ldg(bits + (idx >> 3)) >> (idx & 7u)) & 1u;
+            }
+        }
+    } else {
+        w = warp_position(g, pos);
+        if (g.use_grid) {
+            const uint32_t level = level_from_pos(g, pos, w);
+            idx = cascaded_grid_idx_at(g, pos, w, level) + level * g.cells;
+            occ = (__ldg(bits + (idx >> 3)) >> (idx & 7u)) & 1u;
+        }
+    }
+    *w_out = w;
+    *idx_out = idx;
+    return occ;
+}
+
 // The loop shared by advance_pos_nerf (:771-794) and generate_coords_from_rays_regularly_kernel
 // (:829-860), run to the end of the ray.  emit(w, dt, ordinal, cell, t) is called for every occupied
 // step and returns false to stop.  Returns the RayEnd; *n_steps receives the loop iterations.
@@ -389,47 +467,8 @@ __device__ __forceinline__ uint32_t march_ray(const DevCfg& g, const uint8_t* __
         if (!box_contains(g, pos)) { end = RAY_END_EXIT; ++ordinal; break; }
         const float dt = calc_dt(g, t);
         V3 w;
-        bool occ = true;
-        uint32_t idx = 0;
-        if (g.skip_shell) {
-            // Staged evaluation of warp_sinusoidal + cascaded_grid_idx_at for one cascade: the radial cell
-            // index needs only |p|, the latitude index only asin; a 1-D and a 2-D summary of the bitfield
-            // tell whether any occupied cell has these indices.  Every expression is the one the full path
-            // evaluates, so the decision (and the sample, when there is one) is bit-identical to it; the
-            // atan2 / cos / fp64 part -- most of a step's cost -- runs only where it can matter.
-            const uint32_t N = g.grid_size;
-            const float fn = (float)N, s1 = 1.0f;
-            const int hi = (int)N - 1;
-            const V3 p = mk3(pos.x - 0.5f, pos.y - 0.5f, pos.z - 0.5f);
-            float p_mag = srf_norm3f(p.x, p.y, p.z);
-            const float p_mag_inv = 1.f / p_mag;
-            p_mag = (p_mag <= 1.f) ? p_mag : (2.f - p_mag_inv);
-            w.z = p_mag * 0.5f;
-            const uint32_t iz = (uint32_t)min(max(srf_f2i_rz(((w.z - 0.5f) * s1 + 0.5f) * fn), 0), hi);
-            occ = (__ldg(g.skip_shell + (iz >> 5)) >> (iz & 31u)) & 1u;
-            if (occ) {
-                const float phi = srf_asinf(p.z * p_mag_inv);
-                w.y = (float)fma((double)phi, SRF_INV_PI, 0.5);
-                const uint32_t iy = (uint32_t)min(max(srf_f2i_rz(((w.y - 0.5f) * s1 + 0.5f) * fn), 0), hi);
-                const uint32_t yz = iz * N + iy;
-                occ = (__ldg(g.skip_yz + (yz >> 5)) >> (yz & 31u)) & 1u;
-                if (occ) {
-                    const float theta = srf_atan2f(p.y, p.x);
-                    const double tx = (double)(theta * srf_cosf(phi)) * SRF_INV_PI;
-                    w.x = (float)fma(tx, 0.5, 0.5);
-                    const uint32_t ix = (uint32_t)min(max(srf_f2i_rz(((w.x - 0.5f) * s1 + 0.5f) * fn), 0), hi);
-                    idx = morton3D(ix, iy, iz);
-                    occ = (__ldg(bits + (idx >> 3)) >> (idx & 7u)) & 1u;
-                }
-            }
-        } else {
-            w = warp_position(g, pos);
-            if (g.use_grid) {
-                const uint32_t level = level_from_pos(g, pos, w);
-                idx = cascaded_grid_idx_at(g, pos, w, level) + level * g.cells;
-                occ = (__ldg(bits + (idx >> 3)) >> (idx & 7u)) & 1u;
-            }
-        }
+        uint32_t idx;
+        const bool occ = grid_lookup(g, bits, pos, &w, &idx);
         if (occ) {
             if (dt == 0.f) { end = RAY_END_STUCK; ++ordinal; break; }
             if (n >= g.sample_cap) { end = RAY_END_CAP; ++ordinal; break; }

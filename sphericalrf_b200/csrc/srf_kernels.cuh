@@ -132,6 +132,25 @@ void launch_decay_and_mean(float* grid, const float* grid_current, uint32_t tota
 void launch_grid_to_bitfield(const DevCfg& g, const float* grid, uint8_t* bits, const float* mean,
                              float min_optical_thickness, cudaStream_t stream);
 
+// Training views as the training-side kernels read them (device pointers; xforms are 3x4 column-major).
+struct TrainViews {
+    uint32_t n_images;
+    int width, height;
+    float focal_x, focal_y, pp_x, pp_y;
+    const float* xforms;
+    const __half* images;                   // rgba fp16 per pixel
+    const __half* sampling_probability;     // fp16 per pixel, may be null (every pixel eligible)
+};
+// mark_untrained_density_grid: 0 for cells some training view sees, -1 for the others.
+void launch_mark_untrained(const DevCfg& g, uint32_t aabb_scale, const TrainViews& tv, float* grid_out, cudaStream_t stream);
+// generate_training_samples_nerf as count + scans + emit (srf_training.cu).
+void launch_train_count(const DevCfg& g, const TrainViews& tv, const uint8_t* bits, uint32_t n_rays, uint32_t n_rays_shift,
+                        uint32_t n_max_steps, RefreshRng rng, int snap, uint32_t* counts, uint32_t* flags, cudaStream_t stream);
+void launch_train_emit(const DevCfg& g, const TrainViews& tv, const uint8_t* bits, uint32_t n_rays, uint32_t n_rays_shift,
+                       uint32_t n_coords, RefreshRng rng, int snap, const uint32_t* counts, const uint64_t* offsets,
+                       const uint64_t* ray_rank, uint32_t* ray_counter, uint32_t* numsteps_counter, float* rays_out,
+                       float* rays_rgba, uint32_t* numsteps_out, float* coords_out, cudaStream_t stream);
+
 // Summaries of the bitfield used by the sampler's staged empty-space tests (N/32 and N*N/32 words).
 void launch_build_skip_tables(const DevCfg& g, const uint8_t* bits, uint32_t* shell, uint32_t* yz, cudaStream_t stream);
 

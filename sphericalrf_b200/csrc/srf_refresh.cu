@@ -19,30 +19,6 @@ namespace srf {
 
 namespace {
 
-constexpr uint64_t kPcgMult = 0x5851f42d4c957f2dULL;
-
-struct Pcg { uint64_t state, inc; };
-__device__ __forceinline__ uint32_t pcg_next_uint(Pcg& r) {
-    const uint64_t old = r.state;
-    r.state = old * kPcgMult + r.inc;
-    const uint32_t xorshifted = (uint32_t)(((old >> 18u) ^ old) >> 27u);
-    const uint32_t rot = (uint32_t)(old >> 59u);
-    return (xorshifted >> rot) | (xorshifted << ((~rot + 1u) & 31));
-}
-__device__ __forceinline__ float pcg_next_float(Pcg& r) {
-    return __uint_as_float((pcg_next_uint(r) >> 9) | 0x3f800000u) - 1.0f;
-}
-__device__ __forceinline__ void pcg_advance(Pcg& r, uint64_t delta) {
-    uint64_t cur_mult = kPcgMult, cur_plus = r.inc, acc_mult = 1u, acc_plus = 0u;
-    while (delta > 0) {
-        if (delta & 1) { acc_mult *= cur_mult; acc_plus = acc_plus * cur_mult + cur_plus; }
-        cur_plus = (cur_mult + 1) * cur_plus;
-        cur_mult *= cur_mult;
-        delta >>= 1;
-    }
-    r.state = acc_mult * r.state + acc_plus;
-}
-
 constexpr int kRefreshBlock = 128;
 
 // generate_grid_samples_nerf_nonuniform (:104-185) + hash encoding + density MLP output 0 +

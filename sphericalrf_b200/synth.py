@@ -260,3 +260,18 @@ def scene_config4(grid_size=128, width=3840, height=2160):
     sc["cameras"] = [orbit_camera(3.0, 0.0, 90.0 * k) for k in range(4)]
     sc["cfg"].max_samples_per_ray = 2048
     return sc
+
+
+def training_views(seed, n_images=6, width=32, height=24, radius=3.0, fov_deg=50.0, zero_probability=0.2):
+    """A seeded set of training views in the layout the training-side sampler reads: cameras on an orbit
+    looking at the centre (3x4, column-major, internal convention), fp16 rgba images of uniform noise, and
+    a per-pixel sampling probability with a fraction of zeros (pixels the sampler must never pick)."""
+    rng = np.random.Generator(np.random.PCG64(seed))
+    xforms = np.stack([orbit_camera(radius, float(rng.uniform(-40, 40)), 360.0 * k / n_images).flatten(order="F")
+                       for k in range(n_images)]).astype(np.float32)
+    images = rng.random((n_images, height, width, 4)).astype(np.float16)
+    prob = rng.random((n_images, height, width)).astype(np.float16)
+    prob[rng.random((n_images, height, width)) < zero_probability] = 0
+    focal = float(width) * 0.5 / math.tan(0.5 * math.radians(fov_deg))
+    return dict(n_images=n_images, width=width, height=height, focal_length=(focal, focal), principal_point=(0.5, 0.5),
+                xforms=xforms, images=images, sampling_probability=prob)

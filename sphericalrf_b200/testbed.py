@@ -152,6 +152,54 @@ class Renderer:
                                      None if stats is None else C.byref(stats)))
         return (img, stats.as_dict()) if want_stats else img
 
+    # -- training-side sampler --
+    def _device_views(self, views: dict):
+        """srf_train_views_t over torch device copies of dict(n_images, width, height, focal_length,
+        principal_point, xforms (n,12) column-major, images (n,H,W,4) fp16 | None, sampling_probability | None)."""
+        import torch
+        dev = torch.device("cuda", self.device)
+        keep = [torch.from_numpy(np.ascontiguousarray(views["xforms"], np.float32)).to(dev),
+                None if views.get("images") is None else torch.from_numpy(np.ascontiguousarray(views["images"], np.float16)).to(dev),
+                None if views.get("sampling_probability") is None else
+                torch.from_numpy(np.ascontiguousarray(views["sampling_probability"], np.float16)).to(dev)]
+        tv = abi.TrainViews()
+        tv.n_images, tv.width, tv.height = int(views["n_images"]), int(views["width"]), int(views["height"])
+        tv.focal_length[:] = [float(x) for x in views["focal_length"]]
+        tv.principal_point[:] = [float(x) for x in views["principal_point"]]
+        tv.d_xforms = keep[0].data_ptr()
+        tv.d_images = None if keep[1] is None else keep[1].data_ptr()
+        tv.d_sampling_probability = None if keep[2] is None else keep[2].data_ptr()
+        return tv, keep
+
+    def sampler_init(self, views, init_grid_with_mask=False, rng_seed=0):
+        """OccupancySampler::init: restart the refresh stream, mask or clear the density grid."""
+        import torch
+        tv, keep = (None, None) if views is None else self._device_views(views)
+        self._ck(self.lib.srf_sampler_init(self.ctx, None if tv is None else C.byref(tv), 1 if init_grid_with_mask else 0,
+                                           rng_seed, None))
+        torch.cuda.synchronize(self.device)
+
+    def sample_training_rays(self, views, n_rays, n_rays_shift, n_coords, rng_state, rng_inc, snap=True):
+        """srf_sample_training_rays with device buffers from torch; returns numpy arrays like the oracle's call."""
+        import torch
+        dev = torch.device("cuda", self.device)
+        tv, keep = self._device_views(views)
+        counters = torch.zeros(2, dtype=torch.int32, device=dev)
+        rays = torch.zeros((n_rays, 6), dtype=torch.float32, device=dev)
+        rgba = torch.zeros((n_rays, 4), dtype=torch.float32, device=dev)
+        numsteps = torch.zeros((n_rays, 2), dtype=torch.int32, device=dev)
+        coords = torch.zeros((n_coords, 7), dtype=torch.float32, device=dev)
+        self._ck(self.lib.srf_sample_training_rays(self.ctx, C.byref(tv), n_rays, n_rays_shift, n_coords, rng_state, rng_inc,
+                                                   1 if snap else 0, C.c_void_p(counters.data_ptr()),
+                                                   C.c_void_p(counters.data_ptr() + 4), C.c_void_p(rays.data_ptr()),
+                                                   C.c_void_p(rgba.data_ptr()), C.c_void_p(numsteps.data_ptr()),
+                                                   C.c_void_p(coords.data_ptr()), None))
+        torch.cuda.synchronize(dev)
+        c = counters.cpu().numpy().astype(np.uint32)
+        k = int(c[0])
+        return dict(n_rays=k, n_samples_total=int(c[1]), rays=rays[:k].cpu().numpy(), rgba=rgba[:k].cpu().numpy(),
+                    numsteps=numsteps[:k].cpu().numpy().astype(np.uint32), coords=coords.cpu().numpy())
+
     def dump_samples(self, view, ray_first, ray_count, capacity):
         counts = np.zeros(ray_count, np.uint32)
         pos_dt = np.zeros((capacity, 4), np.float32)
