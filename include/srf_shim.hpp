@@ -57,6 +57,20 @@ public:
                                    float* d_coords, void* stream) {
         check(srf_sample_emit(m.get(), &view, d_offsets, capacity, d_coords, nullptr, nullptr, stream), m.get());
     }
+    // OccupancySampler::init(n_images, resolution, focal, pp, camera_matrices, images, rng, stream)
+    void init(const srf_train_views_t& views, bool init_grid_with_mask, uint64_t rng_seed, void* stream) {
+        check(srf_sampler_init(m.get(), &views, init_grid_with_mask ? 1 : 0, rng_seed, stream), m.get());
+    }
+    // OccupancySampler::sample_coords_from_dataset(n_rays, n_rays_shift, n_coords, dataset, rays, rays_rgba,
+    //     n_rays_counter, ray_coord_indices, coords, n_coords_counter, rng, stream)
+    void sample_coords_from_dataset(uint32_t n_rays, uint32_t n_rays_shift, uint32_t n_coords, const srf_train_views_t& dataset,
+                                    float* d_rays, float* d_rays_rgba, uint32_t* d_n_rays_counter, uint32_t* d_ray_coord_indices,
+                                    float* d_coords, uint32_t* d_n_coords_counter, uint64_t rng_state, uint64_t rng_inc,
+                                    bool snap_to_pixel_centers_in_training, void* stream) {
+        check(srf_sample_training_rays(m.get(), &dataset, n_rays, n_rays_shift, n_coords, rng_state, rng_inc,
+                                       snap_to_pixel_centers_in_training ? 1 : 0, d_n_rays_counter, d_n_coords_counter, d_rays,
+                                       d_rays_rgba, d_ray_coord_indices, d_coords, stream), m.get());
+    }
 private:
     Context& m;
 };

@@ -180,7 +180,7 @@ class Renderer:
         torch.cuda.synchronize(self.device)
 
     def sample_training_rays(self, views, n_rays, n_rays_shift, n_coords, rng_state, rng_inc, snap=True):
-        """srf_sample_training_rays with device buffers from torch; returns numpy arrays like the oracle's call."""
+        """srf_sample_training_rays with device buffers from torch; returns numpy arrays (kept rays only)."""
         import torch
         dev = torch.device("cuda", self.device)
         tv, keep = self._device_views(views)
