@@ -38,6 +38,9 @@ enum { SRF_ACT_NONE = 0, SRF_ACT_RELU = 1, SRF_ACT_LOGISTIC = 2, SRF_ACT_EXPONEN
 enum { SRF_MODE_AO = 0, SRF_MODE_SHADE = 1, SRF_MODE_NORMALS = 2, SRF_MODE_DEPTH = 3,
        SRF_MODE_DISTANCE = 4, SRF_MODE_COST = 5 };
 enum { SRF_COLOR_LINEAR = 0, SRF_COLOR_SRGB = 1, SRF_COLOR_VISPOSNEG = 2 };
+/* ELossType (internal/utils/loss.h:10-18) and ERegularizationType (internal/render/ray_marcher.h) */
+enum { SRF_LOSS_L2 = 0, SRF_LOSS_L1 = 1, SRF_LOSS_MAPE = 2, SRF_LOSS_SMAPE = 3, SRF_LOSS_SMOOTH_L1 = 4, SRF_LOSS_LOG_L1 = 5, SRF_LOSS_RELATIVE_L2 = 6 };
+enum { SRF_REG_NONE = 0, SRF_REG_DISTORTION = 1 };
 enum { SRF_TONEMAP_IDENTITY = 0, SRF_TONEMAP_ACES = 1, SRF_TONEMAP_HABLE = 2, SRF_TONEMAP_REINHARD = 3 };
 enum { SRF_WARP_NGP = 0, SRF_WARP_MIPNERF360 = 1, SRF_WARP_DONERF = 2, SRF_WARP_SIGMOID = 3,
        SRF_WARP_ERP = 4, SRF_WARP_SINUSOIDAL = 5 };
@@ -276,6 +279,39 @@ srf_status srf_sample_training_rays(srf_ctx* ctx, const srf_train_views_t* views
                                     int snap_to_pixel_centers, uint32_t* d_ray_counter, uint32_t* d_numsteps_counter,
                                     float* d_rays, float* d_rays_rgba, uint32_t* d_numsteps, float* d_coords,
                                     void* stream);
+
+/* Arguments of the training compositor that are not buffers. */
+typedef struct srf_loss_params_t {
+    uint32_t n_rays;                    /* rays of the batch (n_rays_per_batch): threads to run and the loss normaliser */
+    uint32_t n_max_compacted_coords;    /* capacity of the compacted buffers, in samples */
+    int32_t  loss_type;                 /* SRF_LOSS_* */
+    float    loss_scale;
+    int32_t  regularization_type;       /* SRF_REG_* */
+    float    background_color[3];
+    int32_t  color_space;               /* SRF_COLOR_* of the training images */
+    int32_t  train_with_random_bg_color;/* draw the background from the RNG state below (one colour for the batch,
+                                           as the reference's by-value rng gives) */
+    uint64_t rng_state, rng_inc;
+    uint32_t padded_output_width;       /* stride of d_dloss_doutput in halves (>= 4; NGPNetwork::padded_output_width) */
+} srf_loss_params_t;
+
+/* RayMarcher::volume_rendering_with_loss_and_gradient (internal/render/ray_marcher.cu:9-202,303-375): for
+   each of the *d_n_rays_counter rays the training sampler kept, composite its samples front to back until the
+   transmittance threshold, compare with the ray's training pixel, and write dL/d(network output) of the
+   samples consumed, compacted ray after ray.
+     in:  d_ray_coord_indices[n*2] (count, base per ray; srf_sample_training_rays' d_numsteps), d_rays_rgba[n*4],
+          d_coords[*7], d_network_output half[*4] (srf_network_inference on d_coords)
+     out: d_ray_coord_indices rewritten to (compacted count, compacted base); d_compacted_coords[*7];
+          d_n_compacted_counter[1] = samples consumed by all rays (may exceed the capacity, as in the reference);
+          d_dloss_doutput half[* padded_output_width] (first 4 of each row written);
+          d_loss_output[n_rays] (may be NULL): mean loss of the ray / n_rays;
+          d_reg_distortion[*2] (required for SRF_REG_DISTORTION, else NULL): running sums of w and w*m.
+   Compacted bases are those of a serial execution in ray order (the reference's depend on scheduling). */
+srf_status srf_volume_rendering_loss(srf_ctx* ctx, const srf_loss_params_t* params, const uint32_t* d_n_rays_counter,
+                                     uint32_t* d_ray_coord_indices, const float* d_rays_rgba, const float* d_coords,
+                                     const uint16_t* d_network_output, float* d_compacted_coords,
+                                     uint32_t* d_n_compacted_counter, uint16_t* d_dloss_doutput, float* d_loss_output,
+                                     float* d_reg_distortion, void* stream);
 
 /* ---- whole frames ------------------------------------------------------------------------ */
 

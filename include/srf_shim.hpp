@@ -101,6 +101,18 @@ public:
                           const uint16_t* d_rgbsigma, float* d_rgba, uint32_t* d_n_composited, void* stream) {
         check(srf_volume_rendering(m.get(), &view, d_offsets, n_rays, d_coords, d_rgbsigma, d_rgba, d_n_composited, stream), m.get());
     }
+    // RayMarcher::volume_rendering_with_loss_and_gradient(n_rays, n_max_compacted_coords, rays, rays_rgba, n_rays_counter,
+    //     ray_coord_indices, coords, compacted_coords, n_compacted_coords_counter, network_output, dloss_doutput, ...)
+    void volume_rendering_with_loss_and_gradient(const srf_loss_params_t& params, const float* d_rays_rgba,
+                                                 const uint32_t* d_n_rays_counter, uint32_t* d_ray_coord_indices,
+                                                 const float* d_coords, float* d_compacted_coords,
+                                                 uint32_t* d_n_compacted_coords_counter, const uint16_t* d_network_output,
+                                                 uint16_t* d_dloss_doutput, float* d_loss_output, float* d_reg_distortion,
+                                                 void* stream) {
+        check(srf_volume_rendering_loss(m.get(), &params, d_n_rays_counter, d_ray_coord_indices, d_rays_rgba, d_coords,
+                                        d_network_output, d_compacted_coords, d_n_compacted_coords_counter, d_dloss_doutput,
+                                        d_loss_output, d_reg_distortion, stream), m.get());
+    }
 private:
     Context& m;
 };

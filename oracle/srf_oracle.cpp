@@ -802,6 +802,143 @@ int srfo_warp_position(const srf_config_t* cfg, const float* pos, float* out, si
 
 uint64_t srfo_shard_ray_count(const srf_view_t* view) { return shard_rows_total(*view) * view->width; }
 
+/* ---- training compositor: internal/render/ray_marcher.cu:9-202, internal/utils/loss.cu:18-101 ---- */
+namespace {
+inline float rgb_derivative(float v, int act) {                      /* common_device.h:331-340 */
+    switch (act) {
+    case SRF_ACT_NONE: return 1.0f;
+    case SRF_ACT_RELU: return v > 0.f ? 1.0f : 0.0f;
+    case SRF_ACT_LOGISTIC: { const float d = srf_logisticf(v); return d * (1.f - d); }
+    case SRF_ACT_EXPONENTIAL: return srf_expf(clampf(v, -10.f, 10.f));
+    default: return 0.f;
+    }
+}
+inline float density_derivative(float v, int act) {                  /* common_device.h:353-362 */
+    switch (act) {
+    case SRF_ACT_NONE: return 1.0f;
+    case SRF_ACT_RELU: return v > 0.f ? 1.0f : 0.0f;
+    case SRF_ACT_LOGISTIC: { const float d = srf_logisticf(v); return d * (1.f - d); }
+    case SRF_ACT_EXPONENTIAL: return srf_expf(clampf(v, -15.f, 15.f));
+    default: return 0.f;
+    }
+}
+inline void loss_channel(int type, float target, float pred, float* loss, float* grad) {
+    const float d = pred - target;
+    switch (type) {
+    case SRF_LOSS_RELATIVE_L2: { const float f = 1.f / (pred * pred + 1e-2f); *loss = d * d * f; *grad = 2.0f * d * f; } break;   /* :26-33 */
+    case SRF_LOSS_L1: *loss = fabsf(d); *grad = copysignf(1.0f, d); break;                                                        /* :35-41 */
+    case SRF_LOSS_MAPE: { const float f = 1.f / (fabsf(pred) + 1e-2f); *loss = fabsf(d) * f; *grad = copysignf(f, d); } break;     /* :80-87 */
+    case SRF_LOSS_SMAPE: { const float f = 1.f / (0.5f * (fabsf(pred) + fabsf(target)) + 1e-2f); *loss = fabsf(d) * f; *grad = copysignf(f, d); } break;   /* :71-78 */
+    case SRF_LOSS_SMOOTH_L1: {                                                                                                    /* :43-59, alpha 0.1 (:95) */
+        const float a = 0.1f, ad = fabsf(d);
+        const float sq = 0.5f / a * d * d;
+        *loss = ad > a ? (ad - 0.5f * a) : sq;
+        *grad = ad > a ? (d > 0.f ? 1.0f : -1.0f) : (d / a);
+    } break;
+    case SRF_LOSS_LOG_L1: { const float dv = fabsf(d) + 1.0f; *loss = srf_logf(dv); *grad = copysignf(1.f / dv, d); } break;      /* :61-69 */
+    default: *loss = d * d; *grad = 2.0f * d; break;                                                                             /* :18-24 */
+    }
+}
+}  // namespace
+
+/* All pointers are HOST pointers.  `mean_density` is the grid mean the sampler holds (update_grid_bitfield). */
+int srfo_volume_rendering_loss(const srf_config_t* cfg, const srf_loss_params_t* p, uint32_t n_rays_kept,
+                               uint32_t* ray_coord_indices, const float* rays_rgba, const float* coords,
+                               const uint16_t* network_output, float mean_density, float* compacted_coords,
+                               uint32_t* n_compacted_counter, uint16_t* dloss_doutput, float* loss_output,
+                               float* reg_distortion) {
+    float bg_in[3] = {p->background_color[0], p->background_color[1], p->background_color[2]};
+    if (p->train_with_random_bg_color) {                             /* :83-85 */
+        srfo_rng_t r = {p->rng_state, p->rng_inc};
+        for (int c = 0; c < 3; ++c) bg_in[c] = pcg_next_float(r);
+    }
+    float bg_linear[3];
+    for (int c = 0; c < 3; ++c) bg_linear[c] = srgb_to_linear(bg_in[c]);   /* :86 */
+    const bool til = cfg->train_in_linear_color != 0;
+    *n_compacted_counter = 0;
+    for (uint32_t i = 0; i < n_rays_kept && i < p->n_rays; ++i) {
+        const uint32_t numsteps = ray_coord_indices[i * 2], base = ray_coord_indices[i * 2 + 1];
+        const float* co = coords + (size_t)base * 7;
+        const uint16_t* no = network_output + (size_t)base * 4;
+        float T = 1.f, rgb_ray[3] = {0.f, 0.f, 0.f};
+        uint32_t n = 0;
+        for (; n < numsteps; ++n) {                                  /* :62-80 */
+            if (T < cfg->transmittance_threshold) break;
+            const float density = network_to_density(h2f(no[4 * n + 3]), cfg->density_activation);
+            const float dt = co[7 * n + 3];
+            const float alpha = 1.f - srf_expf(-density * dt);
+            const float weight = alpha * T;
+            for (int c = 0; c < 3; ++c) rgb_ray[c] += weight * network_to_rgb(h2f(no[4 * n + c]), cfg->rgb_activation);
+            T *= (1.f - alpha);
+        }
+        float bg[3] = {bg_linear[0], bg_linear[1], bg_linear[2]};
+        const float* tex = rays_rgba + (size_t)i * 4;
+        float target[3] = {0.f, 0.f, 0.f};
+        if (til || p->color_space == SRF_COLOR_LINEAR) {             /* :91-98 */
+            for (int c = 0; c < 3; ++c) target[c] = tex[c] + (1.f - tex[3]) * bg[c];
+            if (!til) for (int c = 0; c < 3; ++c) { target[c] = linear_to_srgb(target[c]); bg[c] = linear_to_srgb(bg[c]); }
+        } else if (p->color_space == SRF_COLOR_SRGB) {               /* :99-106 */
+            for (int c = 0; c < 3; ++c) bg[c] = linear_to_srgb(bg[c]);
+            for (int c = 0; c < 3; ++c)
+                target[c] = tex[3] > 0.f ? linear_to_srgb(tex[c] / tex[3]) * tex[3] + (1.f - tex[3]) * bg[c] : bg[c];
+        }
+        if (n == numsteps) for (int c = 0; c < 3; ++c) rgb_ray[c] += T * bg[c];   /* :108-111 */
+        const uint32_t compacted_base = *n_compacted_counter;        /* :118 atomicAdd */
+        *n_compacted_counter += n;
+        const uint32_t n_max = p->n_max_compacted_coords;
+        n = std::min(n_max - std::min(n_max, compacted_base), n);    /* :119 */
+        ray_coord_indices[i * 2] = n;
+        ray_coord_indices[i * 2 + 1] = compacted_base;
+        if (n == 0) continue;
+        float loss[3], grad[3];
+        for (int c = 0; c < 3; ++c) loss_channel(p->loss_type, target[c], rgb_ray[c], &loss[c], &grad[c]);   /* :129 */
+        const float n_rays_f = (float)p->n_rays;
+        if (loss_output) loss_output[i] = ((loss[0] + loss[1]) + loss[2]) / 3.0f / n_rays_f;   /* :131-132 */
+        const float loss_scale = p->loss_scale / n_rays_f;           /* :134 */
+        const float output_l2_reg = cfg->rgb_activation == SRF_ACT_EXPONENTIAL ? 1e-4f : 0.0f;
+        const float output_l1_reg_density = (cfg->use_grid && (mean_density < cfg->min_optical_thickness)) ? 1e-4f : 0.0f;
+        if (p->regularization_type == SRF_REG_DISTORTION && reg_distortion) {   /* :143-167: T stays 1 in this loop */
+            float sum_w = 0.f, sum_wp = 0.f;
+            float* rd = reg_distortion + (size_t)compacted_base * 2;
+            for (uint32_t j = 0; j < n; ++j) {
+                const float alpha = 1.f - srf_expf(-network_to_density(h2f(no[4 * j + 3]), cfg->density_activation) * co[7 * j + 3]);
+                const float weight = alpha * 1.f;
+                sum_w += weight;
+                sum_wp += weight * (float)(j + 1) / (float)n;
+                rd[2 * j] = sum_w;
+                rd[2 * j + 1] = sum_wp;
+            }
+        }
+        T = 1.f;
+        float r2[3] = {0.f, 0.f, 0.f};
+        float* cc = compacted_coords + (size_t)compacted_base * 7;
+        uint16_t* dl = dloss_doutput + (size_t)compacted_base * p->padded_output_width;
+        for (uint32_t j = 0; j < n; ++j) {                           /* :170-201 */
+            for (int k = 0; k < 7; ++k) cc[(size_t)j * 7 + k] = co[7 * j + k];
+            const float dt = co[7 * j + 3];
+            float raw[4], rgb[3];
+            for (int k = 0; k < 4; ++k) raw[k] = h2f(no[4 * j + k]);
+            for (int k = 0; k < 3; ++k) rgb[k] = network_to_rgb(raw[k], cfg->rgb_activation);
+            const float density = network_to_density(raw[3], cfg->density_activation);
+            const float alpha = 1.f - srf_expf(-density * dt);
+            const float weight = alpha * T;
+            for (int k = 0; k < 3; ++k) r2[k] += weight * rgb[k];
+            T *= (1.f - alpha);
+            float out[4], v[3];
+            for (int k = 0; k < 3; ++k) {
+                const float dloss_by_drgb = weight * grad[k];
+                out[k] = loss_scale * (dloss_by_drgb * rgb_derivative(raw[k], cfg->rgb_activation) + fmaxf(0.0f, output_l2_reg * raw[k]));
+                v[k] = T * rgb[k] - (rgb_ray[k] - r2[k]);
+            }
+            const float dot = fmaf(grad[2], v[2], fmaf(grad[1], v[1], grad[0] * v[0]));   /* [E] dot */
+            const float dloss_by_dmlp = density_derivative(raw[3], cfg->density_activation) * (dt * dot);
+            out[3] = loss_scale * dloss_by_dmlp + (raw[3] < 0.f ? -output_l1_reg_density : 0.0f);
+            for (int k = 0; k < 4; ++k) dl[(size_t)j * p->padded_output_width + k] = f2h(out[k]);
+        }
+    }
+    return 0;
+}
+
 /* mark_untrained_density_grid (occupancy_sampler.cu:12-102).  views holds HOST pointers here.
    grid_out: cells * cascades floats: 0 where some training view sees the cell, -1 elsewhere. */
 int srfo_mark_untrained(const srf_config_t* cfg, const srf_train_views_t* tv, float* grid_out) {

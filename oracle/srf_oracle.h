@@ -53,6 +53,13 @@ int srfo_sample_training_rays(const srf_config_t* cfg, const srf_train_views_t* 
                               int snap_to_pixel_centers, uint32_t* ray_counter, uint32_t* numsteps_counter,
                               float* rays_out, float* rays_rgba, uint32_t* numsteps_out, float* coords_out);
 
+/* Training compositor (host pointers); n_rays_kept is the training sampler's ray counter. */
+int srfo_volume_rendering_loss(const srf_config_t* cfg, const srf_loss_params_t* params, uint32_t n_rays_kept,
+                               uint32_t* ray_coord_indices, const float* rays_rgba, const float* coords,
+                               const uint16_t* network_output, float mean_density, float* compacted_coords,
+                               uint32_t* n_compacted_counter, uint16_t* dloss_doutput, float* loss_output,
+                               float* reg_distortion);
+
 int srfo_network_inference(const srf_config_t* cfg, const srfo_model_t* model, const float* coords,
                            uint64_t n, uint16_t* rgbsigma);
 int srfo_network_density(const srf_config_t* cfg, const srfo_model_t* model, const float* positions,

@@ -212,3 +212,21 @@ def sample_training_rays(cfg: abi.Config, views: dict, bitfield, n_rays, n_rays_
     assert rc == 0
     k = rc_.value
     return dict(n_rays=k, n_samples_total=nc_.value, rays=rays[:k], rgba=rgba[:k], numsteps=numsteps[:k], coords=coords)
+
+
+def volume_rendering_loss(cfg: abi.Config, params: "abi.LossParams", n_rays_kept, ray_coord_indices, rays_rgba, coords,
+                          network_output, mean_density):
+    """Serial execution of the training compositor.  Returns dict(indices (n,2), compacted_coords, n_compacted,
+    dloss (capacity, width) float16, loss (n_rays,), reg (capacity, 2))."""
+    idx = np.ascontiguousarray(ray_coord_indices, np.uint32).copy()
+    rgba = np.ascontiguousarray(rays_rgba, np.float32)
+    co = np.ascontiguousarray(coords, np.float32)
+    no = np.ascontiguousarray(network_output, np.float16)
+    cap, w = int(params.n_max_compacted_coords), int(params.padded_output_width)
+    cc = np.zeros((cap, 7), np.float32); dl = np.zeros((cap, w), np.float16)
+    loss = np.zeros(int(params.n_rays), np.float32); reg = np.zeros((cap, 2), np.float32)
+    n_comp = C.c_uint32(0)
+    rc = lib().srfo_volume_rendering_loss(C.byref(cfg), C.byref(params), C.c_uint32(n_rays_kept), _p(idx), _p(rgba), _p(co), _p(no),
+                                          C.c_float(mean_density), _p(cc), C.byref(n_comp), _p(dl), _p(loss), _p(reg))
+    assert rc == 0
+    return dict(indices=idx, compacted_coords=cc, n_compacted=n_comp.value, dloss=dl, loss=loss, reg=reg)

@@ -19,6 +19,8 @@ ACT_NONE, ACT_RELU, ACT_LOGISTIC, ACT_EXPONENTIAL = range(4)
 MODE_AO, MODE_SHADE, MODE_NORMALS, MODE_DEPTH, MODE_DISTANCE, MODE_COST = range(6)
 COLOR_LINEAR, COLOR_SRGB, COLOR_VISPOSNEG = range(3)
 TONEMAP_IDENTITY, TONEMAP_ACES, TONEMAP_HABLE, TONEMAP_REINHARD = range(4)
+LOSS_L2, LOSS_L1, LOSS_MAPE, LOSS_SMAPE, LOSS_SMOOTH_L1, LOSS_LOG_L1, LOSS_RELATIVE_L2 = range(7)
+REG_NONE, REG_DISTORTION = range(2)
 WARP_NGP, WARP_MIPNERF360, WARP_DONERF, WARP_SIGMOID, WARP_ERP, WARP_SINUSOIDAL = range(6)
 SAMPLING_ORIGINAL, SAMPLING_DISPARITY, SAMPLING_LOG = range(3)
 GRID_WARPED_EXP, GRID_WARPED_RECIPROCAL, GRID_METRIC_EXP, GRID_METRIC_RECIPROCAL = range(4)
@@ -66,6 +68,15 @@ class TrainViews(C.Structure):
         ("n_images", C.c_uint32), ("width", C.c_int32), ("height", C.c_int32),
         ("focal_length", C.c_float * 2), ("principal_point", C.c_float * 2),
         ("d_xforms", C.c_void_p), ("d_images", C.c_void_p), ("d_sampling_probability", C.c_void_p),
+    ]
+
+
+class LossParams(C.Structure):
+    _fields_ = [
+        ("n_rays", C.c_uint32), ("n_max_compacted_coords", C.c_uint32), ("loss_type", C.c_int32), ("loss_scale", C.c_float),
+        ("regularization_type", C.c_int32), ("background_color", C.c_float * 3), ("color_space", C.c_int32),
+        ("train_with_random_bg_color", C.c_int32), ("rng_state", C.c_uint64), ("rng_inc", C.c_uint64),
+        ("padded_output_width", C.c_uint32),
     ]
 
 
@@ -185,6 +196,7 @@ SYMBOLS = {
     "srf_sampler_init": (C.c_int, [_ctx, _P(TrainViews), C.c_int, C.c_uint64, _vp]),
     "srf_sample_training_rays": (C.c_int, [_ctx, _P(TrainViews), C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint64, C.c_uint64,
                                            C.c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "srf_volume_rendering_loss": (C.c_int, [_ctx, _P(LossParams), _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "srf_sample_offsets_static": (C.c_int, [C.c_int, _vp, C.c_uint64, _vp, _vp, C.c_char_p, C.c_size_t]),
     "srf_eval_math": (C.c_int, [C.c_int, C.c_int, _vp, _vp, _vp, C.c_size_t]),
 }

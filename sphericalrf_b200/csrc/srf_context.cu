@@ -64,7 +64,7 @@ struct srf_ctx {
     uint32_t n_blobs = 0;
 
     // per-frame scratch
-    DevBuf train_flags, train_rank;
+    DevBuf train_flags, train_rank, loss_rgb;
     DevBuf ray_dir_t, ray_end, counts, offsets, scan_scratch;
     DevBuf pos_dt, sample_ray, rgbs;
     DevBuf pool_pos, pool_shaded, chunk_ray, chunk_next, ray_head;   // paged frame path
@@ -281,6 +281,7 @@ srf_status make_view(srf_ctx* ctx, const srf_view_t* view, DevView* v) {
 }
 
 float host_powf(float x, float y) { return x > 0.f ? srf_expf(y * srf_logf(x)) : 0.f; }
+float host_linear_to_srgb(float l) { return l < 0.0031308f ? 12.92f * l : 1.055f * host_powf(l, 0.41666f) - 0.055f; }
 float host_srgb_to_linear(float s) { return s <= 0.04045f ? s / 12.92f : host_powf((s + 0.055f) / 1.055f, 2.4f); }
 
 void make_post(const srf_post_t* post, DevPost* p) {
@@ -466,7 +467,7 @@ void srf_destroy(srf_ctx* ctx) {
     if (!ctx) return;
     DeviceGuard guard(ctx->device);
     void* ptrs[] = {ctx->grid, ctx->grid_current, ctx->partial_a, ctx->partial_b, ctx->mean, ctx->bits, ctx->table,
-                    ctx->w_density, ctx->w_rgb, ctx->skip_shell, ctx->skip_yz, ctx->train_flags.p, ctx->train_rank.p, ctx->blobs, ctx->cmap, ctx->d_counters, ctx->ray_dir_t.p, ctx->ray_end.p,
+                    ctx->w_density, ctx->w_rgb, ctx->skip_shell, ctx->skip_yz, ctx->train_flags.p, ctx->train_rank.p, ctx->loss_rgb.p, ctx->blobs, ctx->cmap, ctx->d_counters, ctx->ray_dir_t.p, ctx->ray_end.p,
                     ctx->counts.p, ctx->offsets.p, ctx->scan_scratch.p, ctx->pos_dt.p, ctx->sample_ray.p, ctx->rgbs.p,
                     ctx->img_out.p, ctx->img_accum.p, ctx->pool_pos.p, ctx->pool_shaded.p, ctx->chunk_ray.p, ctx->chunk_next.p,
                     ctx->ray_head.p, ctx->d_chunk_cursor};
@@ -694,6 +695,71 @@ srf_status srf_sample_training_rays(srf_ctx* ctx, const srf_train_views_t* views
     SRF_CK(ctx, cudaMemsetAsync(d_ray_counter, 0, sizeof(uint32_t), s));
     launch_train_emit(ctx->g, tv, ctx->bits, n_rays, n_rays_shift, n_coords, rng, snap_to_pixel_centers, counts, offsets, rank,
                       d_ray_counter, d_numsteps_counter, d_rays, d_rays_rgba, d_numsteps, d_coords, s);
+    SRF_CK(ctx, cudaGetLastError());
+    return SRF_OK;
+}
+
+static uint32_t host_pcg_next_uint(RefreshRng& r) {
+    const uint64_t old = r.state;
+    r.state = old * 0x5851f42d4c957f2dULL + r.inc;
+    const uint32_t xorshifted = (uint32_t)(((old >> 18u) ^ old) >> 27u);
+    const uint32_t rot = (uint32_t)(old >> 59u);
+    return (xorshifted >> rot) | (xorshifted << ((~rot + 1u) & 31));
+}
+static float host_pcg_next_float(RefreshRng& r) {
+    const uint32_t u = (host_pcg_next_uint(r) >> 9) | 0x3f800000u;
+    float f;
+    memcpy(&f, &u, 4);
+    return f - 1.0f;
+}
+
+srf_status srf_volume_rendering_loss(srf_ctx* ctx, const srf_loss_params_t* p, const uint32_t* d_n_rays_counter,
+                                     uint32_t* d_ray_coord_indices, const float* d_rays_rgba, const float* d_coords,
+                                     const uint16_t* d_network_output, float* d_compacted_coords, uint32_t* d_n_compacted_counter,
+                                     uint16_t* d_dloss_doutput, float* d_loss_output, float* d_reg_distortion, void* stream) {
+    if (!ctx || !p || !d_n_rays_counter || !d_ray_coord_indices || !d_rays_rgba || !d_coords || !d_network_output ||
+        !d_compacted_coords || !d_n_compacted_counter || !d_dloss_doutput)
+        return SRF_ERR_ARG;
+    if (p->n_rays == 0) return fail(ctx, SRF_ERR_ARG, "n_rays must be positive");
+    if (p->padded_output_width < 4) return fail(ctx, SRF_ERR_ARG, "padded_output_width must be at least 4");
+    if (p->loss_type < SRF_LOSS_L2 || p->loss_type > SRF_LOSS_RELATIVE_L2) return fail(ctx, SRF_ERR_ARG, "Unknown loss type.");
+    if (p->regularization_type != SRF_REG_NONE && p->regularization_type != SRF_REG_DISTORTION)
+        return fail(ctx, SRF_ERR_ARG, "Unknown regularization type.");
+    if (p->regularization_type == SRF_REG_DISTORTION && !d_reg_distortion)
+        return fail(ctx, SRF_ERR_ARG, "distortion regularisation needs d_reg_distortion");
+    DeviceGuard guard(ctx->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    LossParams lp;
+    lp.n_rays = p->n_rays; lp.n_max_compacted_coords = p->n_max_compacted_coords; lp.padded_output_width = p->padded_output_width;
+    lp.loss_type = p->loss_type; lp.color_space = p->color_space; lp.loss_scale = p->loss_scale;
+    lp.transmittance_threshold = ctx->cfg.transmittance_threshold;
+    lp.min_optical_thickness = ctx->min_optical_thickness;
+    float bg[3] = {p->background_color[0], p->background_color[1], p->background_color[2]};
+    if (p->train_with_random_bg_color) {                     // ray_marcher.cu:83-85: the same three draws for every ray
+        RefreshRng r = {p->rng_state, p->rng_inc};
+        for (int c = 0; c < 3; ++c) bg[c] = host_pcg_next_float(r);
+    }
+    for (int c = 0; c < 3; ++c) {
+        lp.bg_linear[c] = host_srgb_to_linear(bg[c]);         // :86
+        lp.bg_final[c] = ctx->cfg.train_in_linear_color ? lp.bg_linear[c] : host_linear_to_srgb(lp.bg_linear[c]);   // :95-100
+    }
+    if (!ctx->cfg.train_in_linear_color && p->color_space != SRF_COLOR_LINEAR && p->color_space != SRF_COLOR_SRGB)
+        for (int c = 0; c < 3; ++c) lp.bg_final[c] = lp.bg_linear[c];
+    const uint32_t n = p->n_rays;
+    srf_status st;
+    if ((st = ensure(ctx, ctx->counts, (size_t)n * sizeof(uint32_t))) != SRF_OK) return st;
+    if ((st = ensure(ctx, ctx->offsets, ((size_t)n + 1) * sizeof(uint64_t))) != SRF_OK) return st;
+    if ((st = ensure(ctx, ctx->loss_rgb, (size_t)n * sizeof(float4))) != SRF_OK) return st;
+    if ((st = ensure(ctx, ctx->scan_scratch, scan_scratch_bytes(n))) != SRF_OK) return st;
+    uint32_t* consumed = (uint32_t*)ctx->counts.p;
+    uint64_t* bases = (uint64_t*)ctx->offsets.p;
+    launch_loss_forward(ctx->g, lp, d_n_rays_counter, d_ray_coord_indices, d_coords, (const uint2*)d_network_output, consumed,
+                        (float4*)ctx->loss_rgb.p, n, s);
+    launch_scan(consumed, n, bases, ctx->scan_scratch.p, s);
+    launch_loss_backward(ctx->g, lp, d_n_rays_counter, d_ray_coord_indices, d_coords, (const uint2*)d_network_output,
+                         (const float4*)d_rays_rgba, consumed, bases, (const float4*)ctx->loss_rgb.p, ctx->mean, d_compacted_coords,
+                         d_n_compacted_counter, (__half*)d_dloss_doutput, d_loss_output,
+                         p->regularization_type == SRF_REG_DISTORTION ? d_reg_distortion : nullptr, n, s);
     SRF_CK(ctx, cudaGetLastError());
     return SRF_OK;
 }

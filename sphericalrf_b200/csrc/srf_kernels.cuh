@@ -151,6 +151,23 @@ void launch_train_emit(const DevCfg& g, const TrainViews& tv, const uint8_t* bit
                        const uint64_t* ray_rank, uint32_t* ray_counter, uint32_t* numsteps_counter, float* rays_out,
                        float* rays_rgba, uint32_t* numsteps_out, float* coords_out, cudaStream_t stream);
 
+// Training compositor (srf_loss.cu).  bg_linear: the background after srgb_to_linear; bg_final: the colour added
+// behind a ray that ran through all its samples (bg_linear, or its sRGB encoding when not training in linear colour).
+struct LossParams {
+    uint32_t n_rays, n_max_compacted_coords, padded_output_width;
+    int loss_type, color_space;
+    float loss_scale, transmittance_threshold, min_optical_thickness;
+    float bg_linear[3], bg_final[3];
+};
+void launch_loss_forward(const DevCfg& g, const LossParams& lp, const uint32_t* n_rays_counter, const uint32_t* ray_coord_indices,
+                         const float* coords, const uint2* net_out, uint32_t* consumed, float4* ray_rgb, uint32_t n_slots,
+                         cudaStream_t stream);
+void launch_loss_backward(const DevCfg& g, const LossParams& lp, const uint32_t* n_rays_counter, uint32_t* ray_coord_indices,
+                          const float* coords, const uint2* net_out, const float4* rays_rgba, const uint32_t* consumed,
+                          const uint64_t* bases, const float4* ray_rgb, const float* mean_density, float* compacted_coords,
+                          uint32_t* n_compacted_counter, __half* dloss_doutput, float* loss_output, float* reg_distortion,
+                          uint32_t n_slots, cudaStream_t stream);
+
 // Summaries of the bitfield used by the sampler's staged empty-space tests (N/32 and N*N/32 words).
 void launch_build_skip_tables(const DevCfg& g, const uint8_t* bits, uint32_t* shell, uint32_t* yz, cudaStream_t stream);
 

@@ -1,0 +1,215 @@
+// srf_loss.cu -- volume rendering of training rays with loss and gradient
+// (volume_rendering_with_loss_and_gradient_kernal, internal/render/ray_marcher.cu:9-202; the losses of
+// internal/utils/loss.cu:18-101).
+//
+// The reference does everything for a ray in one kernel and reserves the ray's slots in the compacted
+// buffers with atomicAdd, so the compacted order changes from run to run.  Here a forward kernel composites
+// each ray and counts the samples it consumed, an exclusive scan turns the counts into bases in ray order
+// (the bases a serial execution of the reference kernel would hand out), and a backward kernel writes the
+// compacted coordinates, the loss and dL/d(network output).
+#include "srf_kernels.cuh"
+
+namespace srf {
+
+namespace {
+
+constexpr int kLossBlock = 128;
+
+__device__ __forceinline__ float network_to_rgb_derivative(float v, int act) {          // common_device.h:331-340
+    switch (act) {
+    case SRF_ACT_NONE: return 1.0f;
+    case SRF_ACT_RELU: return v > 0.f ? 1.0f : 0.0f;
+    case SRF_ACT_LOGISTIC: { const float d = srf_logisticf(v); return d * (1.f - d); }
+    case SRF_ACT_EXPONENTIAL: return srf_expf(fminf(fmaxf(v, -10.f), 10.f));
+    default: return 0.f;
+    }
+}
+__device__ __forceinline__ float network_to_density_derivative(float v, int act) {      // common_device.h:353-362
+    switch (act) {
+    case SRF_ACT_NONE: return 1.0f;
+    case SRF_ACT_RELU: return v > 0.f ? 1.0f : 0.0f;
+    case SRF_ACT_LOGISTIC: { const float d = srf_logisticf(v); return d * (1.f - d); }
+    case SRF_ACT_EXPONENTIAL: return srf_expf(fminf(fmaxf(v, -15.f), 15.f));
+    default: return 0.f;
+    }
+}
+
+// One channel of loss_and_gradient (internal/utils/loss.cu:18-101).
+__device__ __forceinline__ void loss_channel(int type, float target, float pred, float* loss, float* grad) {
+    const float d = pred - target;
+    switch (type) {
+    case SRF_LOSS_RELATIVE_L2: {
+        const float f = 1.f / (pred * pred + 1e-2f);
+        *loss = d * d * f; *grad = 2.0f * d * f;
+    } break;
+    case SRF_LOSS_L1: *loss = fabsf(d); *grad = copysignf(1.0f, d); break;
+    case SRF_LOSS_MAPE: {
+        const float f = 1.f / (fabsf(pred) + 1e-2f);
+        *loss = fabsf(d) * f; *grad = copysignf(f, d);
+    } break;
+    case SRF_LOSS_SMAPE: {
+        const float f = 1.f / (0.5f * (fabsf(pred) + fabsf(target)) + 1e-2f);
+        *loss = fabsf(d) * f; *grad = copysignf(f, d);
+    } break;
+    case SRF_LOSS_SMOOTH_L1: {
+        const float a = 0.1f, ad = fabsf(d);
+        const float sq = 0.5f / a * d * d;
+        *loss = ad > a ? (ad - 0.5f * a) : sq;
+        *grad = ad > a ? (d > 0.f ? 1.0f : -1.0f) : (d / a);
+    } break;
+    case SRF_LOSS_LOG_L1: {
+        const float dv = fabsf(d) + 1.0f;
+        *loss = srf_logf(dv); *grad = copysignf(1.f / dv, d);
+    } break;
+    default: *loss = d * d; *grad = 2.0f * d; break;     // L2
+    }
+}
+
+struct Sample4 { float r, g, b, s; };
+__device__ __forceinline__ Sample4 load_output(const uint2* out, uint64_t k) {
+    const uint2 u = out[k];
+    const __half2 a = *reinterpret_cast<const __half2*>(&u.x), b = *reinterpret_cast<const __half2*>(&u.y);
+    return {__low2float(a), __high2float(a), __low2float(b), __high2float(b)};
+}
+
+// Forward pass (:57-80 and :113-116): composites until the transmittance threshold, records the number of
+// samples consumed and the ray colour (background included when the ray ran through all its samples).
+__global__ void __launch_bounds__(kLossBlock)
+k_loss_forward(const DevCfg g, const LossParams lp, const uint32_t* __restrict__ n_rays_counter,
+               const uint32_t* __restrict__ ray_coord_indices, const float* __restrict__ coords, const uint2* __restrict__ net_out,
+               uint32_t* __restrict__ consumed, float4* __restrict__ ray_rgb, uint32_t n_slots) {
+    const uint32_t i = blockIdx.x * kLossBlock + threadIdx.x;
+    if (i >= n_slots) return;
+    if (i >= *n_rays_counter) { consumed[i] = 0; return; }
+    const uint32_t numsteps = ray_coord_indices[i * 2 + 0], base = ray_coord_indices[i * 2 + 1];
+    float T = 1.f, r = 0.f, gg = 0.f, b = 0.f;
+    uint32_t n = 0;
+    for (; n < numsteps; ++n) {
+        if (T < lp.transmittance_threshold) break;
+        const Sample4 o = load_output(net_out, (uint64_t)base + n);
+        const float density = network_to_density(o.s, g.density_activation);
+        const float dt = coords[((uint64_t)base + n) * 7 + 3];
+        const float alpha = 1.f - srf_expf(-density * dt);
+        const float weight = alpha * T;
+        r += weight * network_to_rgb(o.r, g.rgb_activation);
+        gg += weight * network_to_rgb(o.g, g.rgb_activation);
+        b += weight * network_to_rgb(o.b, g.rgb_activation);
+        T *= (1.f - alpha);
+    }
+    if (n == numsteps) { r += T * lp.bg_final[0]; gg += T * lp.bg_final[1]; b += T * lp.bg_final[2]; }
+    consumed[i] = n;
+    ray_rgb[i] = make_float4(r, gg, b, T);
+}
+
+// Loss and backward pass (:118-201).
+__global__ void __launch_bounds__(kLossBlock)
+k_loss_backward(const DevCfg g, const LossParams lp, const uint32_t* __restrict__ n_rays_counter,
+                uint32_t* __restrict__ ray_coord_indices, const float* __restrict__ coords, const uint2* __restrict__ net_out,
+                const float4* __restrict__ rays_rgba, const uint32_t* __restrict__ consumed, const uint64_t* __restrict__ bases,
+                const float4* __restrict__ ray_rgb, const float* __restrict__ mean_density, float* __restrict__ compacted_coords,
+                uint32_t* __restrict__ n_compacted_counter, __half* __restrict__ dloss_doutput, float* __restrict__ loss_output,
+                float* __restrict__ reg_distortion, uint32_t n_slots) {
+    const uint32_t i = blockIdx.x * kLossBlock + threadIdx.x;
+    if (i == 0) *n_compacted_counter = (uint32_t)bases[n_slots];
+    if (i >= n_slots || i >= *n_rays_counter) return;
+    const uint32_t base = ray_coord_indices[i * 2 + 1];
+    const uint32_t compacted_base = (uint32_t)bases[i];
+    const uint32_t n_max = lp.n_max_compacted_coords;
+    const uint32_t n = min(n_max - min(n_max, compacted_base), consumed[i]);                   // :122
+    ray_coord_indices[i * 2 + 0] = n;
+    ray_coord_indices[i * 2 + 1] = compacted_base;
+    if (n == 0) return;
+
+    // ground-truth colour (:88-111)
+    const float4 tex = rays_rgba[i];
+    float target[3];
+    if (g.train_in_linear_color || lp.color_space == SRF_COLOR_LINEAR) {
+        target[0] = tex.x + (1.f - tex.w) * lp.bg_linear[0];
+        target[1] = tex.y + (1.f - tex.w) * lp.bg_linear[1];
+        target[2] = tex.z + (1.f - tex.w) * lp.bg_linear[2];
+        if (!g.train_in_linear_color) for (int c = 0; c < 3; ++c) target[c] = linear_to_srgb(target[c]);
+    } else if (lp.color_space == SRF_COLOR_SRGB) {
+        const float t3[3] = {tex.x, tex.y, tex.z};
+        for (int c = 0; c < 3; ++c)
+            target[c] = tex.w > 0.f ? linear_to_srgb(t3[c] / tex.w) * tex.w + (1.f - tex.w) * lp.bg_final[c] : lp.bg_final[c];
+    } else {
+        target[0] = target[1] = target[2] = 0.f;          // the reference leaves rgbtarget unset for other colour spaces
+    }
+    const float4 rr = ray_rgb[i];
+    const float rgb_ray[3] = {rr.x, rr.y, rr.z};
+    float loss[3], grad[3];
+    for (int c = 0; c < 3; ++c) loss_channel(lp.loss_type, target[c], rgb_ray[c], &loss[c], &grad[c]);
+    const float n_rays_f = (float)lp.n_rays;
+    if (loss_output) loss_output[i] = ((loss[0] + loss[1]) + loss[2]) / 3.0f / n_rays_f;
+    const float loss_scale = lp.loss_scale / n_rays_f;
+    const float output_l2_reg = g.rgb_activation == SRF_ACT_EXPONENTIAL ? 1e-4f : 0.0f;
+    const float output_l1_reg_density = (g.use_grid && (*mean_density < lp.min_optical_thickness)) ? 1e-4f : 0.0f;
+
+    if (reg_distortion) {                                                                     // :137-163
+        float T = 1.f, sum_w = 0.f, sum_wp = 0.f;
+        float* rd = reg_distortion + (uint64_t)compacted_base * 2;
+        for (uint32_t j = 0; j < n; ++j) {
+            const Sample4 o = load_output(net_out, (uint64_t)base + j);
+            const float dt = coords[((uint64_t)base + j) * 7 + 3];
+            const float alpha = 1.f - srf_expf(-network_to_density(o.s, g.density_activation) * dt);
+            const float weight = alpha * T;       // T is not advanced in this loop of the reference
+            sum_w += weight;
+            sum_wp += weight * (float)(j + 1) / (float)n;
+            rd[2 * j] = sum_w;
+            rd[2 * j + 1] = sum_wp;
+        }
+    }
+
+    float T = 1.f, r2[3] = {0.f, 0.f, 0.f};
+    float* cc = compacted_coords + (uint64_t)compacted_base * 7;
+    __half* dl = dloss_doutput + (uint64_t)compacted_base * lp.padded_output_width;
+    for (uint32_t j = 0; j < n; ++j) {
+        const float* c = coords + ((uint64_t)base + j) * 7;
+        for (int k = 0; k < 7; ++k) cc[(uint64_t)j * 7 + k] = c[k];
+        const float dt = c[3];
+        const Sample4 o = load_output(net_out, (uint64_t)base + j);
+        const float raw[3] = {o.r, o.g, o.b};
+        float rgb[3];
+        for (int k = 0; k < 3; ++k) rgb[k] = network_to_rgb(raw[k], g.rgb_activation);
+        const float density = network_to_density(o.s, g.density_activation);
+        const float alpha = 1.f - srf_expf(-density * dt);
+        const float weight = alpha * T;
+        for (int k = 0; k < 3; ++k) r2[k] += weight * rgb[k];
+        T *= (1.f - alpha);
+        float out[4];
+        float v[3];
+        for (int k = 0; k < 3; ++k) {
+            const float dloss_by_drgb = weight * grad[k];
+            out[k] = loss_scale * (dloss_by_drgb * network_to_rgb_derivative(raw[k], g.rgb_activation) + fmaxf(0.0f, output_l2_reg * raw[k]));
+            v[k] = T * rgb[k] - (rgb_ray[k] - r2[k]);                                         // T * rgb - suffix
+        }
+        const float dot = fmaf(grad[2], v[2], fmaf(grad[1], v[1], grad[0] * v[0]));
+        const float dloss_by_dmlp = network_to_density_derivative(o.s, g.density_activation) * (dt * dot);
+        out[3] = loss_scale * dloss_by_dmlp + (o.s < 0.f ? -output_l1_reg_density : 0.0f);
+        __half* d = dl + (uint64_t)j * lp.padded_output_width;
+        for (int k = 0; k < 4; ++k) d[k] = __float2half_rn(out[k]);
+    }
+}
+
+}  // namespace
+
+void launch_loss_forward(const DevCfg& g, const LossParams& lp, const uint32_t* n_rays_counter, const uint32_t* ray_coord_indices,
+                         const float* coords, const uint2* net_out, uint32_t* consumed, float4* ray_rgb, uint32_t n_slots,
+                         cudaStream_t stream) {
+    if (n_slots == 0) return;
+    k_loss_forward<<<(n_slots + kLossBlock - 1) / kLossBlock, kLossBlock, 0, stream>>>(g, lp, n_rays_counter, ray_coord_indices, coords,
+                                                                                      net_out, consumed, ray_rgb, n_slots);
+}
+
+void launch_loss_backward(const DevCfg& g, const LossParams& lp, const uint32_t* n_rays_counter, uint32_t* ray_coord_indices,
+                          const float* coords, const uint2* net_out, const float4* rays_rgba, const uint32_t* consumed,
+                          const uint64_t* bases, const float4* ray_rgb, const float* mean_density, float* compacted_coords,
+                          uint32_t* n_compacted_counter, __half* dloss_doutput, float* loss_output, float* reg_distortion,
+                          uint32_t n_slots, cudaStream_t stream) {
+    if (n_slots == 0) return;
+    k_loss_backward<<<(n_slots + kLossBlock - 1) / kLossBlock, kLossBlock, 0, stream>>>(
+        g, lp, n_rays_counter, ray_coord_indices, coords, net_out, rays_rgba, consumed, bases, ray_rgb, mean_density, compacted_coords,
+        n_compacted_counter, dloss_doutput, loss_output, reg_distortion, n_slots);
+}
+
+}  // namespace srf

@@ -200,6 +200,28 @@ class Renderer:
         return dict(n_rays=k, n_samples_total=int(c[1]), rays=rays[:k].cpu().numpy(), rgba=rgba[:k].cpu().numpy(),
                     numsteps=numsteps[:k].cpu().numpy().astype(np.uint32), coords=coords.cpu().numpy())
 
+    def volume_rendering_loss(self, params, n_rays_kept, ray_coord_indices, rays_rgba, coords, network_output):
+        """srf_volume_rendering_loss on host arrays (uploaded and read back through torch)."""
+        import torch
+        dev = torch.device("cuda", self.device)
+        up = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a, dt)).to(dev)
+        cap, w, n = int(params.n_max_compacted_coords), int(params.padded_output_width), int(params.n_rays)
+        kept = torch.tensor([n_rays_kept], dtype=torch.int32, device=dev)
+        idx = up(np.asarray(ray_coord_indices).astype(np.int32), np.int32)
+        rgba, co, no = up(rays_rgba, np.float32), up(coords, np.float32), up(network_output, np.float16)
+        cc = torch.zeros((cap, 7), dtype=torch.float32, device=dev)
+        dl = torch.zeros((cap, w), dtype=torch.float16, device=dev)
+        loss = torch.zeros(n, dtype=torch.float32, device=dev)
+        reg = torch.zeros((cap, 2), dtype=torch.float32, device=dev)
+        n_comp = torch.zeros(1, dtype=torch.int32, device=dev)
+        ptr = lambda t: C.c_void_p(t.data_ptr())
+        self._ck(self.lib.srf_volume_rendering_loss(self.ctx, C.byref(params), ptr(kept), ptr(idx), ptr(rgba), ptr(co), ptr(no), ptr(cc),
+                                                    ptr(n_comp), ptr(dl), ptr(loss),
+                                                    ptr(reg) if params.regularization_type == abi.REG_DISTORTION else None, None))
+        torch.cuda.synchronize(dev)
+        return dict(indices=idx.cpu().numpy().astype(np.uint32), compacted_coords=cc.cpu().numpy(), n_compacted=int(n_comp.item()),
+                    dloss=dl.cpu().numpy(), loss=loss.cpu().numpy(), reg=reg.cpu().numpy())
+
     def dump_samples(self, view, ray_first, ray_count, capacity):
         counts = np.zeros(ray_count, np.uint32)
         pos_dt = np.zeros((capacity, 4), np.float32)
