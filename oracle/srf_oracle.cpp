@@ -572,6 +572,75 @@ void density_net(const Cfg& g, const GridLayout& L, const srfo_model_t& m, const
     dense_layer(W.d.data() + 64 * 32, 16, 64, h, out16, false);
 }
 
+/* Density output 0 and its gradient with respect to the (warped) position: what
+   NGPNetwork::input_gradient(stream, 3, coords, coords) leaves in the position rows for the Normals render
+   mode (testbed.cu:557-559).  [T] The reference's dependency runs this backward pass in fp16 with a loss
+   scale; the canonical definition here is fp32 throughout:
+     d enc[l,f] / d x_d = scale_l * sum over the 4 corner pairs along d of (w_a' * w_b') * (v_hi - v_lo),
+       pairs ordered by the other two axes a < b, a's bit first;
+     g_h[j] = W2[0][j] where the (fp16, ReLU) hidden unit j is positive, else 0;
+     g_enc[k] = sum_j W1[j][k] * g_h[j] (j ascending, fused multiply-add);
+     grad[d]  = sum_k g_enc[k] * d enc[k] / d x_d (k ascending, fused multiply-add). */
+void density_with_gradient(const Cfg& g, const GridLayout& L, const srfo_model_t& m, const Weights& W, const float* x3,
+                           uint16_t* sigma_out, float* grad3) {
+    const uint32_t F = g.c.n_features_per_level;
+    uint16_t enc[32], h[64], out16[16];
+    float dydx[32][3];
+    for (uint32_t l = 0; l < g.c.n_levels; ++l) {
+        const float sc = L.scale[l];
+        const uint32_t res = L.res[l], size = L.offsets[l + 1] - L.offsets[l];
+        float w[3]; uint32_t ig[3];
+        for (int d = 0; d < 3; ++d) {
+            const float p = fmaf(sc, x3[d], 0.5f);
+            const float fl = floorf(p);
+            w[d] = p - fl;
+            ig[d] = (uint32_t)srf_f2i_rz(fl);
+        }
+        float v[8][8];
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (uint32_t c = 0; c < 8; ++c) {
+            float wt = 1.f; uint32_t gp[3];
+            for (int d = 0; d < 3; ++d) {
+                if ((c >> d) & 1u) { wt *= w[d]; gp[d] = ig[d] + 1u; }
+                else { wt *= 1.f - w[d]; gp[d] = ig[d]; }
+            }
+            const uint16_t* e = m.hash_table + (size_t)(L.offsets[l] + grid_index(gp[0], gp[1], gp[2], res, size)) * F;
+            for (uint32_t f = 0; f < F; ++f) { v[c][f] = h2f(e[f]); acc[f] = fmaf(wt, v[c][f], acc[f]); }
+        }
+        for (uint32_t f = 0; f < F; ++f) enc[l * F + f] = f2h(acc[f]);
+        for (int d = 0; d < 3; ++d) {
+            const int a = d == 0 ? 1 : 0, b = d == 2 ? 1 : 2;
+            for (uint32_t f = 0; f < F; ++f) {
+                float gs = 0.f;
+                for (uint32_t c2 = 0; c2 < 4; ++c2) {
+                    const uint32_t ba = c2 & 1u, bb = c2 >> 1;
+                    const float wt = (ba ? w[a] : 1.f - w[a]) * (bb ? w[b] : 1.f - w[b]);
+                    const uint32_t lo = (ba << a) | (bb << b), hi = lo | (1u << d);
+                    gs = fmaf(wt, v[hi][f] - v[lo][f], gs);
+                }
+                dydx[l * F + f][d] = sc * gs;
+            }
+        }
+    }
+    dense_layer(W.d.data(), 64, 32, enc, h, true);
+    dense_layer(W.d.data() + 64 * 32, 16, 64, h, out16, false);
+    *sigma_out = out16[0];
+    float g_enc[32];
+    for (int k = 0; k < 32; ++k) {
+        float acc = 0.f;
+        for (int j = 0; j < 64; ++j) {
+            const float gh = h2f(h[j]) > 0.f ? W.d[64 * 32 + j] : 0.f;
+            acc = fmaf(W.d[j * 32 + k], gh, acc);
+        }
+        g_enc[k] = acc;
+    }
+    for (int d = 0; d < 3; ++d) {
+        float acc = 0.f;
+        for (int k = 0; k < 32; ++k) acc = fmaf(g_enc[k], dydx[k][d], acc);
+        grad3[d] = acc;
+    }
+}
+
 /* NGPNetwork::inference_mixed_precision (ngp_network.h:212-279): (r,g,b) from the colour MLP,
    sigma = density output 0. */
 void network_eval(const Cfg& g, const GridLayout& L, const srfo_model_t& m, const Weights& W, const float* pos3, const float* dir3, uint16_t* rgbs4) {
@@ -664,7 +733,10 @@ void finish_pixel(const Cfg& g, const srf_view_t& v, const srf_post_t& post, boo
     float fb[4] = {0.f, 0.f, 0.f, 0.f};                              /* cleared frame buffer (testbed.cu:502) */
     if (hit) {
         float tmp[4] = {rgba_in[0], rgba_in[1], rgba_in[2], rgba_in[3]};
-        if (v.render_mode == SRF_MODE_COST) {                        /* :465-468 */
+        if (v.render_mode == SRF_MODE_NORMALS) {                     /* :463-465 */
+            const float nn = srf_norm3f(tmp[0], tmp[1], tmp[2]);
+            for (int i = 0; i < 3; ++i) tmp[i] = (0.5f * (nn > 0.f ? tmp[i] / nn : tmp[i]) + 0.5f) * tmp[3];
+        } else if (v.render_mode == SRF_MODE_COST) {                 /* :465-468 */
             const float col = (float)n_steps_total / 128;
             tmp[0] = tmp[1] = tmp[2] = col; tmp[3] = 1.0f;
         }
@@ -1162,7 +1234,7 @@ int srfo_render_frame(const srf_config_t* cfg, const srf_view_t* view, const srf
     const Cfg g = resolve(cfg);
     const GridLayout L = grid_layout(g);
     const Weights W(*model);
-    if (view->render_mode == SRF_MODE_NORMALS) return 1;
+    if (view->render_mode == SRF_MODE_NORMALS && g.c.field_type != SRF_FIELD_NETWORK) return 1;
     const uint64_t n_all = srfo_shard_ray_count(view);
     if (ray_count == 0) ray_count = n_all - ray_first;
     const uint32_t cap = sample_cap(g);
@@ -1187,8 +1259,19 @@ int srfo_render_frame(const srf_config_t* cfg, const srf_view_t* view, const srf
             end = march_ray(g, bitfield, r, cap, &steps, [&](const Sample& s) {
                 ++nsamp;
                 float raw[4];
+                float normal[3] = {0.f, 0.f, 0.f};
                 if (g.c.field_type == SRF_FIELD_BLOBS) {
                     blobs_eval(g, *model, s.w, raw);
+                } else if (view->render_mode == SRF_MODE_NORMALS) {
+                    /* testbed.cu:557-559 + ray_marcher.cu:250-255: the position rows hold d sigma_raw / d pos */
+                    const float p3[3] = {s.w.x, s.w.y, s.w.z};
+                    uint16_t sg; float grad[3];
+                    density_with_gradient(g, L, *model, W, p3, &sg, grad);
+                    raw[0] = raw[1] = raw[2] = 0.f; raw[3] = h2f(sg);
+                    const float dd = -density_derivative(raw[3], g.c.density_activation);
+                    for (int c = 0; c < 3; ++c) normal[c] = dd * grad[c];
+                    const float nn = srf_norm3f(normal[0], normal[1], normal[2]);
+                    if (nn > 0.f) for (int c = 0; c < 3; ++c) normal[c] /= nn;   /* [E] normalized() */
                 } else {
                     uint16_t o[4];
                     const float p3[3] = {s.w.x, s.w.y, s.w.z};
@@ -1210,6 +1293,8 @@ int srfo_render_frame(const srf_config_t* cfg, const srf_view_t* view, const srf
                     rgb[0] = rgb[1] = rgb[2] = zz;
                 } else if (view->render_mode == SRF_MODE_AO) {
                     rgb[0] = rgb[1] = rgb[2] = alpha;                /* :264 */
+                } else if (view->render_mode == SRF_MODE_NORMALS) {
+                    rgb[0] = normal[0]; rgb[1] = normal[1]; rgb[2] = normal[2];   /* :255 */
                 }
                 rgba[0] = fmaf(rgb[0], weight, rgba[0]);             /* :268 */
                 rgba[1] = fmaf(rgb[1], weight, rgba[1]);

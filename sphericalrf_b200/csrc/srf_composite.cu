@@ -54,7 +54,10 @@ __device__ void finish_pixel(const DevCfg& g, const DevView& v, const DevPost& p
     float fb[4] = {0.f, 0.f, 0.f, 0.f};
     if (hit) {
         float tmp[4] = {rgba_in[0], rgba_in[1], rgba_in[2], rgba_in[3]};
-        if (v.render_mode == SRF_MODE_COST) {
+        if (v.render_mode == SRF_MODE_NORMALS) {
+            const float nn = srf_norm3f(tmp[0], tmp[1], tmp[2]);
+            for (int i = 0; i < 3; ++i) tmp[i] = (0.5f * (nn > 0.f ? tmp[i] / nn : tmp[i]) + 0.5f) * tmp[3];
+        } else if (v.render_mode == SRF_MODE_COST) {
             const float col = (float)n_steps_total / 128;
             tmp[0] = tmp[1] = tmp[2] = col; tmp[3] = 1.0f;
         }

@@ -258,8 +258,8 @@ srf_status make_view(srf_ctx* ctx, const srf_view_t* view, DevView* v) {
     if (view->width == 0 || view->height == 0) return fail(ctx, SRF_ERR_ARG, "empty image");
     const uint32_t sc = view->shard_count ? view->shard_count : 1;
     if (view->shard_rank >= sc) return fail(ctx, SRF_ERR_ARG, "shard_rank >= shard_count");
-    if (view->render_mode == SRF_MODE_NORMALS)
-        return fail(ctx, SRF_ERR_ARG, "render mode Normals needs the network's input gradient, which this library does not provide");
+    if (view->render_mode == SRF_MODE_NORMALS && ctx->cfg.field_type != SRF_FIELD_NETWORK)
+        return fail(ctx, SRF_ERR_ARG, "render mode Normals needs the network field (it renders the density MLP's input gradient)");
     if (view->render_mode < 0 || view->render_mode > SRF_MODE_COST) return fail(ctx, SRF_ERR_ARG, "unknown render mode");
     memset(v, 0, sizeof(*v));
     memcpy(v->cam, view->camera, sizeof(v->cam));
@@ -930,6 +930,9 @@ static srf_status render_frame_impl(srf_ctx* ctx, const srf_view_t* view, const 
         if (blobs)
             launch_field_blobs(ctx->g, v, ctx->blobs, ctx->n_blobs, ctx->cmap, (const float4*)ctx->pool_pos.p, 0,
                                (float4*)ctx->pool_shaded.p, s, ctx->d_chunk_cursor);
+        else if (v.render_mode == SRF_MODE_NORMALS)
+            launch_field_normals(ctx->g, ctx->net, ctx->table, ctx->w_density, (const float4*)ctx->pool_pos.p, 0,
+                                 (float4*)ctx->pool_shaded.p, s, ctx->d_chunk_cursor);
         else if (ctx->use_tcgen05)
             launch_field_network_tc(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, (const float4*)ctx->pool_pos.p,
                                     (const uint32_t*)ctx->chunk_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, 0, nullptr,

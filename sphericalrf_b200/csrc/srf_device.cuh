@@ -503,6 +503,25 @@ __device__ __forceinline__ float network_to_density(float v, int act) {
     default: return 0.f;
     }
 }
+__device__ __forceinline__ float network_to_rgb_derivative(float v, int act) {          // common_device.h:331-340
+    switch (act) {
+    case SRF_ACT_NONE: return 1.0f;
+    case SRF_ACT_RELU: return v > 0.f ? 1.0f : 0.0f;
+    case SRF_ACT_LOGISTIC: { const float d = srf_logisticf(v); return d * (1.f - d); }
+    case SRF_ACT_EXPONENTIAL: return srf_expf(fminf(fmaxf(v, -10.f), 10.f));
+    default: return 0.f;
+    }
+}
+__device__ __forceinline__ float network_to_density_derivative(float v, int act) {      // common_device.h:353-362
+    switch (act) {
+    case SRF_ACT_NONE: return 1.0f;
+    case SRF_ACT_RELU: return v > 0.f ? 1.0f : 0.0f;
+    case SRF_ACT_LOGISTIC: { const float d = srf_logisticf(v); return d * (1.f - d); }
+    case SRF_ACT_EXPONENTIAL: return srf_expf(fminf(fmaxf(v, -15.f), 15.f));
+    default: return 0.f;
+    }
+}
+
 __device__ __forceinline__ float srf_powf(float x, float y) { return x > 0.f ? srf_expf(y * srf_logf(x)) : 0.f; }
 __device__ __forceinline__ float srgb_to_linear(float s) {
     return s <= 0.04045f ? s / 12.92f : srf_powf((s + 0.055f) / 1.055f, 2.4f);

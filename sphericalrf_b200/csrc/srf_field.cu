@@ -196,6 +196,109 @@ k_field_density(const NetMeta net, const __half* __restrict__ table, const __hal
     }
 }
 
+// Normals render mode (testbed.cu:557-559, ray_marcher.cu:250-255): per sample the density MLP's output 0 and its
+// gradient with respect to the warped position, in the canonical fp32 form:
+//   d enc[l,f] / d x_d = scale_l * sum over the 4 corner pairs along d of (w_a' * w_b') * (v_hi - v_lo);
+//   g_h[j] = W2[0][j] where hidden unit j (fp16, ReLU) is positive; g_enc[k] = sum_j W1[j][k] g_h[j];
+//   grad[d] = sum_k g_enc[k] * d enc[k] / d x_d.
+// One thread per sample, fp32 accumulation in index order (a diagnostic mode: no tensor cores).  The record
+// written is (unit normal, step opacity); the colour MLP is not evaluated.
+template <int F>
+__global__ void __launch_bounds__(128)
+k_field_normals(const DevCfg g, const NetMeta net, const __half* __restrict__ table, const __half* __restrict__ wd,
+                const float4* __restrict__ pos_dt, uint64_t n, float4* __restrict__ shaded, const uint32_t* __restrict__ n_chunks_dev) {
+    __shared__ __align__(16) float sW1[64 * 32];
+    __shared__ float sW2[64];
+    for (int i = threadIdx.x; i < 64 * 32; i += blockDim.x) sW1[i] = __half2float(wd[i]);
+    for (int i = threadIdx.x; i < 64; i += blockDim.x) sW2[i] = __half2float(wd[64 * 32 + i]);
+    __syncthreads();
+    if (n_chunks_dev) n = (uint64_t)(*n_chunks_dev) * kChunkSamples;
+    const uint32_t* table32 = reinterpret_cast<const uint32_t*>(table);
+    for (uint64_t s = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; s < n; s += (uint64_t)gridDim.x * blockDim.x) {
+        const float4 p = pos_dt[s];
+        const float x3[3] = {p.x, p.y, p.z};
+        float enc[32], dydx[32][3];
+        for (uint32_t l = 0; l < net.n_levels; ++l) {
+            const LevelMeta L = net.level[l];
+            float w[3]; uint32_t ig[3];
+            for (int d = 0; d < 3; ++d) {
+                const float q = fmaf(L.scale, x3[d], 0.5f);
+                const float fl = floorf(q);
+                w[d] = q - fl;
+                ig[d] = (uint32_t)srf_f2i_rz(fl);
+            }
+            float v[8][F], acc[F];
+#pragma unroll
+            for (int f = 0; f < F; ++f) acc[f] = 0.f;
+#pragma unroll
+            for (uint32_t c = 0; c < 8; ++c) {
+                const uint32_t gx = ig[0] + (c & 1u), gy = ig[1] + ((c >> 1) & 1u), gz = ig[2] + (c >> 2);
+                const float wt = (((c & 1u) ? w[0] : 1.f - w[0]) * ((c & 2u) ? w[1] : 1.f - w[1])) * ((c & 4u) ? w[2] : 1.f - w[2]);
+                uint32_t idx = L.dense ? gx + gy * L.res + gz * L.res * L.res : (gx ^ (gy * 2654435761u) ^ (gz * 805459861u));
+                idx %= L.size;
+                const uint32_t* e = table32 + (size_t)(L.offset + idx) * (F / 2);
+#pragma unroll
+                for (int f2 = 0; f2 < F / 2; ++f2) {
+                    const uint32_t raw = __ldg(e + f2);
+                    const __half2 h = *reinterpret_cast<const __half2*>(&raw);
+                    v[c][2 * f2] = __low2float(h); v[c][2 * f2 + 1] = __high2float(h);
+                }
+#pragma unroll
+                for (int f = 0; f < F; ++f) acc[f] = fmaf(wt, v[c][f], acc[f]);
+            }
+#pragma unroll
+            for (int f = 0; f < F; ++f) enc[l * F + f] = __half2float(__float2half_rn(acc[f]));
+#pragma unroll
+            for (int d = 0; d < 3; ++d) {
+                const int a = d == 0 ? 1 : 0, b = d == 2 ? 1 : 2;
+#pragma unroll
+                for (int f = 0; f < F; ++f) {
+                    float gs = 0.f;
+#pragma unroll
+                    for (uint32_t c2 = 0; c2 < 4; ++c2) {
+                        const uint32_t ba = c2 & 1u, bb = c2 >> 1;
+                        const float wt = (ba ? w[a] : 1.f - w[a]) * (bb ? w[b] : 1.f - w[b]);
+                        const uint32_t lo = (ba << a) | (bb << b), hi = lo | (1u << d);
+                        gs = fmaf(wt, v[hi][f] - v[lo][f], gs);
+                    }
+                    dydx[l * F + f][d] = L.scale * gs;
+                }
+            }
+        }
+        float g_enc[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) g_enc[k] = 0.f;
+        float out0 = 0.f;
+        for (int o = 0; o < 64; ++o) {
+            const float* wrow = sW1 + o * 32;
+            float acc = 0.f;
+#pragma unroll
+            for (int k = 0; k < 32; ++k) acc = fmaf(wrow[k], enc[k], acc);
+            if (!(acc > 0.f)) acc = 0.f;
+            const float h = __half2float(__float2half_rn(acc));
+            out0 = fmaf(sW2[o], h, out0);
+            const float gh = h > 0.f ? sW2[o] : 0.f;
+#pragma unroll
+            for (int k = 0; k < 32; ++k) g_enc[k] = fmaf(wrow[k], gh, g_enc[k]);      // j ascending for every k
+        }
+        const float raw_sigma = __half2float(__float2half_rn(out0));
+        float grad[3];
+#pragma unroll
+        for (int d = 0; d < 3; ++d) {
+            float acc = 0.f;
+#pragma unroll
+            for (int k = 0; k < 32; ++k) acc = fmaf(g_enc[k], dydx[k][d], acc);
+            grad[d] = acc;
+        }
+        const float dd = -network_to_density_derivative(raw_sigma, g.density_activation);
+        float nx = dd * grad[0], ny = dd * grad[1], nz = dd * grad[2];
+        const float nn = srf_norm3f(nx, ny, nz);
+        if (nn > 0.f) { nx /= nn; ny /= nn; nz /= nn; }
+        const float alpha = 1.f - srf_expf(-network_to_density(raw_sigma, g.density_activation) * p.w);
+        shaded[s] = make_float4(nx, ny, nz, alpha);
+    }
+}
+
 // Analytic stand-in scene, fp32, one thread per sample.
 __global__ void __launch_bounds__(256)
 k_field_blobs(const DevCfg g, const DevView v, const float* __restrict__ blobs, uint32_t n_blobs, const float* __restrict__ cmap,
@@ -257,6 +360,19 @@ void launch_field_density(const NetMeta& net, const __half* table, const __half*
         k_field_density<2><<<grid, kFieldBlock, 0, stream>>>(net, table, w_density, positions, stride, n, out16);
     else
         k_field_density<4><<<grid, kFieldBlock, 0, stream>>>(net, table, w_density, positions, stride, n, out16);
+}
+
+void launch_field_normals(const DevCfg& g, const NetMeta& net, const __half* table, const __half* w_density, const float4* pos_dt,
+                          uint64_t n, float4* shaded, cudaStream_t stream, const uint32_t* n_chunks_dev) {
+    if (n == 0 && !n_chunks_dev) return;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const uint64_t want = n_chunks_dev ? ~0ull >> 8 : (n + 127) / 128;
+    const uint64_t cap = (uint64_t)sms * 8;
+    const unsigned int grid = (unsigned int)(want < cap ? want : cap);
+    if (net.n_features == 2) k_field_normals<2><<<grid, 128, 0, stream>>>(g, net, table, w_density, pos_dt, n, shaded, n_chunks_dev);
+    else k_field_normals<4><<<grid, 128, 0, stream>>>(g, net, table, w_density, pos_dt, n, shaded, n_chunks_dev);
 }
 
 void launch_field_blobs(const DevCfg& g, const DevView& v, const float* blobs, uint32_t n_blobs, const float* color_map,

@@ -95,6 +95,10 @@ void launch_field_blobs(const DevCfg& g, const DevView& v, const float* blobs, u
                         const float4* pos_dt, uint64_t n, float4* shaded, cudaStream_t stream,
                         const uint32_t* n_chunks_dev = nullptr);
 
+//   Normals render mode: (unit normal from the density MLP's input gradient, step opacity) per sample.
+void launch_field_normals(const DevCfg& g, const NetMeta& net, const __half* table, const __half* w_density, const float4* pos_dt,
+                          uint64_t n, float4* shaded, cudaStream_t stream, const uint32_t* n_chunks_dev = nullptr);
+
 struct DevPost {
     float exposure_scale;      // 2^exposure
     float bg[4];               // background colour, already converted to the accumulation space

@@ -15,25 +15,6 @@ namespace {
 
 constexpr int kLossBlock = 128;
 
-__device__ __forceinline__ float network_to_rgb_derivative(float v, int act) {          // common_device.h:331-340
-    switch (act) {
-    case SRF_ACT_NONE: return 1.0f;
-    case SRF_ACT_RELU: return v > 0.f ? 1.0f : 0.0f;
-    case SRF_ACT_LOGISTIC: { const float d = srf_logisticf(v); return d * (1.f - d); }
-    case SRF_ACT_EXPONENTIAL: return srf_expf(fminf(fmaxf(v, -10.f), 10.f));
-    default: return 0.f;
-    }
-}
-__device__ __forceinline__ float network_to_density_derivative(float v, int act) {      // common_device.h:353-362
-    switch (act) {
-    case SRF_ACT_NONE: return 1.0f;
-    case SRF_ACT_RELU: return v > 0.f ? 1.0f : 0.0f;
-    case SRF_ACT_LOGISTIC: { const float d = srf_logisticf(v); return d * (1.f - d); }
-    case SRF_ACT_EXPONENTIAL: return srf_expf(fminf(fmaxf(v, -15.f), 15.f));
-    default: return 0.f;
-    }
-}
-
 // One channel of loss_and_gradient (internal/utils/loss.cu:18-101).
 __device__ __forceinline__ void loss_channel(int type, float target, float pred, float* loss, float* grad) {
     const float d = pred - target;

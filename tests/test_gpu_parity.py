@@ -122,6 +122,32 @@ def test_early_termination_bit_exact(built_lib, oracle_mod):
     assert _bits_equal(got["rgba_raw"], ref["rgba_raw"])
 
 
+@pytest.mark.parametrize("levels,features", [(16, 2), (8, 4)])
+def test_normals_mode_bit_exact(built_lib, oracle_mod, levels, features):
+    """Render mode Normals: density gradient through hash grid and density MLP in fp32, composited and shaded
+    as testbed.cu:463-465 does.  The fp32 path has a fixed operation order, so the frame is the oracle's."""
+    sc = small_scene(kind="net", width=20, height=12)
+    cfg = sc["cfg"]
+    cfg.n_levels, cfg.n_features_per_level = levels, features
+    if features == 4:
+        cfg.per_level_scale = 2.0
+        from sphericalrf_b200 import synth
+        sc["hash_table"], sc["density_mlp"], sc["rgb_mlp"] = synth.network_params(cfg, 11, 12, table_range=0.5)
+    sc["view"].render_mode = abi.MODE_NORMALS
+    r = make_renderer(sc)
+    orc = make_oracle(oracle_mod, sc, r.download_bitfield())
+    post = abi.default_post()
+    got = r.render_frame(sc["view"], post, want_raw=True)
+    ref = orc.render_frame(sc["view"], post)
+    assert _bits_equal(got["rgba_raw"], ref["rgba_raw"])
+    assert _bits_equal(got["out"], ref["out"])
+    hit = ref["rgba_raw"][:, 3] > 0.05
+    assert hit.any()
+    # shaded normals: 0.5 n + 0.5 scaled by the opacity, so every channel lies in [0, A]
+    assert (ref["out"][hit, :3] >= 0).all() and (ref["out"][hit, :3] <= ref["out"][hit, 3:4] + 1e-6).all()
+    assert np.ptp(ref["out"][hit, :3], axis=0).min() > 1e-3          # and they vary over the image
+
+
 @pytest.fixture(params=["tcgen05", "mma_sync"])
 def mlp_engine(request, monkeypatch):
     """Both MLP engines of the render path: tcgen05/TMEM (the default) and the mma.sync kernel."""
@@ -303,10 +329,11 @@ def test_errors_are_reported_not_faked(built_lib):
     with pytest.raises(abi.SrfError) as e:      # no weights uploaded
         r.render_frame(sc["view"], abi.default_post())
     assert e.value.status == abi.ERR_STATE
-    sc["view"].render_mode = abi.MODE_NORMALS
-    r.upload_network(sc["hash_table"], sc["density_mlp"], sc["rgb_mlp"])
+    sb = small_scene(kind="blobs")
+    sb["view"].render_mode = abi.MODE_NORMALS                 # Normals is the density MLP's input gradient: network field only
+    rb = make_renderer(sb)
     with pytest.raises(abi.SrfError) as e:
-        r.render_frame(sc["view"], abi.default_post())
+        rb.render_frame(sb["view"], abi.default_post())
     assert e.value.status == abi.ERR_ARG
 
 
