@@ -328,6 +328,66 @@ def run_ours(args):
         "stage_ms": {"sampler": t_sampler, "field": t_field, "composite_output": t_comp},
     }
     if world == 1 and cfg.field_type == abi.FIELD_NETWORK:
+        # training-side kernels on the same scene: one batch of Testbed::train_nerf_step's data path
+        # (testbed.cu:317-380) -- sample 4096 training rays (<= 1024 samples each, 4 Mi sample slots), evaluate
+        # the network on them, composite with loss and gradient into a 2^18-sample compacted batch
+        from sphericalrf_b200 import synth
+        tviews = synth.training_views(5000, n_images=8, width=400, height=400, radius=0.5, fov_deg=60.0, zero_probability=0.05)
+        tv, keep = r._device_views(tviews)
+        n_tr, n_coords, n_comp = 4096, 1 << 22, 1 << 18
+        ctr = torch.zeros(4, dtype=torch.int32, device=dev)
+        t_rays = torch.zeros((n_tr, 6), device=dev); t_rgba = torch.zeros((n_tr, 4), device=dev)
+        t_idx = torch.zeros((n_tr, 2), dtype=torch.int32, device=dev); t_idx0 = torch.zeros_like(t_idx)
+        t_coords = torch.zeros((n_coords, 7), device=dev); t_out = torch.zeros((n_coords, 4), dtype=torch.float16, device=dev)
+        t_cc = torch.zeros((n_comp, 7), device=dev); t_dl = torch.zeros((n_comp, 4), dtype=torch.float16, device=dev)
+        t_loss = torch.zeros(n_tr, device=dev)
+        lp = abi.LossParams()
+        lp.n_rays, lp.n_max_compacted_coords, lp.loss_type, lp.loss_scale = n_tr, n_comp, abi.LOSS_SMOOTH_L1, 128.0
+        lp.background_color[:] = [1.0, 1.0, 1.0]
+        lp.color_space, lp.train_with_random_bg_color, lp.padded_output_width = abi.COLOR_SRGB, 1, 4
+        lp.rng_state, lp.rng_inc = 0x853c49e6748fea9b, 0xda3e39cb94b95bdb
+        P = lambda t, off=0: C.c_void_p(t.data_ptr() + off)
+        n_used = [0]
+
+        def train_sample():
+            st = r.lib.srf_sample_training_rays(r.ctx, C.byref(tv), n_tr, 0, n_coords, lp.rng_state, lp.rng_inc, 1, P(ctr), P(ctr, 4),
+                                                P(t_rays), P(t_rgba), P(t_idx0), P(t_coords), None)
+            assert st == 0, r.lib.srf_last_error(r.ctx)
+
+        def train_infer():
+            st = r.lib.srf_network_inference(r.ctx, P(t_coords), n_used[0], P(t_out), None)
+            assert st == 0, r.lib.srf_last_error(r.ctx)
+
+        def train_loss():
+            t_idx.copy_(t_idx0)                      # the compositor rewrites the (count, base) pairs
+            st = r.lib.srf_volume_rendering_loss(r.ctx, C.byref(lp), P(ctr), P(t_idx), P(t_rgba), P(t_coords), P(t_out), P(t_cc),
+                                                 P(ctr, 8), P(t_dl), P(t_loss), None, None)
+            assert st == 0, r.lib.srf_last_error(r.ctx)
+
+        def ms_of(fn, reps=5):
+            fn(); fn()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize(); a.record()
+            for _ in range(reps):
+                fn()
+            b.record(); torch.cuda.synchronize()
+            return a.elapsed_time(b) / reps
+
+        ms_s = ms_of(train_sample)
+        kept, total = int(ctr[0].item()), int(ctr[1].item())
+        n_used[0] = min(total, n_coords)
+        ms_i = ms_of(train_infer)
+        ms_l = ms_of(train_loss)
+        line["training_side"] = {
+            "rays": n_tr, "rays_kept": kept, "samples": total, "samples_compacted": int(ctr[2].item()),
+            "ms_sample_rays": ms_s, "ms_network_inference": ms_i, "ms_loss_and_gradient": ms_l,
+            "sampler_msamples_per_s": total / (ms_s * 1e-3) / 1e6, "inference_msamples_per_s": n_used[0] / (ms_i * 1e-3) / 1e6,
+            # sampler: 28 B/sample + 80 B/ray; compositor forward+backward: 2 x (8 + 4) B read per sample + 28 B copied and
+            # 8 B gradient written per compacted sample
+            "sampler_algorithmic_gbs": (28.0 * total + 80.0 * n_tr) / (ms_s * 1e-3) / 1e9,
+            "loss_algorithmic_gbs": (24.0 * total + 64.0 * int(ctr[2].item())) / (ms_l * 1e-3) / 1e9,
+        }
+    if world == 1 and cfg.field_type == abi.FIELD_NETWORK:
         # density-grid refresh (Testbed::train_prep_nerf): 16 consecutive refreshes of the 128^3 grid, all-cells mode
         r.refresh_reset(3001)
         for _ in range(2):

@@ -53,33 +53,53 @@ __device__ __forceinline__ Sample4 load_output(const uint2* out, uint64_t k) {
     return {__low2float(a), __high2float(a), __low2float(b), __high2float(b)};
 }
 
+// Both kernels give a warp to each ray.  The lanes load 32 consecutive samples of the ray at a time (coalesced)
+// and evaluate the activations and the opacity of their own sample in parallel; the short recurrence over the
+// samples (T, the colour sums) is then replayed in sample order by every lane from shuffled values, so each
+// floating-point operation is the one the reference's single thread performs, in the same order.
+
 // Forward pass (:57-80 and :113-116): composites until the transmittance threshold, records the number of
 // samples consumed and the ray colour (background included when the ray ran through all its samples).
 __global__ void __launch_bounds__(kLossBlock)
 k_loss_forward(const DevCfg g, const LossParams lp, const uint32_t* __restrict__ n_rays_counter,
                const uint32_t* __restrict__ ray_coord_indices, const float* __restrict__ coords, const uint2* __restrict__ net_out,
                uint32_t* __restrict__ consumed, float4* __restrict__ ray_rgb, uint32_t n_slots) {
-    const uint32_t i = blockIdx.x * kLossBlock + threadIdx.x;
+    const uint32_t i = (blockIdx.x * kLossBlock + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
     if (i >= n_slots) return;
-    if (i >= *n_rays_counter) { consumed[i] = 0; return; }
+    if (i >= *n_rays_counter) { if (lane == 0) consumed[i] = 0; return; }
     const uint32_t numsteps = ray_coord_indices[i * 2 + 0], base = ray_coord_indices[i * 2 + 1];
     float T = 1.f, r = 0.f, gg = 0.f, b = 0.f;
     uint32_t n = 0;
-    for (; n < numsteps; ++n) {
-        if (T < lp.transmittance_threshold) break;
-        const Sample4 o = load_output(net_out, (uint64_t)base + n);
-        const float density = network_to_density(o.s, g.density_activation);
-        const float dt = coords[((uint64_t)base + n) * 7 + 3];
-        const float alpha = 1.f - srf_expf(-density * dt);
-        const float weight = alpha * T;
-        r += weight * network_to_rgb(o.r, g.rgb_activation);
-        gg += weight * network_to_rgb(o.g, g.rgb_activation);
-        b += weight * network_to_rgb(o.b, g.rgb_activation);
-        T *= (1.f - alpha);
+    bool stopped = false;
+    for (uint32_t b0 = 0; b0 < numsteps && !stopped; b0 += 32) {
+        float alpha = 0.f, cr = 0.f, cg = 0.f, cb = 0.f;
+        if (b0 + lane < numsteps) {
+            const uint64_t k = (uint64_t)base + b0 + lane;
+            const Sample4 o = load_output(net_out, k);
+            const float density = network_to_density(o.s, g.density_activation);
+            alpha = 1.f - srf_expf(-density * coords[k * 7 + 3]);
+            cr = network_to_rgb(o.r, g.rgb_activation);
+            cg = network_to_rgb(o.g, g.rgb_activation);
+            cb = network_to_rgb(o.b, g.rgb_activation);
+        }
+        const int cnt = (int)min(32u, numsteps - b0);
+        for (int j = 0; j < cnt; ++j) {
+            if (T < lp.transmittance_threshold) { stopped = true; break; }
+            const float a_j = __shfl_sync(0xffffffffu, alpha, j);
+            const float weight = a_j * T;
+            r += weight * __shfl_sync(0xffffffffu, cr, j);
+            gg += weight * __shfl_sync(0xffffffffu, cg, j);
+            b += weight * __shfl_sync(0xffffffffu, cb, j);
+            T *= (1.f - a_j);
+            ++n;
+        }
     }
     if (n == numsteps) { r += T * lp.bg_final[0]; gg += T * lp.bg_final[1]; b += T * lp.bg_final[2]; }
-    consumed[i] = n;
-    ray_rgb[i] = make_float4(r, gg, b, T);
+    if (lane == 0) {
+        consumed[i] = n;
+        ray_rgb[i] = make_float4(r, gg, b, T);
+    }
 }
 
 // Loss and backward pass (:118-201).
@@ -90,15 +110,19 @@ k_loss_backward(const DevCfg g, const LossParams lp, const uint32_t* __restrict_
                 const float4* __restrict__ ray_rgb, const float* __restrict__ mean_density, float* __restrict__ compacted_coords,
                 uint32_t* __restrict__ n_compacted_counter, __half* __restrict__ dloss_doutput, float* __restrict__ loss_output,
                 float* __restrict__ reg_distortion, uint32_t n_slots) {
-    const uint32_t i = blockIdx.x * kLossBlock + threadIdx.x;
-    if (i == 0) *n_compacted_counter = (uint32_t)bases[n_slots];
+    const uint32_t i = (blockIdx.x * kLossBlock + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (i == 0 && lane == 0) *n_compacted_counter = (uint32_t)bases[n_slots];
     if (i >= n_slots || i >= *n_rays_counter) return;
     const uint32_t base = ray_coord_indices[i * 2 + 1];
     const uint32_t compacted_base = (uint32_t)bases[i];
     const uint32_t n_max = lp.n_max_compacted_coords;
     const uint32_t n = min(n_max - min(n_max, compacted_base), consumed[i]);                   // :122
-    ray_coord_indices[i * 2 + 0] = n;
-    ray_coord_indices[i * 2 + 1] = compacted_base;
+    __syncwarp();                                      // every lane has read the old (count, base) pair
+    if (lane == 0) {
+        ray_coord_indices[i * 2 + 0] = n;
+        ray_coord_indices[i * 2 + 1] = compacted_base;
+    }
     if (n == 0) return;
 
     // ground-truth colour (:88-111)
@@ -121,54 +145,73 @@ k_loss_backward(const DevCfg g, const LossParams lp, const uint32_t* __restrict_
     float loss[3], grad[3];
     for (int c = 0; c < 3; ++c) loss_channel(lp.loss_type, target[c], rgb_ray[c], &loss[c], &grad[c]);
     const float n_rays_f = (float)lp.n_rays;
-    if (loss_output) loss_output[i] = ((loss[0] + loss[1]) + loss[2]) / 3.0f / n_rays_f;
+    if (loss_output && lane == 0) loss_output[i] = ((loss[0] + loss[1]) + loss[2]) / 3.0f / n_rays_f;
     const float loss_scale = lp.loss_scale / n_rays_f;
     const float output_l2_reg = g.rgb_activation == SRF_ACT_EXPONENTIAL ? 1e-4f : 0.0f;
     const float output_l1_reg_density = (g.use_grid && (*mean_density < lp.min_optical_thickness)) ? 1e-4f : 0.0f;
 
-    if (reg_distortion) {                                                                     // :137-163
-        float T = 1.f, sum_w = 0.f, sum_wp = 0.f;
-        float* rd = reg_distortion + (uint64_t)compacted_base * 2;
-        for (uint32_t j = 0; j < n; ++j) {
-            const Sample4 o = load_output(net_out, (uint64_t)base + j);
-            const float dt = coords[((uint64_t)base + j) * 7 + 3];
-            const float alpha = 1.f - srf_expf(-network_to_density(o.s, g.density_activation) * dt);
-            const float weight = alpha * T;       // T is not advanced in this loop of the reference
-            sum_w += weight;
-            sum_wp += weight * (float)(j + 1) / (float)n;
-            rd[2 * j] = sum_w;
-            rd[2 * j + 1] = sum_wp;
-        }
-    }
-
     float T = 1.f, r2[3] = {0.f, 0.f, 0.f};
-    float* cc = compacted_coords + (uint64_t)compacted_base * 7;
-    __half* dl = dloss_doutput + (uint64_t)compacted_base * lp.padded_output_width;
-    for (uint32_t j = 0; j < n; ++j) {
-        const float* c = coords + ((uint64_t)base + j) * 7;
-        for (int k = 0; k < 7; ++k) cc[(uint64_t)j * 7 + k] = c[k];
-        const float dt = c[3];
-        const Sample4 o = load_output(net_out, (uint64_t)base + j);
-        const float raw[3] = {o.r, o.g, o.b};
-        float rgb[3];
-        for (int k = 0; k < 3; ++k) rgb[k] = network_to_rgb(raw[k], g.rgb_activation);
-        const float density = network_to_density(o.s, g.density_activation);
-        const float alpha = 1.f - srf_expf(-density * dt);
-        const float weight = alpha * T;
-        for (int k = 0; k < 3; ++k) r2[k] += weight * rgb[k];
-        T *= (1.f - alpha);
-        float out[4];
-        float v[3];
-        for (int k = 0; k < 3; ++k) {
-            const float dloss_by_drgb = weight * grad[k];
-            out[k] = loss_scale * (dloss_by_drgb * network_to_rgb_derivative(raw[k], g.rgb_activation) + fmaxf(0.0f, output_l2_reg * raw[k]));
-            v[k] = T * rgb[k] - (rgb_ray[k] - r2[k]);                                         // T * rgb - suffix
+    float sum_w = 0.f, sum_wp = 0.f;                       // distortion sums (:137-163; T stays 1 in that loop)
+    for (uint32_t b0 = 0; b0 < n; b0 += 32) {
+        const uint32_t j_mine = b0 + lane;
+        const bool have = j_mine < n;
+        const uint64_t k = (uint64_t)base + j_mine;
+        Sample4 o = {0.f, 0.f, 0.f, 0.f};
+        float dt = 0.f, alpha = 0.f, rgb[3] = {0.f, 0.f, 0.f};
+        if (have) {
+            o = load_output(net_out, k);
+            dt = coords[k * 7 + 3];
+            alpha = 1.f - srf_expf(-network_to_density(o.s, g.density_activation) * dt);
+            rgb[0] = network_to_rgb(o.r, g.rgb_activation);
+            rgb[1] = network_to_rgb(o.g, g.rgb_activation);
+            rgb[2] = network_to_rgb(o.b, g.rgb_activation);
         }
-        const float dot = fmaf(grad[2], v[2], fmaf(grad[1], v[1], grad[0] * v[0]));
-        const float dloss_by_dmlp = network_to_density_derivative(o.s, g.density_activation) * (dt * dot);
-        out[3] = loss_scale * dloss_by_dmlp + (o.s < 0.f ? -output_l1_reg_density : 0.0f);
-        __half* d = dl + (uint64_t)j * lp.padded_output_width;
-        for (int k = 0; k < 4; ++k) d[k] = __float2half_rn(out[k]);
+        // replay the recurrence; lane j keeps the state right after its own sample
+        float my_T = 0.f, my_w = 0.f, my_r2[3] = {0.f, 0.f, 0.f}, my_sw = 0.f, my_swp = 0.f;
+        const int cnt = (int)min(32u, n - b0);
+        for (int j = 0; j < cnt; ++j) {
+            const float a_j = __shfl_sync(0xffffffffu, alpha, j);
+            const float weight = a_j * T;
+            r2[0] += weight * __shfl_sync(0xffffffffu, rgb[0], j);
+            r2[1] += weight * __shfl_sync(0xffffffffu, rgb[1], j);
+            r2[2] += weight * __shfl_sync(0xffffffffu, rgb[2], j);
+            T *= (1.f - a_j);
+            if (reg_distortion) {
+                const float w1 = a_j * 1.f;
+                sum_w += w1;
+                sum_wp += w1 * (float)(b0 + j + 1) / (float)n;
+            }
+            if (j == lane) { my_T = T; my_w = weight; my_r2[0] = r2[0]; my_r2[1] = r2[1]; my_r2[2] = r2[2]; my_sw = sum_w; my_swp = sum_wp; }
+        }
+        // 28-byte coordinate records of these samples, copied by the whole warp
+        {
+            const float* src = coords + ((uint64_t)base + b0) * 7;
+            float* dst = compacted_coords + ((uint64_t)compacted_base + b0) * 7;
+            for (int q = lane; q < cnt * 7; q += 32) dst[q] = src[q];
+        }
+        if (have) {
+            if (reg_distortion) {
+                float* rd = reg_distortion + ((uint64_t)compacted_base + j_mine) * 2;
+                rd[0] = my_sw; rd[1] = my_swp;
+            }
+            const float raw[3] = {o.r, o.g, o.b};
+            float out[4], v[3];
+            for (int c = 0; c < 3; ++c) {
+                const float dloss_by_drgb = my_w * grad[c];
+                out[c] = loss_scale * (dloss_by_drgb * network_to_rgb_derivative(raw[c], g.rgb_activation) + fmaxf(0.0f, output_l2_reg * raw[c]));
+                v[c] = my_T * rgb[c] - (rgb_ray[c] - my_r2[c]);                               // T * rgb - suffix
+            }
+            const float dot = fmaf(grad[2], v[2], fmaf(grad[1], v[1], grad[0] * v[0]));
+            const float dloss_by_dmlp = network_to_density_derivative(o.s, g.density_activation) * (dt * dot);
+            out[3] = loss_scale * dloss_by_dmlp + (o.s < 0.f ? -output_l1_reg_density : 0.0f);
+            __half* d = dloss_doutput + ((uint64_t)compacted_base + j_mine) * lp.padded_output_width;
+            const __half2 h01 = __floats2half2_rn(out[0], out[1]), h23 = __floats2half2_rn(out[2], out[3]);
+            if ((lp.padded_output_width & 3u) == 0 && (reinterpret_cast<uintptr_t>(dloss_doutput) & 7u) == 0) {
+                *reinterpret_cast<uint2*>(d) = make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+            } else {
+                d[0] = __low2half(h01); d[1] = __high2half(h01); d[2] = __low2half(h23); d[3] = __high2half(h23);
+            }
+        }
     }
 }
 
@@ -178,7 +221,7 @@ void launch_loss_forward(const DevCfg& g, const LossParams& lp, const uint32_t* 
                          const float* coords, const uint2* net_out, uint32_t* consumed, float4* ray_rgb, uint32_t n_slots,
                          cudaStream_t stream) {
     if (n_slots == 0) return;
-    k_loss_forward<<<(n_slots + kLossBlock - 1) / kLossBlock, kLossBlock, 0, stream>>>(g, lp, n_rays_counter, ray_coord_indices, coords,
+    k_loss_forward<<<(unsigned int)(((uint64_t)n_slots * 32 + kLossBlock - 1) / kLossBlock), kLossBlock, 0, stream>>>(g, lp, n_rays_counter, ray_coord_indices, coords,
                                                                                       net_out, consumed, ray_rgb, n_slots);
 }
 
@@ -188,7 +231,7 @@ void launch_loss_backward(const DevCfg& g, const LossParams& lp, const uint32_t*
                           uint32_t* n_compacted_counter, __half* dloss_doutput, float* loss_output, float* reg_distortion,
                           uint32_t n_slots, cudaStream_t stream) {
     if (n_slots == 0) return;
-    k_loss_backward<<<(n_slots + kLossBlock - 1) / kLossBlock, kLossBlock, 0, stream>>>(
+    k_loss_backward<<<(unsigned int)(((uint64_t)n_slots * 32 + kLossBlock - 1) / kLossBlock), kLossBlock, 0, stream>>>(
         g, lp, n_rays_counter, ray_coord_indices, coords, net_out, rays_rgba, consumed, bases, ray_rgb, mean_density, compacted_coords,
         n_compacted_counter, dloss_doutput, loss_output, reg_distortion, n_slots);
 }

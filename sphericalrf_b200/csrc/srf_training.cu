@@ -5,7 +5,7 @@
 //
 // The reference's training sampler reserves each ray's slots with atomicAdd on two global counters, so the
 // order of rays and samples in its output changes from run to run.  Here the same per-ray work is split into
-// a counting march, two exclusive scans (samples per ray -> base; "has samples" -> compacted ray index) and
+// a counting march (a warp per ray: see train_march_warp), two exclusive scans (samples per ray -> base; "has samples" -> compacted ray index) and
 // an emitting march: the output is the one a serial execution of the reference kernel (ray 0, 1, 2, ...)
 // would produce, every time, and sample writes of neighbouring rays land next to each other.
 #include "srf_kernels.cuh"
@@ -14,7 +14,6 @@ namespace srf {
 
 namespace {
 
-constexpr int kTrainBlock = 128;
 
 __device__ __forceinline__ float dot3(const V3& a, const float* b) {
     return fmaf(a.z, b[2], fmaf(a.y, b[1], a.x * b[0]));
@@ -107,67 +106,94 @@ __device__ __forceinline__ TrainRay train_ray_setup(const DevCfg& g, const Train
     return r;
 }
 
-// The two marches of the reference kernel (:596-628 and :650-688): emit(w, dt) for each of at most `limit`
-// occupied steps.  Returns the number of occupied steps.
+// The two marches of the reference kernel (:596-628 and :650-688), run by a whole warp for one ray.  The
+// recurrence t += calc_dt(t) is cheap and inherently serial: every lane replays 32 steps of it and keeps the t
+// of "its" step; the expensive part of a step (box test, warp, level, bit lookup) then runs on the 32 steps in
+// parallel, and ballots give each occupied step its index within the ray.  The values of t, dt and the
+// positions are exactly those of the serial loop; emit(j, w, dt) is called by the lane that owns occupied step
+// j, for j < limit.  Returns the number of occupied steps (the same in all lanes), at most `limit`.
 template <class Emit>
-__device__ __forceinline__ uint32_t train_march(const DevCfg& g, const uint8_t* __restrict__ bits, const TrainRay& r,
-                                                uint32_t limit, Emit emit) {
+__device__ __forceinline__ uint32_t train_march_warp(const DevCfg& g, const uint8_t* __restrict__ bits, const TrainRay& r,
+                                                     uint32_t limit, Emit emit) {
+    const int lane = threadIdx.x & 31;
     uint32_t j = 0;
     float t = r.t;
-    for (uint32_t it = 0; it < g.step_limit && j < limit; ++it) {
-        const V3 pos = mk3(fmaf(r.d.x, t, r.o.x), fmaf(r.d.y, t, r.o.y), fmaf(r.d.z, t, r.o.z));
-        if (!box_contains(g, pos)) break;
-        const float dt = calc_dt(g, t);
-        V3 w;
-        uint32_t idx;
-        if (grid_lookup(g, bits, pos, &w, &idx)) {
-            emit(j, w, dt);
-            ++j;
+    for (uint32_t block = 0; block < (g.step_limit >> 5) && j < limit; ++block) {
+        float my_t = 0.f, my_dt = 0.f;
+#pragma unroll 4
+        for (int k = 0; k < 32; ++k) {
+            const float dt = calc_dt(g, t);
+            if (k == lane) { my_t = t; my_dt = dt; }
+            t += dt;
         }
-        t += dt;
-        if (dt == 0.f) break;
+        const V3 pos = mk3(fmaf(r.d.x, my_t, r.o.x), fmaf(r.d.y, my_t, r.o.y), fmaf(r.d.z, my_t, r.o.z));
+        const bool inside = box_contains(g, pos);
+        const unsigned out_mask = __ballot_sync(0xffffffffu, !inside);          // the loop ends before the first such step
+        const unsigned zero_mask = __ballot_sync(0xffffffffu, my_dt == 0.f);    // and after the first step with dt == 0
+        unsigned valid = out_mask ? ((1u << (__ffs(out_mask) - 1)) - 1u) : 0xffffffffu;
+        if (zero_mask) {
+            const int z = __ffs(zero_mask) - 1;
+            valid &= (z == 31) ? 0xffffffffu : ((2u << z) - 1u);
+        }
+        const bool mine = (valid >> lane) & 1u;
+        V3 w = mk3(0.f, 0.f, 0.f);
+        uint32_t idx;
+        bool occ = false;
+        if (mine) occ = grid_lookup(g, bits, pos, &w, &idx);
+        const unsigned occ_mask = __ballot_sync(0xffffffffu, occ);
+        const uint32_t my_j = j + __popc(occ_mask & ((1u << lane) - 1u));
+        if (occ && my_j < limit) emit(my_j, w, my_dt);
+        j += __popc(occ_mask);
+        if (valid != 0xffffffffu) break;
     }
-    return j;
+    return j < limit ? j : limit;
 }
 
-__global__ void __launch_bounds__(kTrainBlock)
+constexpr int kTrainWarpBlock = 128;      // 4 rays per block
+
+__global__ void __launch_bounds__(kTrainWarpBlock)
 k_train_count(const DevCfg g, const TrainViews tv, const uint8_t* __restrict__ bits, uint32_t n_rays, uint32_t n_rays_shift,
               uint32_t n_max_steps, Pcg rng, int snap, uint32_t* __restrict__ counts, uint32_t* __restrict__ flags) {
-    const uint32_t i = blockIdx.x * kTrainBlock + threadIdx.x;
+    const uint32_t i = (blockIdx.x * kTrainWarpBlock + threadIdx.x) >> 5;
     if (i >= n_rays) return;
     const TrainRay r = train_ray_setup(g, tv, i, n_rays, n_rays_shift, rng, snap);
     uint32_t n = 0;
-    if (r.valid) n = train_march(g, bits, r, n_max_steps, [](uint32_t, const V3&, float) {});
-    counts[i] = n;
-    flags[i] = n ? 1u : 0u;
+    if (r.valid) n = train_march_warp(g, bits, r, n_max_steps, [](uint32_t, const V3&, float) {});
+    if ((threadIdx.x & 31) == 0) {
+        counts[i] = n;
+        flags[i] = n ? 1u : 0u;
+    }
 }
 
-__global__ void __launch_bounds__(kTrainBlock)
+__global__ void __launch_bounds__(kTrainWarpBlock)
 k_train_emit(const DevCfg g, const TrainViews tv, const uint8_t* __restrict__ bits, uint32_t n_rays, uint32_t n_rays_shift,
              uint32_t n_coords, Pcg rng, int snap, const uint32_t* __restrict__ counts, const uint64_t* __restrict__ offsets,
              const uint64_t* __restrict__ ray_rank, uint32_t* __restrict__ ray_counter, uint32_t* __restrict__ numsteps_counter,
              float* __restrict__ rays_out, float* __restrict__ rays_rgba, uint32_t* __restrict__ numsteps_out,
              float* __restrict__ coords_out) {
-    const uint32_t i = blockIdx.x * kTrainBlock + threadIdx.x;
-    if (i == 0) *numsteps_counter = (uint32_t)offsets[n_rays];       // includes the rays that found no room, as :633 does
+    const uint32_t i = (blockIdx.x * kTrainWarpBlock + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (i == 0 && lane == 0) *numsteps_counter = (uint32_t)offsets[n_rays];   // includes the rays that found no room, as :633 does
     if (i >= n_rays) return;
     const uint32_t numsteps = counts[i];
     if (numsteps == 0) return;
     const uint64_t base = offsets[i];
     if (base + numsteps > (uint64_t)n_coords) return;                  // :634-636
     const uint32_t ray_idx = (uint32_t)ray_rank[i];
-    atomicAdd(ray_counter, 1u);                                        // a count only: the index comes from the scan
     const TrainRay r = train_ray_setup(g, tv, i, n_rays, n_rays_shift, rng, snap);
-    float* ro = rays_out + (size_t)ray_idx * 6;
-    ro[0] = r.o.x; ro[1] = r.o.y; ro[2] = r.o.z; ro[3] = r.d.x; ro[4] = r.d.y; ro[5] = r.d.z;
-    const uint2 texel = reinterpret_cast<const uint2*>(tv.images)[r.pixel];     // 4 halves (read_rgba, common_device.h:203-213)
-    const __half2 rg = *reinterpret_cast<const __half2*>(&texel.x), ba = *reinterpret_cast<const __half2*>(&texel.y);
-    reinterpret_cast<float4*>(rays_rgba)[ray_idx] = make_float4(__low2float(rg), __high2float(rg), __low2float(ba), __high2float(ba));
-    numsteps_out[ray_idx * 2 + 0] = numsteps;
-    numsteps_out[ray_idx * 2 + 1] = (uint32_t)base;
+    if (lane == 0) {
+        atomicAdd(ray_counter, 1u);                                    // a count only: the index comes from the scan
+        float* ro = rays_out + (size_t)ray_idx * 6;
+        ro[0] = r.o.x; ro[1] = r.o.y; ro[2] = r.o.z; ro[3] = r.d.x; ro[4] = r.d.y; ro[5] = r.d.z;
+        const uint2 texel = reinterpret_cast<const uint2*>(tv.images)[r.pixel];     // 4 halves (read_rgba, common_device.h:203-213)
+        const __half2 rg = *reinterpret_cast<const __half2*>(&texel.x), ba = *reinterpret_cast<const __half2*>(&texel.y);
+        reinterpret_cast<float4*>(rays_rgba)[ray_idx] = make_float4(__low2float(rg), __high2float(rg), __low2float(ba), __high2float(ba));
+        numsteps_out[ray_idx * 2 + 0] = numsteps;
+        numsteps_out[ray_idx * 2 + 1] = (uint32_t)base;
+    }
     const V3 wd = mk3((r.d.x + 1.f) * 0.5f, (r.d.y + 1.f) * 0.5f, (r.d.z + 1.f) * 0.5f);   // warp_direction
     float* c0 = coords_out + base * 7;
-    train_march(g, bits, r, numsteps, [&](uint32_t j, const V3& w, float dt) {
+    train_march_warp(g, bits, r, numsteps, [&](uint32_t j, const V3& w, float dt) {
         float* c = c0 + (size_t)j * 7;
         c[0] = w.x; c[1] = w.y; c[2] = w.z; c[3] = dt; c[4] = wd.x; c[5] = wd.y; c[6] = wd.z;
     });
@@ -185,7 +211,7 @@ void launch_train_count(const DevCfg& g, const TrainViews& tv, const uint8_t* bi
                         uint32_t n_max_steps, RefreshRng rng, int snap, uint32_t* counts, uint32_t* flags, cudaStream_t stream) {
     if (n_rays == 0) return;
     const Pcg r = {rng.state, rng.inc};
-    k_train_count<<<(n_rays + kTrainBlock - 1) / kTrainBlock, kTrainBlock, 0, stream>>>(g, tv, bits, n_rays, n_rays_shift,
+    k_train_count<<<(unsigned int)(((uint64_t)n_rays * 32 + kTrainWarpBlock - 1) / kTrainWarpBlock), kTrainWarpBlock, 0, stream>>>(g, tv, bits, n_rays, n_rays_shift,
                                                                                        n_max_steps, r, snap, counts, flags);
 }
 
@@ -195,7 +221,7 @@ void launch_train_emit(const DevCfg& g, const TrainViews& tv, const uint8_t* bit
                        float* rays_rgba, uint32_t* numsteps_out, float* coords_out, cudaStream_t stream) {
     if (n_rays == 0) return;
     const Pcg r = {rng.state, rng.inc};
-    k_train_emit<<<(n_rays + kTrainBlock - 1) / kTrainBlock, kTrainBlock, 0, stream>>>(
+    k_train_emit<<<(unsigned int)(((uint64_t)n_rays * 32 + kTrainWarpBlock - 1) / kTrainWarpBlock), kTrainWarpBlock, 0, stream>>>(
         g, tv, bits, n_rays, n_rays_shift, n_coords, r, snap, counts, offsets, ray_rank, ray_counter, numsteps_counter, rays_out,
         rays_rgba, numsteps_out, coords_out);
 }
