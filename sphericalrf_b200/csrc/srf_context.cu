@@ -79,6 +79,7 @@ struct srf_ctx {
     // refresh
     uint32_t refresh_step = 0;
     RefreshRng rng = {0, 0};
+    RefreshWeights refresh_w;                // fp32 images of the density MLP weights the refresh reads
 
     // which engine runs the MLPs of the render path: tcgen05/TMEM (default) or the mma.sync kernel
     bool use_tcgen05 = true;
@@ -510,6 +511,8 @@ srf_status srf_upload_network(srf_ctx* ctx, const uint16_t* h_table, size_t n_ta
     SRF_CK(ctx, cudaMemcpy(ctx->table, h_table, n_table * sizeof(__half), cudaMemcpyHostToDevice));
     SRF_CK(ctx, cudaMemcpy(ctx->w_density, h_d, n_d * sizeof(__half), cudaMemcpyHostToDevice));
     SRF_CK(ctx, cudaMemcpy(ctx->w_rgb, h_c, n_c * sizeof(__half), cudaMemcpyHostToDevice));
+    for (int i = 0; i < 64 * 32; ++i) ctx->refresh_w.w1[i] = __half2float(__ushort_as_half(h_d[i]));
+    for (int i = 0; i < 64; ++i) ctx->refresh_w.w2[i] = __half2float(__ushort_as_half(h_d[64 * 32 + i]));
     ctx->have_net = true;
     return SRF_OK;
 }
@@ -617,10 +620,10 @@ srf_status srf_refresh_grid(srf_ctx* ctx, uint32_t training_step, void* stream) 
     const uint32_t n_uniform = training_step >= 256 ? total / 4 : total;          // testbed.cu:206
     const uint32_t n_nonuniform = training_step >= 256 ? total / 4 : 0;           // testbed.cu:207
     SRF_CK(ctx, cudaMemsetAsync(ctx->grid_current, 0, (size_t)total * sizeof(float), s));   // occupancy_sampler.cu:1039
-    launch_refresh_sample(ctx->g, ctx->net, ctx->table, ctx->w_density, ctx->grid, ctx->grid_current, n_uniform,
+    launch_refresh_sample(ctx->g, ctx->net, ctx->table, ctx->refresh_w, ctx->grid, ctx->grid_current, n_uniform,
                           ctx->refresh_step, ctx->rng, (float)-0.01, ctx->cfg.aabb_scale, s);
     host_pcg_advance(ctx->rng, 1ull << 32);                                        // rng.advance(), :1009
-    launch_refresh_sample(ctx->g, ctx->net, ctx->table, ctx->w_density, ctx->grid, ctx->grid_current, n_nonuniform,
+    launch_refresh_sample(ctx->g, ctx->net, ctx->table, ctx->refresh_w, ctx->grid, ctx->grid_current, n_nonuniform,
                           ctx->refresh_step, ctx->rng, ctx->min_optical_thickness, ctx->cfg.aabb_scale, s);
     host_pcg_advance(ctx->rng, 1ull << 32);                                        // :1028
     launch_decay_and_mean(ctx->grid, ctx->grid_current, total, ctx->g.cells, ctx->cfg.ema_decay, 1, ctx->partial_a,

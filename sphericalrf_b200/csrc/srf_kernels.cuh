@@ -126,8 +126,11 @@ void launch_composite_coords(const DevCfg& g, const DevView& v, const uint64_t* 
 
 // Grid refresh pieces (srf_refresh.cu).
 struct RefreshRng { uint64_t state, inc; };
+// Density MLP weights the refresh needs, as fp32 (exact images of the fp16 parameters): layer 1 [64][32] and
+// row 0 of layer 2.  Passed to the kernel by value (8.4 KB of its parameter block).
+struct RefreshWeights { float w1[64 * 32]; float w2[64]; };
 // One sampling pass: cell pick, jitter, encoding, density output 0, atomicMax into grid_current.
-void launch_refresh_sample(const DevCfg& g, const NetMeta& net, const __half* table, const __half* w_density,
+void launch_refresh_sample(const DevCfg& g, const NetMeta& net, const __half* table, const RefreshWeights& w,
                            const float* grid, float* grid_current, uint32_t n_elements, uint32_t step, RefreshRng rng,
                            float thresh, uint32_t aabb_scale, cudaStream_t stream);
 // Max-decay of every cell (when do_decay) and the mean of max(v,0) over the first `cells` entries.

@@ -25,18 +25,29 @@ constexpr int kRefreshBlock = 128;
 // splat_grid_samples_nerf_max_nearest_neighbor (:187-212) for one of the two sampling passes.
 template <int F>
 __global__ void __launch_bounds__(kRefreshBlock)
-k_refresh_sample(const DevCfg g, const NetMeta net, const __half* __restrict__ table, const __half* __restrict__ wd,
+k_refresh_sample(const DevCfg g, const NetMeta net, const __grid_constant__ RefreshWeights W, const __half* __restrict__ table,
                  const float* __restrict__ grid_in, float* __restrict__ grid_current, uint32_t n_elements,
-                 uint32_t step, Pcg rng0, float thresh, uint32_t aabb_scale) {
-    __shared__ __align__(16) float sW1[64 * 32];
-    __shared__ float sW2[64];
+                 uint32_t step, Pcg rng0, float thresh, uint32_t aabb_scale, uint32_t inv_mult) {
+    // The 2 112 weights the MLP needs arrive in the kernel's parameter block (constant bank): with the loops
+    // below fully unrolled every multiply-add names its weight as a constant operand, so the layer costs no
+    // load instructions at all (a shared-memory copy of the matrix made this kernel L1/shared-memory bound).
     __shared__ EncMeta enc_meta;
     prepare_enc_meta(net, &enc_meta);
-    for (int i = threadIdx.x; i < 64 * 32; i += blockDim.x) sW1[i] = __half2float(wd[i]);
-    for (int i = threadIdx.x; i < 64; i += blockDim.x) sW2[i] = __half2float(wd[64 * 32 + i]);   // row 0 of layer 2
     __syncthreads();
-    const uint32_t i = blockIdx.x * kRefreshBlock + threadIdx.x;
-    if (i >= n_elements) return;
+    const uint32_t tid = blockIdx.x * kRefreshBlock + threadIdx.x;
+    if (tid >= n_elements) return;
+    // Which sample index i this thread takes.  The reference gives thread i the cell
+    // ((i + step*n) * 56924617 + 96925573) mod cells: a pseudo-random cell, so neighbouring threads gather from
+    // unrelated table lines.  The result does not depend on which thread handles which i (the splat is an
+    // atomic max), so when the map is a bijection (power-of-two cell count, n a multiple of it: inv_mult != 0)
+    // thread t takes the i whose first-try cell is t: neighbouring threads then work on neighbouring Morton cells
+    // and their gathers share lines.
+    uint32_t i = tid;
+    if (inv_mult) {
+        const uint32_t q = tid / g.cells, c = tid % g.cells;
+        const uint32_t v = (c - 96925573u) * inv_mult;                    // (i + step*n) mod cells
+        i = q * g.cells + ((v - step * n_elements) & (g.cells - 1u));
+    }
 
     Pcg rng = rng0;
     pcg_advance(rng, (uint64_t)i * 4u);
@@ -79,20 +90,14 @@ k_refresh_sample(const DevCfg g, const NetMeta net, const __half* __restrict__ t
 #pragma unroll
     for (int k = 0; k < 32; ++k) x[k] = __half2float(enc[k]);
     float out0 = 0.f;
+#pragma unroll
     for (int o = 0; o < 64; ++o) {
-        const float4* w = reinterpret_cast<const float4*>(sW1 + o * 32);
         float acc = 0.f;
 #pragma unroll
-        for (int k4 = 0; k4 < 8; ++k4) {
-            const float4 q = w[k4];
-            acc = fmaf(q.x, x[4 * k4], acc);
-            acc = fmaf(q.y, x[4 * k4 + 1], acc);
-            acc = fmaf(q.z, x[4 * k4 + 2], acc);
-            acc = fmaf(q.w, x[4 * k4 + 3], acc);
-        }
+        for (int k = 0; k < 32; ++k) acc = fmaf(W.w1[o * 32 + k], x[k], acc);
         if (!(acc > 0.f)) acc = 0.f;
         const float h = __half2float(__float2half_rn(acc));
-        out0 = fmaf(sW2[o], h, out0);
+        out0 = fmaf(W.w2[o], h, out0);
     }
     const float raw = __half2float(__float2half_rn(out0));
     const float thickness = network_to_density(raw, g.density_activation) * g.min_step;
@@ -207,16 +212,21 @@ void launch_build_skip_tables(const DevCfg& g, const uint8_t* bits, uint32_t* sh
     k_build_skip_tables<<<(n_bytes + 255) / 256, 256, 0, stream>>>(bits, n_bytes, N, shell, yz);
 }
 
-void launch_refresh_sample(const DevCfg& g, const NetMeta& net, const __half* table, const __half* w_density,
+void launch_refresh_sample(const DevCfg& g, const NetMeta& net, const __half* table, const RefreshWeights& w,
                            const float* grid, float* grid_current, uint32_t n_elements, uint32_t step, RefreshRng rng,
                            float thresh, uint32_t aabb_scale, cudaStream_t stream) {
     if (n_elements == 0) return;
     const unsigned int nb = (n_elements + kRefreshBlock - 1) / kRefreshBlock;
     Pcg r = {rng.state, rng.inc};
+    uint32_t inv_mult = 0;
+    if ((g.cells & (g.cells - 1u)) == 0 && n_elements % g.cells == 0) {
+        inv_mult = 1;                                      // inverse of 56924617 modulo 2^32 (Newton iteration)
+        for (int it = 0; it < 6; ++it) inv_mult *= 2u - 56924617u * inv_mult;
+    }
     if (net.n_features == 2)
-        k_refresh_sample<2><<<nb, kRefreshBlock, 0, stream>>>(g, net, table, w_density, grid, grid_current, n_elements, step, r, thresh, aabb_scale);
+        k_refresh_sample<2><<<nb, kRefreshBlock, 0, stream>>>(g, net, w, table, grid, grid_current, n_elements, step, r, thresh, aabb_scale, inv_mult);
     else
-        k_refresh_sample<4><<<nb, kRefreshBlock, 0, stream>>>(g, net, table, w_density, grid, grid_current, n_elements, step, r, thresh, aabb_scale);
+        k_refresh_sample<4><<<nb, kRefreshBlock, 0, stream>>>(g, net, w, table, grid, grid_current, n_elements, step, r, thresh, aabb_scale, inv_mult);
 }
 
 // Max-decay (optional) + mean.  partial_a / partial_b: ceil(cells/1024) floats each.
