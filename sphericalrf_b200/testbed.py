@@ -152,6 +152,16 @@ class Renderer:
                                      None if stats is None else C.byref(stats)))
         return (img, stats.as_dict()) if want_stats else img
 
+    def network_inference(self, coords):
+        """srf_network_inference on host Coordinate records (n, 7) float32 -> (n, 4) float16 raw (r, g, b, sigma)."""
+        import torch
+        dev = torch.device("cuda", self.device)
+        c = torch.from_numpy(np.ascontiguousarray(coords, np.float32)).to(dev)
+        out = torch.zeros((c.shape[0], 4), dtype=torch.float16, device=dev)
+        self._ck(self.lib.srf_network_inference(self.ctx, C.c_void_p(c.data_ptr()), c.shape[0], C.c_void_p(out.data_ptr()), None))
+        torch.cuda.synchronize(dev)
+        return out.cpu().numpy()
+
     # -- training-side sampler --
     def _device_views(self, views: dict):
         """srf_train_views_t over torch device copies of dict(n_images, width, height, focal_length,
