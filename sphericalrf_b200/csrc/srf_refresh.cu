@@ -184,21 +184,35 @@ __global__ void k_bitfield_max_pool(uint32_t n_elements, uint32_t n_grid_size, c
 }
 
 // Summaries of the level-0 bitfield for the sampler's staged empty-space tests: which radial indices z, and
-// which (z, y) index pairs, have at least one occupied cell.
-__global__ void k_build_skip_tables(const uint8_t* __restrict__ bits, uint32_t n_bytes, uint32_t n_grid_size,
+// which (z, y) index pairs, have at least one occupied cell.  One thread per 32-bit word of the bitfield: 32
+// Morton-consecutive cells are a block of 4 x 4 x 2 cells (bit layout of the low Morton bits: x0 y0 z0 x1 y1),
+// so a word contributes at most two z values and eight (z, y) pairs.
+__global__ void k_build_skip_tables(const uint32_t* __restrict__ bits32, uint32_t n_words, uint32_t n_grid_size,
                                     uint32_t* __restrict__ shell, uint32_t* __restrict__ yz) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_bytes) return;
-    const uint32_t b = bits[i];
+    if (i >= n_words) return;
+    const uint32_t b = bits32[i];
     if (!b) return;
-    for (uint32_t j = 0; j < 8; ++j) {
-        if (!((b >> j) & 1u)) continue;
-        const uint32_t m = i * 8u + j;
-        const uint32_t y = morton3D_invert(m >> 1), z = morton3D_invert(m >> 2);
-        const uint32_t sb = 1u << (z & 31u);
-        if (!(shell[z >> 5] & sb)) atomicOr(shell + (z >> 5), sb);          // mostly already set: read first
-        const uint32_t k = z * n_grid_size + y, kb = 1u << (k & 31u);
-        if (!(yz[k >> 5] & kb)) atomicOr(yz + (k >> 5), kb);
+    const uint32_t m0 = i * 32u;
+    const uint32_t y_base = morton3D_invert(m0 >> 1), z_base = morton3D_invert(m0 >> 2);
+#pragma unroll
+    for (uint32_t zl = 0; zl < 2; ++zl) {
+        bool any_z = false;
+#pragma unroll
+        for (uint32_t yl = 0; yl < 4; ++yl) {
+            // the four cells x = 0..3 of this (y, z): Morton offsets with bits x0 (1) and x1 (8)
+            const uint32_t o = ((yl & 1u) << 1) | (zl << 2) | ((yl >> 1) << 4);
+            const uint32_t mask = (1u << o) | (1u << (o | 1u)) | (1u << (o | 8u)) | (1u << (o | 9u));
+            if (b & mask) {
+                any_z = true;
+                const uint32_t k = (z_base + zl) * n_grid_size + (y_base + yl), kb = 1u << (k & 31u);
+                if (!(yz[k >> 5] & kb)) atomicOr(yz + (k >> 5), kb);          // mostly already set: read first
+            }
+        }
+        if (any_z) {
+            const uint32_t z = z_base + zl, sb = 1u << (z & 31u);
+            if (!(shell[z >> 5] & sb)) atomicOr(shell + (z >> 5), sb);
+        }
     }
 }
 
@@ -208,8 +222,8 @@ void launch_build_skip_tables(const DevCfg& g, const uint8_t* bits, uint32_t* sh
     const uint32_t N = g.grid_size;
     cudaMemsetAsync(shell, 0, ((N + 31) / 32) * sizeof(uint32_t), stream);
     cudaMemsetAsync(yz, 0, ((size_t)N * N + 31) / 32 * sizeof(uint32_t), stream);
-    const uint32_t n_bytes = g.cells / 8;
-    k_build_skip_tables<<<(n_bytes + 255) / 256, 256, 0, stream>>>(bits, n_bytes, N, shell, yz);
+    const uint32_t n_words = g.cells / 32;          // grid_size is a power of two >= 8: whole words
+    k_build_skip_tables<<<(n_words + 255) / 256, 256, 0, stream>>>(reinterpret_cast<const uint32_t*>(bits), n_words, N, shell, yz);
 }
 
 void launch_refresh_sample(const DevCfg& g, const NetMeta& net, const __half* table, const RefreshWeights& w,
