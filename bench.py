@@ -379,13 +379,14 @@ def run_ours(args):
         ms_i = ms_of(train_infer)
         ms_l = ms_of(train_loss)
         line["training_side"] = {
-            "rays": n_tr, "rays_kept": kept, "samples": total, "samples_compacted": int(ctr[2].item()),
+            "rays": n_tr, "rays_kept": kept, "samples": total, "samples_consumed": int(ctr[2].item()),
+            "samples_with_gradient": min(int(ctr[2].item()), n_comp),
             "ms_sample_rays": ms_s, "ms_network_inference": ms_i, "ms_loss_and_gradient": ms_l,
             "sampler_msamples_per_s": total / (ms_s * 1e-3) / 1e6, "inference_msamples_per_s": n_used[0] / (ms_i * 1e-3) / 1e6,
             # sampler: 28 B/sample + 80 B/ray; compositor forward+backward: 2 x (8 + 4) B read per sample + 28 B copied and
             # 8 B gradient written per compacted sample
             "sampler_algorithmic_gbs": (28.0 * total + 80.0 * n_tr) / (ms_s * 1e-3) / 1e9,
-            "loss_algorithmic_gbs": (24.0 * total + 64.0 * int(ctr[2].item())) / (ms_l * 1e-3) / 1e9,
+            "loss_algorithmic_gbs": (24.0 * total + 64.0 * min(int(ctr[2].item()), n_comp)) / (ms_l * 1e-3) / 1e9,
         }
     if world == 1 and cfg.field_type == abi.FIELD_NETWORK:
         # density-grid refresh (Testbed::train_prep_nerf): 16 consecutive refreshes of the 128^3 grid, all-cells mode
