@@ -335,6 +335,15 @@ srf_status srf_render_frame(srf_ctx* ctx, const srf_view_t* view, const srf_post
 srf_status srf_render_frame_scatter(srf_ctx* ctx, const srf_view_t* view, const srf_post_t* post, float* d_image,
                                     float* d_accum, srf_frame_stats_t* stats, void* stream);
 
+/* How srf_render_frame schedules a frame.  The reference alternates rounds of <= 8 march steps per ray with
+   network evaluation, compositing and compaction of finished rays (internal/testbed.cu:523-583), so samples behind
+   the point where a ray saturates are never evaluated.  Here a frame runs in a few large waves: wave k takes every
+   unfinished ray steps[k] march steps further, the field and the compositor run on what was emitted, rays whose
+   pixel is final are dropped; a last wave finishes whatever is left.  The image does not depend on the schedule.
+   Default {128, 512}; n = 0 renders each frame in one pass.  (A call that asks srf_render_frame for per-ray
+   sampler counts always runs in one pass.) */
+srf_status srf_set_wave_schedule(srf_ctx* ctx, const uint32_t* steps, uint32_t n);
+
 /* Testbed::render (internal/python_api.cu:17-41): spp passes of srf_render_frame and the copy
    to a host image h_image float[height*width*4] (whole image; shard_count must be 1).
    Synchronises. */

@@ -133,6 +133,8 @@ public:
     void render(const srf_view_t& view, const srf_post_t& post, uint32_t spp, float* h_image) {
         check(srf_render(m_ctx.get(), &view, &post, spp, h_image, nullptr), m_ctx.get());
     }
+    // RenderingBuffer::MIN/MAX_STEPS_INBETWEEN_COMPACTION have no meaning here; the counterpart is the wave schedule
+    void set_wave_schedule(const uint32_t* steps, uint32_t n) { check(srf_set_wave_schedule(m_ctx.get(), steps, n), m_ctx.get()); }
     void train_prep_nerf(uint32_t training_step, void* stream) {
         check(srf_refresh_grid(m_ctx.get(), training_step, stream), m_ctx.get());
     }

@@ -145,14 +145,22 @@ k_composite_rays(const DevCfg g, const DevView v, const DevPost post, const uint
                  const uint32_t* __restrict__ ray_head, const uint32_t* __restrict__ ray_count,
                  const uint32_t* __restrict__ chunk_next,
                  uint64_t ray_begin, uint64_t ray_end, const float4* __restrict__ shaded,
-                 const uint8_t* __restrict__ ray_end_reason, float4* __restrict__ out, float4* __restrict__ accum,
-                 float4* __restrict__ rgba_raw, uint32_t* __restrict__ n_composited, FrameCounters* __restrict__ counters) {
+                 uint8_t* __restrict__ ray_end_reason, float4* __restrict__ out, float4* __restrict__ accum,
+                 float4* __restrict__ rgba_raw, uint32_t* __restrict__ n_composited, FrameCounters* __restrict__ counters,
+                 uint32_t wave, float4* __restrict__ ray_rgba, uint32_t* __restrict__ ray_ncomp) {
     const uint64_t r = ray_begin + (uint64_t)blockIdx.x * kRayBlock + threadIdx.x;
     unsigned long long comp = 0;
     unsigned int hits = 0;
-    if (r < ray_end) {
+    const uint32_t end = r < ray_end ? ray_end_reason[r] : (uint32_t)RAY_END_DONE;
+    if (r < ray_end && !(wave > 0 && end == RAY_END_DONE)) {
         float R = 0.f, G = 0.f, B = 0.f, A = 0.f;
         uint32_t n = 0;
+        if (wave > 0) {                                // the state an earlier wave left
+            const float4 q = ray_rgba[r];
+            R = q.x; G = q.y; B = q.z; A = q.w;
+            n = ray_ncomp[r];
+        }
+        const uint32_t n_before = n;
         bool terminated = false;
         auto take = [&](const float4 q) {
             const float T = 1.f - A;
@@ -181,21 +189,28 @@ k_composite_rays(const DevCfg g, const DevView v, const DevPost post, const uint
             for (uint64_t j = 0; j < cnt; ++j)
                 if (take(__ldg(p + j))) { terminated = true; break; }
         }
-        const uint32_t end = ray_end_reason[r];
-        // A ray reaches the hit buffer when it stops being alive (terminated, left the box, or its step
-        // size fell to 0 in empty space) and its opacity exceeds 0.001 (testbed.cu:438-445).  Rays that
-        // stay alive until the reference's loop bound leave their pixel untouched.
-        const bool finished = terminated || end == RAY_END_EXIT || end == RAY_END_DT0;
-        const bool hit = finished && A > 0.001f;
-        const uint32_t n_steps_total = terminated ? n : 1u + n;
-        const float rgba[4] = {R, G, B, A};
-        if (rgba_raw) rgba_raw[r] = make_float4(R, G, B, A);
-        if (n_composited) n_composited[r] = n;
-        if (out || accum)
-            finish_pixel(g, v, post, hit, rgba, n_steps_total, accum ? accum + r : nullptr,
-                         out ? out + (v.out_by_pixel ? (uint64_t)shard_ray_pixel(v, r) : r) : nullptr);
-        comp = n;
-        hits = hit ? 1u : 0u;
+        if (!terminated && end == RAY_END_PAUSED) {
+            // more samples to come: keep the running sums, write no pixel yet
+            ray_rgba[r] = make_float4(R, G, B, A);
+            ray_ncomp[r] = n;
+            comp = n - n_before;
+        } else {
+            // A ray reaches the hit buffer when it stops being alive (terminated, left the box, or its step
+            // size fell to 0 in empty space) and its opacity exceeds 0.001 (testbed.cu:438-445).  Rays that
+            // stay alive until the reference's loop bound leave their pixel untouched.
+            const bool finished = terminated || end == RAY_END_EXIT || end == RAY_END_DT0;
+            const bool hit = finished && A > 0.001f;
+            const uint32_t n_steps_total = terminated ? n : 1u + n;
+            const float rgba[4] = {R, G, B, A};
+            if (rgba_raw) rgba_raw[r] = make_float4(R, G, B, A);
+            if (n_composited) n_composited[r] = n;
+            if (out || accum)
+                finish_pixel(g, v, post, hit, rgba, n_steps_total, accum ? accum + r : nullptr,
+                             out ? out + (v.out_by_pixel ? (uint64_t)shard_ray_pixel(v, r) : r) : nullptr);
+            if (ray_rgba) ray_end_reason[r] = (uint8_t)RAY_END_DONE;
+            comp = n - n_before;
+            hits = hit ? 1u : 0u;
+        }
     }
     for (int o = 16; o > 0; o >>= 1) {
         comp += __shfl_down_sync(0xffffffffu, comp, o);
@@ -238,18 +253,21 @@ void launch_composite(const DevCfg& g, const DevView& v, const DevPost& post, co
     const uint64_t n = ray_end - ray_begin;
     const unsigned int nb = (unsigned int)((n + kRayBlock - 1) / kRayBlock);
     k_composite_rays<false><<<nb, kRayBlock, 0, stream>>>(g, v, post, offsets, nullptr, nullptr, nullptr, ray_begin, ray_end, shaded,
-                                                          ray_end_reason, out, accum, rgba_raw, n_composited, counters);
+                                                          const_cast<uint8_t*>(ray_end_reason), out, accum, rgba_raw, n_composited,
+                                                          counters, 0u, nullptr, nullptr);
 }
 
 void launch_composite_paged(const DevCfg& g, const DevView& v, const DevPost& post, uint64_t ray_begin, uint64_t ray_end,
                             const uint32_t* ray_head, const uint32_t* ray_count, const uint32_t* chunk_next,
-                            const float4* pool_shaded, const uint8_t* ray_end_reason, float4* out, float4* accum,
-                            float4* rgba_raw, uint32_t* n_composited, FrameCounters* counters, cudaStream_t stream) {
+                            const float4* pool_shaded, uint8_t* ray_end_reason, float4* out, float4* accum,
+                            float4* rgba_raw, uint32_t* n_composited, FrameCounters* counters, cudaStream_t stream,
+                            uint32_t wave, float4* ray_rgba, uint32_t* ray_ncomp) {
     if (ray_end <= ray_begin) return;
     const uint64_t n = ray_end - ray_begin;
     const unsigned int nb = (unsigned int)((n + kRayBlock - 1) / kRayBlock);
     k_composite_rays<true><<<nb, kRayBlock, 0, stream>>>(g, v, post, nullptr, ray_head, ray_count, chunk_next, ray_begin, ray_end,
-                                                         pool_shaded, ray_end_reason, out, accum, rgba_raw, n_composited, counters);
+                                                         pool_shaded, ray_end_reason, out, accum, rgba_raw, n_composited, counters,
+                                                         wave, ray_rgba, ray_ncomp);
 }
 
 void launch_composite_coords(const DevCfg& g, const DevView& v, const uint64_t* offsets, uint64_t n_rays,

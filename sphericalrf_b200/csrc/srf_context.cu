@@ -65,6 +65,9 @@ struct srf_ctx {
 
     // per-frame scratch
     DevBuf train_flags, train_rank, loss_rgb;
+    DevBuf ray_ordinal, ray_total, ray_rgba, ray_ncomp;        // per-ray state between the waves of a frame
+    uint32_t wave_budget[8] = {128, 512, 0, 0, 0, 0, 0, 0};   // march steps per ray in waves 0, 1, ...; a final unlimited wave follows
+    uint32_t n_wave_budgets = 2;
     DevBuf ray_dir_t, ray_end, counts, offsets, scan_scratch;
     DevBuf pos_dt, sample_ray, rgbs;
     DevBuf pool_pos, pool_shaded, chunk_ray, chunk_next, ray_head;   // paged frame path
@@ -435,6 +438,16 @@ srf_status srf_create(const srf_config_t* cfg, int device, srf_ctx** out) {
     ctx->skip_capable = cfg->use_grid && cfg->num_cascades == 1 &&
                         (cfg->warping_type == SRF_WARP_ERP || cfg->warping_type == SRF_WARP_SINUSOIDAL) &&
                         (cfg->grid_distribution_type == SRF_GRID_WARPED_EXP || cfg->grid_distribution_type == SRF_GRID_WARPED_RECIPROCAL);
+    if (const char* e = getenv("SRF_B200_WAVES")) {      // "0" = one pass per frame; "64,256" = march steps of the leading waves
+        ctx->n_wave_budgets = 0;
+        for (const char* q = e; *q && ctx->n_wave_budgets < 8;) {
+            char* endp = nullptr;
+            const unsigned long b = strtoul(q, &endp, 10);
+            if (endp == q) break;
+            if (b > 0) ctx->wave_budget[ctx->n_wave_budgets++] = (uint32_t)b;
+            q = *endp ? endp + 1 : endp;
+        }
+    }
     if (const char* e = getenv("SRF_B200_SKIP_TABLES")) if (std::string(e) == "0") ctx->skip_capable = false;
     if (ctx->skip_capable) {
         const size_t N = cfg->grid_size;
@@ -468,7 +481,7 @@ void srf_destroy(srf_ctx* ctx) {
     if (!ctx) return;
     DeviceGuard guard(ctx->device);
     void* ptrs[] = {ctx->grid, ctx->grid_current, ctx->partial_a, ctx->partial_b, ctx->mean, ctx->bits, ctx->table,
-                    ctx->w_density, ctx->w_rgb, ctx->skip_shell, ctx->skip_yz, ctx->train_flags.p, ctx->train_rank.p, ctx->loss_rgb.p, ctx->blobs, ctx->cmap, ctx->d_counters, ctx->ray_dir_t.p, ctx->ray_end.p,
+                    ctx->w_density, ctx->w_rgb, ctx->skip_shell, ctx->skip_yz, ctx->train_flags.p, ctx->train_rank.p, ctx->loss_rgb.p, ctx->ray_ordinal.p, ctx->ray_total.p, ctx->ray_rgba.p, ctx->ray_ncomp.p, ctx->blobs, ctx->cmap, ctx->d_counters, ctx->ray_dir_t.p, ctx->ray_end.p,
                     ctx->counts.p, ctx->offsets.p, ctx->scan_scratch.p, ctx->pos_dt.p, ctx->sample_ray.p, ctx->rgbs.p,
                     ctx->img_out.p, ctx->img_accum.p, ctx->pool_pos.p, ctx->pool_shaded.p, ctx->chunk_ray.p, ctx->chunk_next.p,
                     ctx->ray_head.p, ctx->d_chunk_cursor};
@@ -922,36 +935,61 @@ static srf_status render_frame_impl(srf_ctx* ctx, const srf_view_t* view, const 
     const bool blobs = ctx->cfg.field_type == SRF_FIELD_BLOBS;
     const uint8_t* bits = ctx->cfg.use_grid ? ctx->bits : nullptr;
     uint32_t n_batches = 0;
+    // Waves: the leading waves take every ray a limited number of march steps further, so that rays the compositor
+    // finishes early never have the rest of their samples generated or evaluated; the last wave is unlimited.  A
+    // caller who asks for the sampler's per-ray counts gets the whole march in one wave.
+    uint32_t budgets[9];                       // pause_at of each wave: cumulative march steps
+    uint32_t n_waves = 0;
+    if (!d_n_samples) {
+        uint64_t total_steps = 0;
+        for (uint32_t k = 0; k < ctx->n_wave_budgets; ++k) {
+            total_steps += ctx->wave_budget[k];
+            if (total_steps < ctx->g.step_limit) budgets[n_waves++] = (uint32_t)total_steps;
+        }
+    }
+    budgets[n_waves++] = 0xffffffffu;
+    const bool waves = n_waves > 1;
+    if (waves) {
+        if ((st = ensure(ctx, ctx->ray_ordinal, v.n_rays * sizeof(uint32_t))) != SRF_OK) return st;
+        if ((st = ensure(ctx, ctx->ray_total, v.n_rays * sizeof(uint32_t))) != SRF_OK) return st;
+        if ((st = ensure(ctx, ctx->ray_rgba, v.n_rays * sizeof(float4))) != SRF_OK) return st;
+        if ((st = ensure(ctx, ctx->ray_ncomp, v.n_rays * sizeof(uint32_t))) != SRF_OK) return st;
+    }
     for (uint64_t r0 = 0; r0 < v.n_rays; r0 += rays_per_batch) {
         const uint64_t r1 = std::min<uint64_t>(r0 + rays_per_batch, v.n_rays);
-        SRF_CK(ctx, cudaMemsetAsync(ctx->d_chunk_cursor, 0, sizeof(uint32_t), s));
-        if (tm) cudaEventRecord(ctx->ev[2], s);
-        launch_march_paged(ctx->g, v, bits, r0, r1, (float4*)ctx->pool_pos.p, (uint32_t*)ctx->chunk_ray.p, (uint32_t*)ctx->chunk_next.p,
-                           pool_chunks, ctx->d_chunk_cursor, (float4*)ctx->ray_dir_t.p, (uint8_t*)ctx->ray_end.p,
-                           (uint32_t*)ctx->counts.p, (uint32_t*)ctx->ray_head.p, ctx->d_counters, s);
-        if (tm) cudaEventRecord(ctx->ev[3], s);
-        if (blobs)
-            launch_field_blobs(ctx->g, v, ctx->blobs, ctx->n_blobs, ctx->cmap, (const float4*)ctx->pool_pos.p, 0,
-                               (float4*)ctx->pool_shaded.p, s, ctx->d_chunk_cursor);
-        else if (v.render_mode == SRF_MODE_NORMALS)
-            launch_field_normals(ctx->g, ctx->net, ctx->table, ctx->w_density, (const float4*)ctx->pool_pos.p, 0,
-                                 (float4*)ctx->pool_shaded.p, s, ctx->d_chunk_cursor);
-        else if (ctx->use_tcgen05)
-            launch_field_network_tc(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, (const float4*)ctx->pool_pos.p,
-                                    (const uint32_t*)ctx->chunk_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, 0, nullptr,
-                                    (float4*)ctx->pool_shaded.p, &ctx->g, &v, &ctx->d_counters->error_flags, s,
-                                    ctx->d_chunk_cursor, kChunkShift);
-        else
-            launch_field_network(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, (const float4*)ctx->pool_pos.p,
-                                 (const uint32_t*)ctx->chunk_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, 0, nullptr,
-                                 (float4*)ctx->pool_shaded.p, &ctx->g, &v, s, ctx->d_chunk_cursor, kChunkShift);
-        if (tm) cudaEventRecord(ctx->ev[4], s);
-        launch_composite_paged(ctx->g, v, dp, r0, r1, (const uint32_t*)ctx->ray_head.p, (const uint32_t*)ctx->counts.p,
-                               (const uint32_t*)ctx->chunk_next.p, (const float4*)ctx->pool_shaded.p, (const uint8_t*)ctx->ray_end.p,
-                               (float4*)d_out, (float4*)d_accum, (float4*)d_rgba_raw, nullptr, ctx->d_counters, s);
-        if (tm) {
-            cudaEventRecord(ctx->ev[5], s);
-            lap(2, 3, &ms_sampler); lap(3, 4, &ms_field); lap(4, 5, &ms_comp);
+        for (uint32_t wave = 0; wave < n_waves; ++wave) {
+            SRF_CK(ctx, cudaMemsetAsync(ctx->d_chunk_cursor, 0, sizeof(uint32_t), s));
+            if (tm) cudaEventRecord(ctx->ev[2], s);
+            launch_march_paged(ctx->g, v, bits, r0, r1, (float4*)ctx->pool_pos.p, (uint32_t*)ctx->chunk_ray.p,
+                               (uint32_t*)ctx->chunk_next.p, pool_chunks, ctx->d_chunk_cursor, (float4*)ctx->ray_dir_t.p,
+                               (uint8_t*)ctx->ray_end.p, (uint32_t*)ctx->counts.p, (uint32_t*)ctx->ray_head.p, ctx->d_counters, s,
+                               wave, budgets[wave], waves ? (uint32_t*)ctx->ray_ordinal.p : nullptr,
+                               waves ? (uint32_t*)ctx->ray_total.p : nullptr);
+            if (tm) cudaEventRecord(ctx->ev[3], s);
+            if (blobs)
+                launch_field_blobs(ctx->g, v, ctx->blobs, ctx->n_blobs, ctx->cmap, (const float4*)ctx->pool_pos.p, 0,
+                                   (float4*)ctx->pool_shaded.p, s, ctx->d_chunk_cursor);
+            else if (v.render_mode == SRF_MODE_NORMALS)
+                launch_field_normals(ctx->g, ctx->net, ctx->table, ctx->w_density, (const float4*)ctx->pool_pos.p, 0,
+                                     (float4*)ctx->pool_shaded.p, s, ctx->d_chunk_cursor);
+            else if (ctx->use_tcgen05)
+                launch_field_network_tc(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, (const float4*)ctx->pool_pos.p,
+                                        (const uint32_t*)ctx->chunk_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, 0, nullptr,
+                                        (float4*)ctx->pool_shaded.p, &ctx->g, &v, &ctx->d_counters->error_flags, s,
+                                        ctx->d_chunk_cursor, kChunkShift);
+            else
+                launch_field_network(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, (const float4*)ctx->pool_pos.p,
+                                     (const uint32_t*)ctx->chunk_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, 0, nullptr,
+                                     (float4*)ctx->pool_shaded.p, &ctx->g, &v, s, ctx->d_chunk_cursor, kChunkShift);
+            if (tm) cudaEventRecord(ctx->ev[4], s);
+            launch_composite_paged(ctx->g, v, dp, r0, r1, (const uint32_t*)ctx->ray_head.p, (const uint32_t*)ctx->counts.p,
+                                   (const uint32_t*)ctx->chunk_next.p, (const float4*)ctx->pool_shaded.p, (uint8_t*)ctx->ray_end.p,
+                                   (float4*)d_out, (float4*)d_accum, (float4*)d_rgba_raw, nullptr, ctx->d_counters, s, wave,
+                                   waves ? (float4*)ctx->ray_rgba.p : nullptr, waves ? (uint32_t*)ctx->ray_ncomp.p : nullptr);
+            if (tm) {
+                cudaEventRecord(ctx->ev[5], s);
+                lap(2, 3, &ms_sampler); lap(3, 4, &ms_field); lap(4, 5, &ms_comp);
+            }
         }
         ++n_batches;
     }
@@ -973,6 +1011,17 @@ static srf_status render_frame_impl(srf_ctx* ctx, const srf_view_t* view, const 
         if (stats->error_flags & 2u) return fail(ctx, SRF_ERR_TIMEOUT, "a wait on the tensor-core commit barrier expired");
         if (stats->error_flags & 4u) return fail(ctx, SRF_ERR_CAPACITY, "the sample pool ran out of chunks");
     }
+    return SRF_OK;
+}
+
+srf_status srf_set_wave_schedule(srf_ctx* ctx, const uint32_t* steps, uint32_t n) {
+    if (!ctx) return SRF_ERR_ARG;
+    if (n > 8) return fail(ctx, SRF_ERR_ARG, "at most 8 leading waves");
+    if (n && !steps) return fail(ctx, SRF_ERR_ARG, "steps is NULL");
+    for (uint32_t k = 0; k < n; ++k)
+        if (steps[k] == 0) return fail(ctx, SRF_ERR_ARG, "a wave must advance by at least one march step");
+    for (uint32_t k = 0; k < n; ++k) ctx->wave_budget[k] = steps[k];
+    ctx->n_wave_budgets = n;
     return SRF_OK;
 }
 

@@ -379,8 +379,13 @@ enum RayEnd : uint32_t {
     RAY_END_LIMIT = 3,      // the march loop's hard bound (an error)
     RAY_END_BORN_DEAD = 4,  // entry point outside the box
     RAY_END_CAP = 5,        // sample cap reached
-    RAY_END_TERMINATED = 6  // stopped by the consumer (early termination)
+    RAY_END_TERMINATED = 6, // stopped by the consumer (early termination)
+    RAY_END_PAUSED = 7,     // the wave's step budget is used up: the march resumes later from the saved MarchState
+    RAY_END_DONE = 8        // frame path: the ray's pixel has been written by an earlier wave
 };
+
+// Where a march stands: ray parameter, loop iterations so far, samples emitted so far.
+struct MarchState { float t; uint32_t ordinal, n; };
 
 struct RayInit { bool alive; V3 o, d; float t; };
 
@@ -455,14 +460,19 @@ __device__ __forceinline__ bool grid_lookup(const DevCfg& g, const uint8_t* __re
 }
 
 // The loop shared by advance_pos_nerf (:771-794) and generate_coords_from_rays_regularly_kernel
-// (:829-860), run to the end of the ray.  emit(w, dt, ordinal, cell, t) is called for every occupied
-// step and returns false to stop.  Returns the RayEnd; *n_steps receives the loop iterations.
+// (:829-860), run from `st` until the ray ends, the consumer stops it, or the loop has made `pause_at`
+// iterations in all (RAY_END_PAUSED: `st` then holds the state to resume from).  emit(w, dt, ordinal, cell, t)
+// is called for every occupied step and returns false to stop.  Returns the RayEnd; st.ordinal counts the
+// loop iterations of the whole ray.  Pausing on the iteration count (not on the number of samples) keeps the
+// lanes of a warp in step: they all pause after the same number of iterations.
 template <class Emit>
-__device__ __forceinline__ uint32_t march_ray(const DevCfg& g, const uint8_t* __restrict__ bits, const V3& o,
-                                              const V3& d, float t, uint32_t* n_steps, Emit emit) {
-    uint32_t ordinal = 0, n = 0;
-    uint32_t end = RAY_END_LIMIT;
-    for (; ordinal < g.step_limit; ++ordinal) {
+__device__ __forceinline__ uint32_t march_ray_from(const DevCfg& g, const uint8_t* __restrict__ bits, const V3& o,
+                                                   const V3& d, MarchState& st, uint32_t pause_at, Emit emit) {
+    float t = st.t;
+    uint32_t ordinal = st.ordinal, n = st.n;
+    const uint32_t stop = pause_at < g.step_limit ? pause_at : g.step_limit;
+    uint32_t end = pause_at < g.step_limit ? RAY_END_PAUSED : RAY_END_LIMIT;
+    for (; ordinal < stop; ++ordinal) {
         const V3 pos = mk3(fmaf(d.x, t, o.x), fmaf(d.y, t, o.y), fmaf(d.z, t, o.z));
         if (!box_contains(g, pos)) { end = RAY_END_EXIT; ++ordinal; break; }
         const float dt = calc_dt(g, t);
@@ -480,7 +490,17 @@ __device__ __forceinline__ uint32_t march_ray(const DevCfg& g, const uint8_t* __
             if (dt == 0.f) { end = RAY_END_DT0; ++ordinal; break; }
         }
     }
-    *n_steps = ordinal;
+    st.t = t; st.ordinal = ordinal; st.n = n;
+    return end;
+}
+
+// The whole march in one go.  *n_steps receives the loop iterations.
+template <class Emit>
+__device__ __forceinline__ uint32_t march_ray(const DevCfg& g, const uint8_t* __restrict__ bits, const V3& o,
+                                              const V3& d, float t, uint32_t* n_steps, Emit emit) {
+    MarchState st = {t, 0u, 0u};
+    const uint32_t end = march_ray_from(g, bits, o, d, st, 0xffffffffu, emit);
+    *n_steps = st.ordinal;
     return end;
 }
 

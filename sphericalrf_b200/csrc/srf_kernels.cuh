@@ -61,7 +61,10 @@ constexpr uint32_t kNoChunk = 0xffffffffu;
 void launch_march_paged(const DevCfg& g, const DevView& v, const uint8_t* bits, uint64_t ray_begin, uint64_t ray_end,
                         float4* pool_pos_dt, uint32_t* chunk_ray, uint32_t* chunk_next, uint32_t pool_chunks,
                         uint32_t* chunk_cursor, float4* ray_dir_t, uint8_t* ray_end_out, uint32_t* ray_count,
-                        uint32_t* ray_head, FrameCounters* counters, cudaStream_t stream);
+                        uint32_t* ray_head, FrameCounters* counters, cudaStream_t stream, uint32_t wave = 0,
+                        uint32_t pause_at = 0xffffffffu, uint32_t* ray_ordinal = nullptr, uint32_t* ray_total = nullptr);
+//   wave / pause_at: rays are marched up to `pause_at` loop iterations in all; paused rays resume in the next wave from
+//   ray_dir_t.w (t), ray_ordinal (loop iterations) and ray_total (samples so far).
 
 // Rays only (generate_rays_from_camera_matrix): direction, t at the first occupied step, alive, pixel.
 void launch_generate_rays(const DevCfg& g, const DevView& v, const uint8_t* bits, float* dir, float* t,
@@ -116,8 +119,11 @@ void launch_composite(const DevCfg& g, const DevView& v, const DevPost& post, co
 // The same over per-ray chunk lists (frame path).
 void launch_composite_paged(const DevCfg& g, const DevView& v, const DevPost& post, uint64_t ray_begin, uint64_t ray_end,
                             const uint32_t* ray_head, const uint32_t* ray_count, const uint32_t* chunk_next,
-                            const float4* pool_shaded, const uint8_t* ray_end_reason, float4* out, float4* accum,
-                            float4* rgba_raw, uint32_t* n_composited, FrameCounters* counters, cudaStream_t stream);
+                            const float4* pool_shaded, uint8_t* ray_end_reason, float4* out, float4* accum,
+                            float4* rgba_raw, uint32_t* n_composited, FrameCounters* counters, cudaStream_t stream,
+                            uint32_t wave = 0, float4* ray_rgba = nullptr, uint32_t* ray_ncomp = nullptr);
+//   waves: a paused ray's running colour/opacity and consumed-sample count wait in ray_rgba / ray_ncomp; a ray whose
+//   pixel has been written is marked RAY_END_DONE in ray_end_reason.
 
 // Compositing over Coordinate records (stage entry srf_volume_rendering): no post stage.
 void launch_composite_coords(const DevCfg& g, const DevView& v, const uint64_t* offsets, uint64_t n_rays,

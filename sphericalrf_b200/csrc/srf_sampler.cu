@@ -96,22 +96,49 @@ k_ray_emit(const DevCfg g, const DevView v, const uint8_t* __restrict__ bits, co
 // warp march neighbouring pixels in near lockstep, so they usually run out of room together).  There is
 // no counting pass, no scan and no read-back: the field kernel later walks the pool densely, the
 // compositor walks each ray's chunk list.
+//
+// Waves.  A frame may run the sampler several times: a wave takes every running ray up to `pause_at` march
+// steps in all and leaves the rest of the march for the next wave (RAY_END_PAUSED; t in ray_dir_t.w, loop iterations and samples so far
+// in ray_ordinal / ray_total).  Between waves the field and the compositor run on what was emitted, and rays the
+// compositor has finished (RAY_END_DONE) are not marched further -- the counterpart of the reference's
+// rounds of <= 8 steps with compaction of dead rays (testbed.cu:523-583), with round sizes that keep the
+// kernels large.  The arithmetic of a ray does not depend on where it is paused.
 __global__ void __launch_bounds__(kBlock)
 k_march_paged(const DevCfg g, const DevView v, const uint8_t* __restrict__ bits, uint64_t ray_begin, uint64_t ray_end,
               float4* __restrict__ pool_pos_dt, uint32_t* __restrict__ chunk_ray, uint32_t* __restrict__ chunk_next,
               uint32_t pool_chunks, uint32_t* __restrict__ chunk_cursor, float4* __restrict__ ray_dir_t,
               uint8_t* __restrict__ ray_end_out, uint32_t* __restrict__ ray_count, uint32_t* __restrict__ ray_head,
-              FrameCounters* __restrict__ counters) {
+              FrameCounters* __restrict__ counters, uint32_t wave, uint32_t pause_at, uint32_t* __restrict__ ray_ordinal,
+              uint32_t* __restrict__ ray_total) {
     const uint64_t i = ray_begin + (uint64_t)blockIdx.x * kBlock + threadIdx.x;
     unsigned long long alive = 0, steps = 0, samples = 0;
     unsigned int err = 0;
     if (i < ray_end) {
-        const uint32_t pixel = shard_ray_pixel(v, i);
-        const RayInit r = init_ray(g, v, pixel);
-        uint32_t n = 0, end = RAY_END_BORN_DEAD, n_steps = 0, head = kNoChunk;
-        if (r.alive) {
+        V3 o, d;
+        MarchState st = {0.f, 0u, 0u};
+        uint32_t end = RAY_END_BORN_DEAD;
+        bool run = false;
+        if (wave == 0) {
+            const uint32_t pixel = shard_ray_pixel(v, i);
+            const RayInit r = init_ray(g, v, pixel);
+            o = r.o; d = r.d; st.t = r.t;
+            run = r.alive;
+            alive = r.alive ? 1 : 0;
+        } else {
+            end = ray_end_out[i];
+            if (end == RAY_END_PAUSED) {
+                const float4 q = ray_dir_t[i];
+                o = mk3(v.cam[3], v.cam[7], v.cam[11]);
+                d = mk3(q.x, q.y, q.z);
+                st.t = q.w; st.ordinal = ray_ordinal[i]; st.n = ray_total[i];
+                run = true;
+            }
+        }
+        uint32_t n = 0, head = kNoChunk;
+        const uint32_t steps_before = st.ordinal;
+        if (run) {
             uint32_t chunk = kNoChunk, fill = kChunkSamples;
-            end = march_ray(g, bits, r.o, r.d, r.t, &n_steps, [&](const V3& w, float dt, uint32_t, uint32_t, float) {
+            end = march_ray_from(g, bits, o, d, st, pause_at, [&](const V3& w, float dt, uint32_t, uint32_t, float) {
                 if (fill == kChunkSamples) {
                     const cg::coalesced_group lanes = cg::coalesced_threads();
                     uint32_t base = 0;
@@ -129,14 +156,16 @@ k_march_paged(const DevCfg g, const DevView v, const uint8_t* __restrict__ bits,
                 ++n;
                 return true;
             });
-            alive = 1;
             if (end == RAY_END_LIMIT) err |= 1u;
         }
-        ray_dir_t[i] = make_float4(r.d.x, r.d.y, r.d.z, r.t);
-        ray_end_out[i] = (uint8_t)end;
+        if (wave == 0 || run) {
+            ray_dir_t[i] = make_float4(d.x, d.y, d.z, st.t);
+            ray_end_out[i] = (uint8_t)end;
+            if (ray_ordinal) { ray_ordinal[i] = st.ordinal; ray_total[i] = st.n; }
+        }
         ray_count[i] = n;
         ray_head[i] = head;
-        steps = n_steps;
+        steps = st.ordinal - steps_before;
         samples = n;
     }
     alive = warp_sum_u64(alive);
@@ -301,11 +330,12 @@ void launch_ray_emit(const DevCfg& g, const DevView& v, const uint8_t* bits, con
 void launch_march_paged(const DevCfg& g, const DevView& v, const uint8_t* bits, uint64_t ray_begin, uint64_t ray_end,
                         float4* pool_pos_dt, uint32_t* chunk_ray, uint32_t* chunk_next, uint32_t pool_chunks,
                         uint32_t* chunk_cursor, float4* ray_dir_t, uint8_t* ray_end_out, uint32_t* ray_count,
-                        uint32_t* ray_head, FrameCounters* counters, cudaStream_t stream) {
+                        uint32_t* ray_head, FrameCounters* counters, cudaStream_t stream, uint32_t wave, uint32_t pause_at,
+                        uint32_t* ray_ordinal, uint32_t* ray_total) {
     if (ray_end <= ray_begin) return;
     k_march_paged<<<blocks_for(ray_end - ray_begin, kBlock), kBlock, 0, stream>>>(
         g, v, bits, ray_begin, ray_end, pool_pos_dt, chunk_ray, chunk_next, pool_chunks, chunk_cursor, ray_dir_t, ray_end_out,
-        ray_count, ray_head, counters);
+        ray_count, ray_head, counters, wave, pause_at, ray_ordinal, ray_total);
 }
 
 void launch_generate_rays(const DevCfg& g, const DevView& v, const uint8_t* bits, float* dir, float* t,

@@ -152,6 +152,11 @@ class Renderer:
                                      None if stats is None else C.byref(stats)))
         return (img, stats.as_dict()) if want_stats else img
 
+    def set_wave_schedule(self, steps):
+        """March steps per ray of the leading waves of a frame ([] = one pass); see srf_set_wave_schedule."""
+        a = (C.c_uint32 * max(len(steps), 1))(*steps)
+        self._ck(self.lib.srf_set_wave_schedule(self.ctx, a, len(steps)))
+
     def network_inference(self, coords):
         """srf_network_inference on host Coordinate records (n, 7) float32 -> (n, 4) float16 raw (r, g, b, sigma)."""
         import torch

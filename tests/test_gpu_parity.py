@@ -390,3 +390,42 @@ def test_staged_empty_space_tests_change_nothing(built_lib, oracle_mod, monkeypa
     assert np.array_equal(oc, gc) and np.array_equal(oo, go) and np.array_equal(ocell, gcell)
     assert _bits_equal(opd, gpd)
     assert oc.sum() > 0
+
+
+@pytest.mark.parametrize("kind,budgets", [("blobs", "1000,1000,1000"), ("blobs", "64,512"), ("net", "5,40,300"), ("blobs", "1")])
+def test_waves_change_nothing_but_the_work(built_lib, monkeypatch, kind, budgets):
+    """A frame rendered in waves (a budget of march steps per ray and wave, compositing in between, finished rays dropped) is
+    byte-identical to the one-pass frame; on a scene with opaque blobs it generates and evaluates fewer samples."""
+    sc = small_scene(kind=kind, sampling="Original", radius=4.0, width=32, height=24)
+    if kind == "blobs":
+        sc["blobs"][:, 4] = 4000.0            # opaque blobs: rays stop inside them
+    post = abi.default_post()
+    post.background_color[:] = [0.2, 0.4, 0.6, 1.0]
+    res = {}
+    for key, env in (("one", "0"), ("waves", budgets)):
+        monkeypatch.setenv("SRF_B200_WAVES", "0" if key == "one" else "7")
+        r = make_renderer(sc)
+        if key == "waves":
+            r.set_wave_schedule([int(x) for x in budgets.split(",")])      # replaces the environment's schedule
+        a = r.render_frame(sc["view"], post, want_raw=True, want_stats=True)
+        v2 = abi.View.from_buffer_copy(sc["view"]); v2.spp_index = 1
+        b = r.render_frame(v2, post, accum=a["accum"], want_raw=True)
+        v3 = abi.View.from_buffer_copy(sc["view"]); v3.render_mode = abi.MODE_DEPTH
+        c = r.render_frame(v3, post, want_raw=True)
+        res[key] = (a, b, c)
+    for x, y in zip(res["one"], res["waves"]):
+        for k in ("out", "accum", "rgba_raw"):
+            assert _bits_equal(x[k], y[k]), k
+    s1, s2 = res["one"][0]["stats"], res["waves"][0]["stats"]
+    assert s1["n_samples_composited"] == s2["n_samples_composited"] and s1["n_rays_hit"] == s2["n_rays_hit"]
+    assert s1["n_rays_alive"] == s2["n_rays_alive"]
+    assert s2["n_samples"] <= s1["n_samples"] and s2["n_march_steps"] <= s1["n_march_steps"]
+    if kind == "blobs":
+        assert s1["n_samples_composited"] < s1["n_samples"]                 # rays do terminate early here
+        if budgets == "1000,1000,1000":                                     # the blobs start ~1500 steps into the march
+            assert s2["n_samples"] < s1["n_samples"]                        # and the waves skip what lies behind
+    # per-ray sampler counts are those of the whole march, whatever the schedule
+    counts_waves = make_renderer(sc).render_frame(sc["view"], post, want_counts=True)["n_samples"]
+    monkeypatch.setenv("SRF_B200_WAVES", "0")
+    counts_one = make_renderer(sc).render_frame(sc["view"], post, want_counts=True)["n_samples"]
+    assert np.array_equal(counts_waves, counts_one) and int(counts_one.sum()) == s1["n_samples"]
