@@ -96,6 +96,7 @@ WORKLOAD_NAMES = {
     "1": "config1 full inference frame {w}x{h}, fp16 network, 128^3 bitfield",
     "0O": "config0-O sampler+compositing, analytic blob field fp32, Original sampling, {w}x{h}",
     "0D": "config0-D sampler+compositing, analytic blob field fp32, Disparity sampling, {w}x{h}",
+    "0X": "config0-O with opaque blobs (rays saturate early), analytic blob field fp32, Original sampling, {w}x{h}",
     "4": "config4 dense inward-facing scene, fp16 network, Original sampling, 2048-sample cap, {w}x{h}",
 }
 
@@ -104,7 +105,7 @@ def build_scene():
     from sphericalrf_b200 import abi, synth
     if WORKLOAD == "1":
         return synth.scene_config1(grid_size=128, width=WIDTH, height=HEIGHT)
-    if WORKLOAD in ("0O", "0D"):
+    if WORKLOAD in ("0O", "0D", "0X"):
         return synth.scene_config0(WORKLOAD[1], 128, WIDTH, HEIGHT)
     if WORKLOAD == "4":
         return synth.scene_config4(128, WIDTH, HEIGHT)
@@ -427,7 +428,7 @@ def main():
     args = ap.parse_args()
     global WIDTH, HEIGHT, WORKLOAD
     WORKLOAD = args.workload
-    if WORKLOAD in ("0O", "0D"):
+    if WORKLOAD in ("0O", "0D", "0X"):
         WIDTH, HEIGHT = 800, 800
     elif WORKLOAD == "4":
         WIDTH, HEIGHT = 3840, 2160

@@ -340,7 +340,7 @@ srf_status srf_render_frame_scatter(srf_ctx* ctx, const srf_view_t* view, const 
    the point where a ray saturates are never evaluated.  Here a frame runs in a few large waves: wave k takes every
    unfinished ray steps[k] march steps further, the field and the compositor run on what was emitted, rays whose
    pixel is final are dropped; a last wave finishes whatever is left.  The image does not depend on the schedule.
-   Default {128, 512}; n = 0 renders each frame in one pass.  (A call that asks srf_render_frame for per-ray
+   Default {128, 512, 2048, 8192}; n = 0 renders each frame in one pass.  (A call that asks srf_render_frame for per-ray
    sampler counts always runs in one pass.) */
 srf_status srf_set_wave_schedule(srf_ctx* ctx, const uint32_t* steps, uint32_t n);
 

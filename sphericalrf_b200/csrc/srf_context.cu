@@ -66,8 +66,8 @@ struct srf_ctx {
     // per-frame scratch
     DevBuf train_flags, train_rank, loss_rgb;
     DevBuf ray_ordinal, ray_total, ray_rgba, ray_ncomp;        // per-ray state between the waves of a frame
-    uint32_t wave_budget[8] = {128, 512, 0, 0, 0, 0, 0, 0};   // march steps per ray in waves 0, 1, ...; a final unlimited wave follows
-    uint32_t n_wave_budgets = 2;
+    uint32_t wave_budget[8] = {128, 512, 2048, 8192, 0, 0, 0, 0};   // march steps per ray in waves 0, 1, ...; a final unlimited wave follows
+    uint32_t n_wave_budgets = 4;
     DevBuf ray_dir_t, ray_end, counts, offsets, scan_scratch;
     DevBuf pos_dt, sample_ray, rgbs;
     DevBuf pool_pos, pool_shaded, chunk_ray, chunk_next, ray_head;   // paged frame path

@@ -208,14 +208,19 @@ def sampler_config(sampling="Disparity", grid_size=128):
 
 
 def scene_config0(variant="D", grid_size=128, width=800, height=800):
-    """Sampler + compositing only, analytic blob field in fp32."""
-    cfg = sampler_config("Original" if variant == "O" else "Disparity", grid_size)
+    """Sampler + compositing only, analytic blob field in fp32.  Variant "X" is variant "O" with the blob
+    densities raised 80-fold after the grid is built: an opaque scene, as a trained one is, where every ray that
+    meets a blob saturates inside it (same bitfield and march as "O", early termination everywhere)."""
+    cfg = sampler_config("Disparity" if variant == "D" else "Original", grid_size)
     cfg.field_type = abi.FIELD_BLOBS
     cfg.density_activation = abi.ACT_NONE
     cfg.rgb_activation = abi.ACT_LOGISTIC
     blobs = blob_scene(1000, 32, 50.0)
     cmap = color_map(1001)
     grid, reachable = density_grid_from_blobs(cfg, blobs)
+    if variant == "X":
+        blobs = blobs.copy()
+        blobs[:, 4] *= 80.0
     cam = orbit_camera(4.0, 20.0, 30.0)
     rfl = relative_focal_length(50.0, width, height)
     return dict(cfg=cfg, blobs=blobs, color_map=cmap, grid=grid, reachable=reachable,
