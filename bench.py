@@ -287,7 +287,7 @@ def run_ours(args):
     for _ in range(args.steps):
         r.render_frame_device(view, post, out[0], accum, None, None, stats, None)
         t_field += stats.ms_field; t_sampler += stats.ms_sampler; t_comp += stats.ms_composite
-        n_samples = stats.n_samples; n_batches = stats.n_batches
+        n_samples = stats.n_samples; n_batches = stats.n_batches * max(stats.n_waves, 1)   # launches of each stage per frame
     r.set_timing(False)
     t_field /= args.steps; t_sampler /= args.steps; t_comp /= args.steps
     if rank != 0:
@@ -295,7 +295,7 @@ def run_ours(args):
             dist.destroy_process_group()
         return
     peak, peak_kind = _peaks()
-    launches_per_frame = 3 * n_batches               # march, field, composite per batch of rays
+    launches_per_frame = 3 * n_batches               # march, field, composite per batch of rays and wave
     achieved = ALG_BYTES_PER_SAMPLE * n_samples / max(n_batches, 1) / (t_field / max(n_batches, 1) * 1e-3) / 1e9 if t_field > 0 else 0.0
     roof_kernel = "k_field_network_tc (hash-grid gather + tcgen05 MLPs + shading)"
     roof_ms = t_field / max(n_batches, 1)
@@ -313,7 +313,8 @@ def run_ours(args):
         "config": {"workload": workload_name(),
                    "frames_per_step": n_views, "rays_per_frame": WIDTH * HEIGHT, "samples_per_frame_shard": int(n_samples),
                    "partition": f"rows in blocks of 8 round-robin over {world} rank(s)", "gather": gather_kind,
-                   "l2": "per-frame working set (sample buffers) far larger than L2; no flush needed"},
+                   "l2": "per-frame working set (sample buffers) far larger than L2; no flush needed",
+                   "schedule": f"{stats.n_batches} ray batch(es) x {stats.n_waves} wave(s) per frame (trailing waves empty when every ray has ended)"},
         "frames_per_s": n_views / (ms_step * 1e-3),
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "Mrays/s", "h2d_bytes_per_step": int(C.sizeof(abi.View) + C.sizeof(abi.Post)) * n_views,

@@ -134,6 +134,7 @@ typedef struct srf_frame_stats_t {
     uint32_t n_batches;        /* sample-buffer batches the frame was cut into */
     uint32_t error_flags;      /* bit 0: a bounded device loop hit its limit */
     float    ms_sampler, ms_field, ms_composite, ms_post; /* CUDA-event times, when timing is on */
+    uint32_t n_waves;          /* sampler / field / compositor launches per batch (see srf_set_wave_schedule) */
 } srf_frame_stats_t;
 
 typedef struct srf_ctx srf_ctx;

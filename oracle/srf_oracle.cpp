@@ -1321,6 +1321,7 @@ int srfo_render_frame(const srf_config_t* cfg, const srf_view_t* view, const srf
         stats->n_rays = ray_count; stats->n_rays_alive = s_alive; stats->n_march_steps = s_steps;
         stats->n_samples = s_samples; stats->n_samples_composited = s_comp; stats->n_rays_hit = s_hit;
         stats->n_batches = 1;
+        stats->n_waves = 1;
     }
     return 0;
 }

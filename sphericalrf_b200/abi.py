@@ -86,6 +86,7 @@ class FrameStats(C.Structure):
         ("n_samples", C.c_uint64), ("n_samples_composited", C.c_uint64), ("n_rays_hit", C.c_uint64),
         ("n_batches", C.c_uint32), ("error_flags", C.c_uint32),
         ("ms_sampler", C.c_float), ("ms_field", C.c_float), ("ms_composite", C.c_float), ("ms_post", C.c_float),
+        ("n_waves", C.c_uint32),
     ]
 
     def as_dict(self):

@@ -917,8 +917,15 @@ static srf_status render_frame_impl(srf_ctx* ctx, const srf_view_t* view, const 
     const uint64_t limit = ctx->reserve_samples ? ctx->reserve_samples : kAutoSampleCapacity;
     uint64_t rays_per_batch = limit / per_ray_slots;
     if (rays_per_batch == 0) return fail(ctx, SRF_ERR_CAPACITY, "srf_reserve limit is smaller than the samples one ray may emit");
-    if (rays_per_batch >= v.n_rays) rays_per_batch = v.n_rays;
-    else if (rays_per_batch > 128) rays_per_batch -= rays_per_batch % 128;
+    if (rays_per_batch >= v.n_rays) {
+        rays_per_batch = v.n_rays;
+    } else {
+        // equal batches (no small tail batch), in multiples of 128 rays
+        if (rays_per_batch > 128) rays_per_batch -= rays_per_batch % 128;
+        const uint64_t n_b = (v.n_rays + rays_per_batch - 1) / rays_per_batch;
+        const uint64_t even = ((v.n_rays + n_b - 1) / n_b + 127) / 128 * 128;
+        if (even < rays_per_batch) rays_per_batch = even;
+    }
     const uint64_t pool_slots = rays_per_batch * per_ray_slots;
     if (pool_slots / kChunkSamples >= 0xffffffffull) return fail(ctx, SRF_ERR_CAPACITY, "sample pool exceeds 2^32 chunks");
     const uint32_t pool_chunks = (uint32_t)(pool_slots / kChunkSamples);
@@ -1005,6 +1012,7 @@ static srf_status render_frame_impl(srf_ctx* ctx, const srf_view_t* view, const 
         stats->n_samples_composited = ctx->h_counters->n_composited;
         stats->n_rays_hit = ctx->h_counters->n_hit;
         stats->n_batches = n_batches;
+        stats->n_waves = n_waves;
         stats->error_flags = ctx->h_counters->error_flags;
         stats->ms_sampler = ms_sampler; stats->ms_field = ms_field; stats->ms_composite = ms_comp; stats->ms_post = 0.f;
         if (stats->error_flags & 1u) return fail(ctx, SRF_ERR_TIMEOUT, "a ray hit the march loop's iteration bound");
