@@ -91,7 +91,7 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-WORKLOAD = "1"          # BASELINE configuration: "1" (the benchmark), "0O", "0D", "4": other configurations, for the record
+WORKLOAD = "1"          # benchmark configuration: "1" (the headline), "0O", "0D", "0X", "4": other configurations, for the record
 WORKLOAD_NAMES = {
     "1": "config1 full inference frame {w}x{h}, fp16 network, 128^3 bitfield",
     "0O": "config0-O sampler+compositing, analytic blob field fp32, Original sampling, {w}x{h}",
@@ -423,7 +423,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"], help="N > 1: how tiles reach rank 0")
-    ap.add_argument("--workload", default="1", choices=sorted(WORKLOAD_NAMES), help="BASELINE configuration; the benchmark is 1")
+    ap.add_argument("--workload", default="1", choices=sorted(WORKLOAD_NAMES), help="configuration to time; the benchmark is 1")
     ap.add_argument("--res", default=None, help="WxH: a smaller image of the same scene, for profiler captures only "
                                                 "(the benchmark number is the default 1245x825)")
     args = ap.parse_args()

@@ -1225,8 +1225,8 @@ int srfo_network_density(const srf_config_t* cfg, const srfo_model_t* model, con
     return 0;
 }
 
-/* Testbed::render_frame (testbed.cu:479-606) per ray; see SURVEY of per-ray semantics in the
-   function comments above. */
+/* Testbed::render_frame (testbed.cu:479-606) per ray: the per-ray semantics of its host loop are
+   described at march_ray and finish_pixel above. */
 int srfo_render_frame(const srf_config_t* cfg, const srf_view_t* view, const srf_post_t* post,
                       const uint8_t* bitfield, const srfo_model_t* model, uint64_t ray_first,
                       uint64_t ray_count, float* out, float* accum, float* rgba_raw,
