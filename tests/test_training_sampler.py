@@ -152,3 +152,32 @@ def test_sampler_init_mask_bit_exact(built_lib, oracle_mod, grid_dist, cascades)
     r.upload_density_grid(np.full(32 ** 3 * cascades, 7.0, np.float32))
     r.sampler_init(None, init_grid_with_mask=False, rng_seed=3)
     assert not r.download_density_grid().any()
+
+
+@pytest.mark.gpu
+def test_training_sampler_large_batch(built_lib, oracle_mod):
+    """32 768 rays (16 tiles of the exclusive scans), a sample buffer that overflows part of the way through:
+    every output equals the oracle's serial execution."""
+    sc, views = _scene(warp=abi.WARP_ERP, sampling="Disparity")
+    views = synth.training_views(77, n_images=7, width=64, height=48, radius=0.4, zero_probability=0.1)
+    r = make_renderer(sc)
+    bits = r.download_bitfield()
+    rng = _rng(oracle_mod, 99)
+    n_rays = 32768
+    probe = oracle_mod.sample_training_rays(sc["cfg"], views, bits, n_rays, 12345, 1 << 23, rng, True)
+    total = probe["n_samples_total"]
+    assert probe["n_rays"] > n_rays // 2 and total > 100000
+    n_coords = int(total * 0.7)                                    # the last ~30 % of the rays find no room
+    want = oracle_mod.sample_training_rays(sc["cfg"], views, bits, n_rays, 12345, n_coords, rng, True)
+    got = r.sample_training_rays(views, n_rays, 12345, n_coords, rng.state, rng.inc, True)
+    assert 0 < want["n_rays"] < probe["n_rays"]
+    assert got["n_rays"] == want["n_rays"] and got["n_samples_total"] == want["n_samples_total"] == total
+    assert np.array_equal(got["numsteps"], want["numsteps"])
+    assert got["rays"].tobytes() == want["rays"].tobytes() and got["rgba"].tobytes() == want["rgba"].tobytes()
+    used = int(want["numsteps"][-1, 0]) + int(want["numsteps"][-1, 1])
+    assert got["coords"][:used].tobytes() == want["coords"][:used].tobytes()
+    # every emitted position lies in an occupied cell of the bitfield (sinusoidal warp, one cascade: cell = floor(w * N))
+    w = want["coords"][:used, :3]
+    cell = np.clip((w * 32).astype(np.int64), 0, 31)
+    idx = synth.morton3d(cell[:, 0].astype(np.uint32), cell[:, 1].astype(np.uint32), cell[:, 2].astype(np.uint32))
+    assert ((bits[idx >> 3] >> (idx & 7)) & 1).all()
