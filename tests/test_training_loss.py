@@ -157,3 +157,26 @@ def test_training_compositor_bit_exact(built_lib, oracle_mod, case):
             assert got["loss"].tobytes() == want["loss"].tobytes()
             if p.regularization_type == abi.REG_DISTORTION:
                 assert got["reg"][:used].tobytes() == want["reg"][:used].tobytes()
+
+
+@pytest.mark.gpu
+def test_training_compositor_large_batch(built_lib, oracle_mod):
+    """6 000 rays (three tiles of the scan over consumed counts), capacity reached part of the way through."""
+    from sphericalrf_b200.testbed import Renderer
+    idx, coords, net, rgba = _batch(123, n_rays=6000, max_steps=60, early=True)
+    n = idx.shape[0]
+    cfg = _cfg(til=False, thr=1e-3)
+    cfg.field_type = abi.FIELD_BLOBS
+    r = Renderer(cfg, 0)
+    r.upload_density_grid(np.full(32 ** 3, 0.5, np.float32))
+    r.update_grid_bitfield()
+    for cap in (1 << 18, 40000):
+        p = _params(n, cap, loss=abi.LOSS_SMOOTH_L1, space=abi.COLOR_SRGB, random_bg=True, reg=abi.REG_DISTORTION)
+        want = oracle_mod.volume_rendering_loss(cfg, p, n, idx, rgba, coords, net, 0.5)
+        got = r.volume_rendering_loss(p, n, idx, rgba, coords, net)
+        assert got["n_compacted"] == want["n_compacted"] and np.array_equal(got["indices"], want["indices"])
+        used = int(want["indices"][:, 0].sum())
+        assert used == min(cap, want["n_compacted"])
+        assert got["compacted_coords"][:used].tobytes() == want["compacted_coords"][:used].tobytes()
+        assert got["dloss"][:used].view(np.uint16).tobytes() == want["dloss"][:used].view(np.uint16).tobytes()
+        assert got["loss"].tobytes() == want["loss"].tobytes() and got["reg"][:used].tobytes() == want["reg"][:used].tobytes()
