@@ -2,13 +2,13 @@
 //
 // Same data flow as srf_field.cu (NGPNetwork::inference_mixed_precision,
 // internal/network/ngp_network.h:212-279), different engine for the five dense layers.  A CTA of
-// 256 threads is two independent groups of 128 threads; a group owns a tile of 128 samples: thread
+// 1024 threads -- one per SM -- is eight independent groups of 128 threads; a group owns a tile of 128 samples: thread
 // r gathers and interpolates the hash-grid features of sample r straight into the shared-memory
 // image of the MMA's A operand; the group's first thread issues tcgen05.mma (M = 128 samples,
 // N = 64 or 16 neurons, K = 16 per instruction) with the fp32 accumulator in tensor memory; after
 // the commit barrier every thread reads its own sample's row back with tcgen05.ld, applies ReLU,
 // rounds to fp16 and writes the next layer's A operand.  Weights (20 KB) sit in shared memory in the
-// B-operand layout for the lifetime of the CTA and are shared by both groups.
+// B-operand layout for the lifetime of the CTA and are shared by all groups.
 //
 // Operand layout (no swizzle, K-major): a matrix of R rows x K halves is stored as K/8 column
 // blocks; block j holds, for every row, the 8 halves k = 8j..8j+7 as one 16-byte unit, rows
@@ -21,9 +21,14 @@
 // has finished reading shared memory by then).  The spherical harmonics wait in registers.
 //
 // Tensor memory: 64 columns per group (all 64 for the 64-wide layers, the first 16 for the 16-wide
-// ones), 128 per CTA.  Four CTAs fit an SM (4 x 52 KB shared memory, 4 x 128 = 512 columns, 32
-// warps at <= 64 registers per thread); a fifth cannot be resident, so tensor-memory allocation
-// never has to wait.
+// ones): the CTA allocates all 512 columns of its SM.  Its 1024 threads at 64 registers take the whole
+// register file and its 148 KB of shared memory more than half of the SM's, so a second CTA can never be
+// resident and the allocation never has to wait.
+//
+// Why one large CTA instead of four of 256 threads: the gathers of the encoding live on L1 hits
+// (neighbouring samples share cells), and L1 is what the unified 256 KB array has left after shared
+// memory.  Four CTAs carried four copies of the 20 KB weight images (208 KB of shared memory, ~48 KB of
+// L1); one CTA carries one copy (148 KB, ~92 KB of L1).  Measured on the benchmark frame: 208 -> 183 ms.
 //
 // Every wait on a commit barrier is bounded; on expiry the group raises an error flag and leaves its
 // tile loop; the CTA frees its tensor memory and returns.
@@ -34,9 +39,10 @@ namespace srf {
 
 namespace {
 
-constexpr int kTcBlock = 256;                   // two groups of 128 threads
+constexpr int kGroups = 8;                      // groups of 128 threads per CTA
 constexpr int kGroup = 128;
-constexpr uint32_t kTmemCols = 128;               // 64 per group
+constexpr int kTcBlock = kGroup * kGroups;
+constexpr uint32_t kTmemCols = 64 * kGroups;      // 64 per group: the whole tensor memory of the SM
 constexpr uint32_t kWaitLimit = 1u << 20;
 
 // shared-memory map (bytes)
@@ -45,13 +51,14 @@ constexpr int kSmW_D2 = kSmW_D1 + 4 * 64 * 16;    // [8][16][8]
 constexpr int kSmW_C1 = kSmW_D2 + 8 * 16 * 16;    // [4][64][8]
 constexpr int kSmW_C2 = kSmW_C1 + 4 * 64 * 16;    // [8][64][8]
 constexpr int kSmW_C3 = kSmW_C2 + 8 * 64 * 16;    // [8][16][8]
-constexpr int kSmAct = kSmW_C3 + 8 * 16 * 16;     // 2 groups x [8][128][8]: the activation region
+constexpr int kSmAct = kSmW_C3 + 8 * 16 * 16;     // kGroups x [8][128][8]: the activation regions
 constexpr int kActBytes = 8 * 128 * 16;
-constexpr int kSmBar = kSmAct + 2 * kActBytes;    // 2 mbarriers (16 B) + tensor-memory base (4 B)
-constexpr int kSmEnc = kSmBar + 32;               // per-level constants of the encoding
+constexpr int kSmBar = kSmAct + kGroups * kActBytes;   // kGroups mbarriers + tensor-memory base (4 B)
+constexpr int kSmEnc = kSmBar + kGroups * 8 + 16;  // per-level constants of the encoding
 constexpr int kSmTotal = kSmEnc + (int)sizeof(EncMeta);
-static_assert(kSmTotal > 227 * 1024 / 5, "a fifth CTA must not fit: 5 x 128 tensor-memory columns exceed 512");
-static_assert(kSmTotal <= 227 * 1024 / 4, "four CTAs per SM are intended");
+static_assert(kTmemCols == 512, "the CTA owns the SM's tensor memory");
+static_assert(kSmTotal > 227 * 1024 / 2, "a second CTA must not fit: it would wait for tensor memory forever");
+static_assert(kSmTotal <= 227 * 1024, "shared memory of one SM");
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -142,25 +149,19 @@ __device__ __forceinline__ void store_units(const uint32_t (&acc)[16], unsigned 
     *reinterpret_cast<uint4*>(image + ((size_t)(j0 + 1) * 128 + row) * 16) = u1;
 }
 
-// group-local barriers with literal ids 1 and 2 (id 0 is __syncthreads); literal ids keep the CTA's
-// barrier count at 3
+// group-local named barriers 1..kGroups (id 0 is __syncthreads)
 __device__ __forceinline__ void group_sync(int group) {
-    if (group == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
-    else asm volatile("bar.sync 2, 128;" ::: "memory");
+    asm volatile("bar.sync %0, 128;" :: "r"(group + 1) : "memory");
 }
 __device__ __forceinline__ bool group_any(int group, bool v) {
     uint32_t r;
-    if (group == 0)
-        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.or.pred q, 1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}\n"
-                     : "=r"(r) : "r"((uint32_t)v) : "memory");
-    else
-        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.or.pred q, 2, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}\n"
-                     : "=r"(r) : "r"((uint32_t)v) : "memory");
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.or.pred q, %2, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}\n"
+                 : "=r"(r) : "r"((uint32_t)v), "r"(group + 1) : "memory");
     return r != 0;
 }
 
 template <int F>
-__global__ void __launch_bounds__(kTcBlock, 4)
+__global__ void __launch_bounds__(kTcBlock, 1)
 k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __half* __restrict__ wd,
                    const __half* __restrict__ wc, const float4* __restrict__ pos_dt,
                    const uint32_t* __restrict__ sample_ray, const float4* __restrict__ ray_dir_t,
@@ -172,7 +173,7 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
     const int tid = threadIdx.x, warp = tid >> 5;
     const int group = tid >> 7, row = tid & 127;
     uint64_t* bar_ptr = reinterpret_cast<uint64_t*>(smem + kSmBar) + group;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kSmBar + 16);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kSmBar + kGroups * 8);
     const uint32_t bar = smem_u32(bar_ptr);
 
     EncMeta* enc_meta = reinterpret_cast<EncMeta*>(smem + kSmEnc);
@@ -239,7 +240,7 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
         return !group_any(group, expired);
     };
     const uint64_t n_tiles = (n + kGroup - 1) / kGroup;
-    for (uint64_t tile = (uint64_t)blockIdx.x * 2 + group; tile < n_tiles; tile += (uint64_t)gridDim.x * 2) {
+    for (uint64_t tile = (uint64_t)blockIdx.x * kGroups + group; tile < n_tiles; tile += (uint64_t)gridDim.x * kGroups) {
         const uint64_t s = tile * kGroup + row;
         // ---- encode: one thread per sample, written as 16-byte units of the A image ----
         float x = 0.f, y = 0.f, z = 0.f, dx = 0.5f, dy = 0.5f, dz = 0.5f;
@@ -354,11 +355,15 @@ void launch_field_network_tc(const NetMeta& net, const __half* table, const __ha
     // per device and cheap: set on every launch rather than cached per process
     cudaFuncSetAttribute(k_field_network_tc<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmTotal);
     cudaFuncSetAttribute(k_field_network_tc<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmTotal);
+    // no more shared memory than the CTA needs: the rest of the unified array serves the gathers as L1
+    constexpr int kCarveout = (kSmTotal * 100 + 228 * 1024 - 1) / (228 * 1024);
+    cudaFuncSetAttribute(k_field_network_tc<2>, cudaFuncAttributePreferredSharedMemoryCarveout, kCarveout);
+    cudaFuncSetAttribute(k_field_network_tc<4>, cudaFuncAttributePreferredSharedMemoryCarveout, kCarveout);
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const uint64_t tiles = (n + kTcBlock - 1) / kTcBlock;    // pairs of 128-sample tiles
-    const uint64_t cap = (uint64_t)sms * 4;                  // four resident CTAs per SM
+    const uint64_t tiles = (n + kTcBlock - 1) / kTcBlock;    // kGroups 128-sample tiles per CTA and sweep
+    const uint64_t cap = (uint64_t)sms;                      // one resident CTA per SM
     const int grid = n_chunks_dev ? (int)cap : (int)(tiles < cap ? tiles : cap);
     DevCfg g0; DevView v0;
     memset(&g0, 0, sizeof(g0)); memset(&v0, 0, sizeof(v0));
