@@ -106,16 +106,25 @@ __device__ __forceinline__ void hash_encode_range(const EncMeta* m, const __half
         const uint32_t y0 = c.iy * L.res, z0 = c.iz * L.r2;
         const uint32_t xy[4] = {c.ix + y0, c.ix + 1u + y0, c.ix + y0 + L.res, c.ix + 1u + y0 + L.res};
         uint32_t raw[8][F / 2];
+        if (xy[3] + z0 + L.r2 < L.size) {        // the largest of the eight indices: no corner wraps (almost always)
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            uint32_t i = xy[k & 3] + ((k & 4) ? z0 + L.r2 : z0);
-            if (i >= L.size) {                   // only cells touching the upper faces wrap
-                i -= L.size;
-                if (i >= L.size) i %= L.size;
+            for (int k = 0; k < 8; ++k) {
+                const uint32_t* e = base + (size_t)(xy[k & 3] + ((k & 4) ? z0 + L.r2 : z0)) * (F / 2);
+#pragma unroll
+                for (int f = 0; f < F / 2; ++f) raw[k][f] = __ldg(e + f);
             }
-            const uint32_t* e = base + (size_t)i * (F / 2);
+        } else {                                 // cells touching the upper faces of a dense level
 #pragma unroll
-            for (int f = 0; f < F / 2; ++f) raw[k][f] = __ldg(e + f);
+            for (int k = 0; k < 8; ++k) {
+                uint32_t i = xy[k & 3] + ((k & 4) ? z0 + L.r2 : z0);
+                if (i >= L.size) {
+                    i -= L.size;
+                    if (i >= L.size) i %= L.size;
+                }
+                const uint32_t* e = base + (size_t)i * (F / 2);
+#pragma unroll
+                for (int f = 0; f < F / 2; ++f) raw[k][f] = __ldg(e + f);
+            }
         }
         level_finish<F>(c, raw, l, out);
     }
