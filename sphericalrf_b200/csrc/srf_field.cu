@@ -31,7 +31,7 @@ k_field_network(const NetMeta net, const __half* __restrict__ table, const __hal
     __shared__ __align__(16) __half sW[kWeightHalves];
     __shared__ __align__(16) __half sRows[kFieldBlock * kRowLd];
     __shared__ EncMeta enc_meta;
-    prepare_enc_meta(net, &enc_meta);
+    prepare_enc_meta(net, table, &enc_meta);
     load_weights(wd, wc, sW, true);
     __syncthreads();
 
@@ -151,7 +151,7 @@ k_field_density(const NetMeta net, const __half* __restrict__ table, const __hal
     __shared__ __align__(16) __half sW[kOffC1];
     __shared__ __align__(16) __half sRows[kFieldBlock * kRowLd];
     __shared__ EncMeta enc_meta;
-    prepare_enc_meta(net, &enc_meta);
+    prepare_enc_meta(net, table, &enc_meta);
     load_weights(wd, nullptr, sW, false);
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;

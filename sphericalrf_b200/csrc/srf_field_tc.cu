@@ -177,7 +177,7 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
     const uint32_t bar = smem_u32(bar_ptr);
 
     EncMeta* enc_meta = reinterpret_cast<EncMeta*>(smem + kSmEnc);
-    prepare_enc_meta(net, enc_meta);
+    prepare_enc_meta(net, table, enc_meta);
     load_weight_image(wd, 64, 32, smem + kSmW_D1);
     load_weight_image(wd + 64 * 32, 16, 64, smem + kSmW_D2);
     load_weight_image(wc, 64, 32, smem + kSmW_C1);

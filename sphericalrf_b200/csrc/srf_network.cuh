@@ -22,7 +22,8 @@ namespace srf {
 
 struct EncLevel {
     float scale;
-    uint32_t res, r2, offset, size;      // offset in entries
+    uint32_t res, r2, size, mask, pad;   // mask = size - 1 (hashed levels hold 2^k entries)
+    const uint32_t* base;                // first entry of the level, as 32-bit words
 };
 struct EncMeta {
     EncLevel level[kMaxLevels];
@@ -31,12 +32,13 @@ struct EncMeta {
 
 // Filled once per CTA (all threads call it, followed by a barrier the caller provides).
 // Dense levels always precede hashed ones: the resolution grows with the level.
-__device__ __forceinline__ void prepare_enc_meta(const NetMeta& net, EncMeta* m) {
+__device__ __forceinline__ void prepare_enc_meta(const NetMeta& net, const __half* __restrict__ table, EncMeta* m) {
     const int t = threadIdx.x;
     if (t < (int)net.n_levels) {
         const LevelMeta& L = net.level[t];
         m->level[t].scale = L.scale; m->level[t].res = L.res; m->level[t].r2 = L.res * L.res;
-        m->level[t].offset = L.offset; m->level[t].size = L.size;
+        m->level[t].size = L.size; m->level[t].mask = L.size - 1u; m->level[t].pad = 0u;
+        m->level[t].base = reinterpret_cast<const uint32_t*>(table) + (size_t)L.offset * (net.n_features / 2);
     }
     if (t == 0) {
         int d = 0;
@@ -95,13 +97,13 @@ __device__ __forceinline__ void level_finish(const LevelCell& c, const uint32_t 
 template <int F>
 __device__ __forceinline__ void hash_encode_range(const EncMeta* m, const __half* __restrict__ table, float x, float y,
                                                   float z, int l_begin, int l_end, uint32_t (&out)[16]) {
-    const uint32_t* table32 = reinterpret_cast<const uint32_t*>(table);
+    (void)table;                                  // the level bases in `m` were derived from it
     const int n_dense = m->n_dense;
     const int dense_end = l_end < n_dense ? l_end : n_dense;
 #pragma unroll 1
     for (int l = l_begin; l < dense_end; ++l) {
         const EncLevel L = m->level[l];
-        const uint32_t* base = table32 + (size_t)L.offset * (F / 2);
+        const uint32_t* base = L.base;
         const LevelCell c = level_cell(L.scale, x, y, z);
         const uint32_t y0 = c.iy * L.res, z0 = c.iz * L.r2;
         const uint32_t xy[4] = {c.ix + y0, c.ix + 1u + y0, c.ix + y0 + L.res, c.ix + 1u + y0 + L.res};
@@ -131,8 +133,8 @@ __device__ __forceinline__ void hash_encode_range(const EncMeta* m, const __half
 #pragma unroll 2
     for (int l = l_begin > n_dense ? l_begin : n_dense; l < l_end; ++l) {
         const float scale = m->level[l].scale;
-        const uint32_t mask = m->level[l].size - 1u;
-        const uint32_t* base = table32 + (size_t)m->level[l].offset * (F / 2);
+        const uint32_t mask = m->level[l].mask;
+        const uint32_t* base = m->level[l].base;
         const LevelCell c = level_cell(scale, x, y, z);
         const uint32_t y0 = c.iy * 2654435761u, y1 = y0 + 2654435761u;
         const uint32_t z0 = c.iz * 805459861u, z1 = z0 + 805459861u;

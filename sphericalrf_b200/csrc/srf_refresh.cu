@@ -32,7 +32,7 @@ k_refresh_sample(const DevCfg g, const NetMeta net, const __grid_constant__ Refr
     // below fully unrolled every multiply-add names its weight as a constant operand, so the layer costs no
     // load instructions at all (a shared-memory copy of the matrix made this kernel L1/shared-memory bound).
     __shared__ EncMeta enc_meta;
-    prepare_enc_meta(net, &enc_meta);
+    prepare_enc_meta(net, table, &enc_meta);
     __syncthreads();
     const uint32_t tid = blockIdx.x * kRefreshBlock + threadIdx.x;
     if (tid >= n_elements) return;
