@@ -65,6 +65,7 @@ struct srf_ctx {
 
     // per-frame scratch
     DevBuf train_flags, train_rank, loss_rgb;
+    DevBuf ray_sh;                                             // 16 SH halves per ray (frame path, network field)
     DevBuf ray_ordinal, ray_total, ray_rgba, ray_ncomp;        // per-ray state between the waves of a frame
     uint32_t wave_budget[8] = {128, 512, 2048, 8192, 0, 0, 0, 0};   // march steps per ray in waves 0, 1, ...; a final unlimited wave follows
     uint32_t n_wave_budgets = 4;
@@ -481,7 +482,7 @@ void srf_destroy(srf_ctx* ctx) {
     if (!ctx) return;
     DeviceGuard guard(ctx->device);
     void* ptrs[] = {ctx->grid, ctx->grid_current, ctx->partial_a, ctx->partial_b, ctx->mean, ctx->bits, ctx->table,
-                    ctx->w_density, ctx->w_rgb, ctx->skip_shell, ctx->skip_yz, ctx->train_flags.p, ctx->train_rank.p, ctx->loss_rgb.p, ctx->ray_ordinal.p, ctx->ray_total.p, ctx->ray_rgba.p, ctx->ray_ncomp.p, ctx->blobs, ctx->cmap, ctx->d_counters, ctx->ray_dir_t.p, ctx->ray_end.p,
+                    ctx->w_density, ctx->w_rgb, ctx->skip_shell, ctx->skip_yz, ctx->train_flags.p, ctx->train_rank.p, ctx->loss_rgb.p, ctx->ray_sh.p, ctx->ray_ordinal.p, ctx->ray_total.p, ctx->ray_rgba.p, ctx->ray_ncomp.p, ctx->blobs, ctx->cmap, ctx->d_counters, ctx->ray_dir_t.p, ctx->ray_end.p,
                     ctx->counts.p, ctx->offsets.p, ctx->scan_scratch.p, ctx->pos_dt.p, ctx->sample_ray.p, ctx->rgbs.p,
                     ctx->img_out.p, ctx->img_accum.p, ctx->pool_pos.p, ctx->pool_shaded.p, ctx->chunk_ray.p, ctx->chunk_next.p,
                     ctx->ray_head.p, ctx->d_chunk_cursor};
@@ -941,6 +942,8 @@ static srf_status render_frame_impl(srf_ctx* ctx, const srf_view_t* view, const 
 
     const bool blobs = ctx->cfg.field_type == SRF_FIELD_BLOBS;
     const uint8_t* bits = ctx->cfg.use_grid ? ctx->bits : nullptr;
+    const bool sh_per_ray = !blobs && ctx->use_tcgen05 && v.render_mode != SRF_MODE_NORMALS;
+    if (sh_per_ray && (st = ensure(ctx, ctx->ray_sh, v.n_rays * 2 * sizeof(uint4))) != SRF_OK) return st;
     uint32_t n_batches = 0;
     // Waves: the leading waves take every ray a limited number of march steps further, so that rays the compositor
     // finishes early never have the rest of their samples generated or evaluated; the last wave is unlimited.  A
@@ -971,7 +974,7 @@ static srf_status render_frame_impl(srf_ctx* ctx, const srf_view_t* view, const 
                                (uint32_t*)ctx->chunk_next.p, pool_chunks, ctx->d_chunk_cursor, (float4*)ctx->ray_dir_t.p,
                                (uint8_t*)ctx->ray_end.p, (uint32_t*)ctx->counts.p, (uint32_t*)ctx->ray_head.p, ctx->d_counters, s,
                                wave, budgets[wave], waves ? (uint32_t*)ctx->ray_ordinal.p : nullptr,
-                               waves ? (uint32_t*)ctx->ray_total.p : nullptr);
+                               waves ? (uint32_t*)ctx->ray_total.p : nullptr, sh_per_ray ? (uint4*)ctx->ray_sh.p : nullptr);
             if (tm) cudaEventRecord(ctx->ev[3], s);
             if (blobs)
                 launch_field_blobs(ctx->g, v, ctx->blobs, ctx->n_blobs, ctx->cmap, (const float4*)ctx->pool_pos.p, 0,
@@ -983,7 +986,7 @@ static srf_status render_frame_impl(srf_ctx* ctx, const srf_view_t* view, const 
                 launch_field_network_tc(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, (const float4*)ctx->pool_pos.p,
                                         (const uint32_t*)ctx->chunk_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, 0, nullptr,
                                         (float4*)ctx->pool_shaded.p, &ctx->g, &v, &ctx->d_counters->error_flags, s,
-                                        ctx->d_chunk_cursor, kChunkShift);
+                                        ctx->d_chunk_cursor, kChunkShift, sh_per_ray ? (const uint4*)ctx->ray_sh.p : nullptr);
             else
                 launch_field_network(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, (const float4*)ctx->pool_pos.p,
                                      (const uint32_t*)ctx->chunk_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, 0, nullptr,

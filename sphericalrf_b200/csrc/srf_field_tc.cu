@@ -167,7 +167,8 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
                    const uint32_t* __restrict__ sample_ray, const float4* __restrict__ ray_dir_t,
                    const float* __restrict__ coords7, uint64_t n, uint2* __restrict__ rgbsigma,
                    float4* __restrict__ shaded, const DevCfg g, const DevView v,
-                   unsigned int* __restrict__ error_flags, const uint32_t* __restrict__ n_chunks_dev, uint32_t ray_shift) {
+                   unsigned int* __restrict__ error_flags, const uint32_t* __restrict__ n_chunks_dev, uint32_t ray_shift,
+                   const uint4* __restrict__ ray_sh) {
     if (n_chunks_dev) n = (uint64_t)(*n_chunks_dev) * kChunkSamples;        // frame path: the sampler's chunk count
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, warp = tid >> 5;
@@ -244,15 +245,19 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
         const uint64_t s = tile * kGroup + row;
         // ---- encode: one thread per sample, written as 16-byte units of the A image ----
         float x = 0.f, y = 0.f, z = 0.f, dx = 0.5f, dy = 0.5f, dz = 0.5f;
+        uint32_t ray = 0;
         if (s < n) {
             if (coords7) {
                 const float* c = coords7 + s * 7;
                 x = c[0]; y = c[1]; z = c[2]; dx = c[4]; dy = c[5]; dz = c[6];
             } else {
                 const float4 p = pos_dt[s];
-                const float4 d = ray_dir_t[sample_ray[s >> ray_shift]];
                 x = p.x; y = p.y; z = p.z;
-                dx = (d.x + 1.f) * 0.5f; dy = (d.y + 1.f) * 0.5f; dz = (d.z + 1.f) * 0.5f;   // warp_direction
+                ray = sample_ray[s >> ray_shift];
+                if (!ray_sh) {
+                    const float4 d = ray_dir_t[ray];
+                    dx = (d.x + 1.f) * 0.5f; dy = (d.y + 1.f) * 0.5f; dz = (d.z + 1.f) * 0.5f;   // warp_direction
+                }
             }
         }
         {
@@ -264,7 +269,10 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
                     make_uint4(enc[4 * j], enc[4 * j + 1], enc[4 * j + 2], enc[4 * j + 3]);
         }
         uint4 sh0, sh1;                                   // spherical harmonics wait in registers
-        {
+        if (ray_sh && !coords7) {                         // frame path: the sampler encoded the ray's direction once
+            sh0 = __ldg(ray_sh + 2 * (size_t)ray);
+            sh1 = __ldg(ray_sh + 2 * (size_t)ray + 1);
+        } else {
             __align__(16) __half sh[16];
             sh_encode(dx, dy, dz, sh);
             sh0 = *reinterpret_cast<const uint4*>(sh);
@@ -350,7 +358,7 @@ void launch_field_network_tc(const NetMeta& net, const __half* table, const __ha
                              const float4* pos_dt, const uint32_t* sample_ray, const float4* ray_dir_t,
                              const float* coords7, uint64_t n, uint2* rgbsigma, float4* shaded, const DevCfg* g,
                              const DevView* v, unsigned int* error_flags, cudaStream_t stream,
-                             const uint32_t* n_chunks_dev, uint32_t ray_shift) {
+                             const uint32_t* n_chunks_dev, uint32_t ray_shift, const uint4* ray_sh) {
     if (n == 0 && !n_chunks_dev) return;
     // per device and cheap: set on every launch rather than cached per process
     cudaFuncSetAttribute(k_field_network_tc<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmTotal);
@@ -370,9 +378,9 @@ void launch_field_network_tc(const NetMeta& net, const __half* table, const __ha
     if (g) g0 = *g;
     if (v) v0 = *v;
     if (net.n_features == 2)
-        k_field_network_tc<2><<<grid, kTcBlock, kSmTotal, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0, error_flags, n_chunks_dev, ray_shift);
+        k_field_network_tc<2><<<grid, kTcBlock, kSmTotal, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0, error_flags, n_chunks_dev, ray_shift, ray_sh);
     else
-        k_field_network_tc<4><<<grid, kTcBlock, kSmTotal, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0, error_flags, n_chunks_dev, ray_shift);
+        k_field_network_tc<4><<<grid, kTcBlock, kSmTotal, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0, error_flags, n_chunks_dev, ray_shift, ray_sh);
 }
 
 }  // namespace srf

@@ -62,7 +62,8 @@ void launch_march_paged(const DevCfg& g, const DevView& v, const uint8_t* bits, 
                         float4* pool_pos_dt, uint32_t* chunk_ray, uint32_t* chunk_next, uint32_t pool_chunks,
                         uint32_t* chunk_cursor, float4* ray_dir_t, uint8_t* ray_end_out, uint32_t* ray_count,
                         uint32_t* ray_head, FrameCounters* counters, cudaStream_t stream, uint32_t wave = 0,
-                        uint32_t pause_at = 0xffffffffu, uint32_t* ray_ordinal = nullptr, uint32_t* ray_total = nullptr);
+                        uint32_t pause_at = 0xffffffffu, uint32_t* ray_ordinal = nullptr, uint32_t* ray_total = nullptr,
+                        uint4* ray_sh = nullptr);
 //   wave / pause_at: rays are marched up to `pause_at` loop iterations in all; paused rays resume in the next wave from
 //   ray_dir_t.w (t), ray_ordinal (loop iterations) and ray_total (samples so far).
 
@@ -86,7 +87,8 @@ void launch_field_network_tc(const NetMeta& net, const __half* table, const __ha
                              const float4* pos_dt, const uint32_t* sample_ray, const float4* ray_dir_t,
                              const float* coords7, uint64_t n, uint2* rgbsigma, float4* shaded, const DevCfg* g,
                              const DevView* v, unsigned int* error_flags, cudaStream_t stream,
-                             const uint32_t* n_chunks_dev = nullptr, uint32_t ray_shift = 0);
+                             const uint32_t* n_chunks_dev = nullptr, uint32_t ray_shift = 0, const uint4* ray_sh = nullptr);
+//   ray_sh (frame path, optional): the 16 spherical-harmonics halves of every ray's direction, written by the sampler.
 //   n_chunks_dev (frame path): the number of samples is *n_chunks_dev * kChunkSamples, read on the device, and
 //   the ray of sample s is sample_ray[s >> ray_shift] (one entry per chunk).
 //   density only: positions (3 floats, stride given in floats) -> 16 halves per position.

@@ -8,7 +8,7 @@
 // emit pass fills it.
 #include <cooperative_groups.h>
 
-#include "srf_kernels.cuh"
+#include "srf_network.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -109,7 +109,7 @@ k_march_paged(const DevCfg g, const DevView v, const uint8_t* __restrict__ bits,
               uint32_t pool_chunks, uint32_t* __restrict__ chunk_cursor, float4* __restrict__ ray_dir_t,
               uint8_t* __restrict__ ray_end_out, uint32_t* __restrict__ ray_count, uint32_t* __restrict__ ray_head,
               FrameCounters* __restrict__ counters, uint32_t wave, uint32_t pause_at, uint32_t* __restrict__ ray_ordinal,
-              uint32_t* __restrict__ ray_total) {
+              uint32_t* __restrict__ ray_total, uint4* __restrict__ ray_sh) {
     const uint64_t i = ray_begin + (uint64_t)blockIdx.x * kBlock + threadIdx.x;
     unsigned long long alive = 0, steps = 0, samples = 0;
     unsigned int err = 0;
@@ -124,6 +124,12 @@ k_march_paged(const DevCfg g, const DevView v, const uint8_t* __restrict__ bits,
             o = r.o; d = r.d; st.t = r.t;
             run = r.alive;
             alive = r.alive ? 1 : 0;
+            if (ray_sh && r.alive) {                // the direction encoding is the same for every sample of the ray
+                __align__(16) __half sh[16];
+                sh_encode((d.x + 1.f) * 0.5f, (d.y + 1.f) * 0.5f, (d.z + 1.f) * 0.5f, sh);      // warp_direction
+                ray_sh[2 * i] = *reinterpret_cast<const uint4*>(sh);
+                ray_sh[2 * i + 1] = *reinterpret_cast<const uint4*>(sh + 8);
+            }
         } else {
             end = ray_end_out[i];
             if (end == RAY_END_PAUSED) {
@@ -331,11 +337,11 @@ void launch_march_paged(const DevCfg& g, const DevView& v, const uint8_t* bits, 
                         float4* pool_pos_dt, uint32_t* chunk_ray, uint32_t* chunk_next, uint32_t pool_chunks,
                         uint32_t* chunk_cursor, float4* ray_dir_t, uint8_t* ray_end_out, uint32_t* ray_count,
                         uint32_t* ray_head, FrameCounters* counters, cudaStream_t stream, uint32_t wave, uint32_t pause_at,
-                        uint32_t* ray_ordinal, uint32_t* ray_total) {
+                        uint32_t* ray_ordinal, uint32_t* ray_total, uint4* ray_sh) {
     if (ray_end <= ray_begin) return;
     k_march_paged<<<blocks_for(ray_end - ray_begin, kBlock), kBlock, 0, stream>>>(
         g, v, bits, ray_begin, ray_end, pool_pos_dt, chunk_ray, chunk_next, pool_chunks, chunk_cursor, ray_dir_t, ray_end_out,
-        ray_count, ray_head, counters, wave, pause_at, ray_ordinal, ray_total);
+        ray_count, ray_head, counters, wave, pause_at, ray_ordinal, ray_total, ray_sh);
 }
 
 void launch_generate_rays(const DevCfg& g, const DevView& v, const uint8_t* bits, float* dir, float* t,
