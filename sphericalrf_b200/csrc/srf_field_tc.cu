@@ -160,7 +160,9 @@ __device__ __forceinline__ bool group_any(int group, bool v) {
     return r != 0;
 }
 
-template <int F>
+// FRAME: the frame path's argument set (paged pool records in, per-ray SH table, shaded records out), fixed at compile
+// time so that the stage entry points' alternatives cost it neither branches nor registers.
+template <int F, bool FRAME>
 __global__ void __launch_bounds__(kTcBlock, 1)
 k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __half* __restrict__ wd,
                    const __half* __restrict__ wc, const float4* __restrict__ pos_dt,
@@ -247,14 +249,14 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
         float x = 0.f, y = 0.f, z = 0.f, dx = 0.5f, dy = 0.5f, dz = 0.5f;
         uint32_t ray = 0;
         if (s < n) {
-            if (coords7) {
+            if (!FRAME && coords7) {
                 const float* c = coords7 + s * 7;
                 x = c[0]; y = c[1]; z = c[2]; dx = c[4]; dy = c[5]; dz = c[6];
             } else {
                 const float4 p = pos_dt[s];
                 x = p.x; y = p.y; z = p.z;
                 ray = sample_ray[s >> ray_shift];
-                if (!ray_sh) {
+                if (!FRAME && !ray_sh) {
                     const float4 d = ray_dir_t[ray];
                     dx = (d.x + 1.f) * 0.5f; dy = (d.y + 1.f) * 0.5f; dz = (d.z + 1.f) * 0.5f;   // warp_direction
                 }
@@ -268,11 +270,11 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
                 *reinterpret_cast<uint4*>(act + ((size_t)j * 128 + row) * 16) =
                     make_uint4(enc[4 * j], enc[4 * j + 1], enc[4 * j + 2], enc[4 * j + 3]);
         }
-        uint4 sh0, sh1;                                   // spherical harmonics wait in registers
-        if (ray_sh && !coords7) {                         // frame path: the sampler encoded the ray's direction once
-            sh0 = __ldg(ray_sh + 2 * (size_t)ray);
-            sh1 = __ldg(ray_sh + 2 * (size_t)ray + 1);
-        } else {
+        // Spherical harmonics of the direction: read later from the per-ray table the sampler wrote (frame path), or
+        // computed here and kept in registers (stage entry points).
+        const bool sh_from_ray = FRAME || (ray_sh && !coords7);
+        uint4 sh0 = make_uint4(0u, 0u, 0u, 0u), sh1 = sh0;
+        if (!sh_from_ray) {
             __align__(16) __half sh[16];
             sh_encode(dx, dy, dz, sh);
             sh0 = *reinterpret_cast<const uint4*>(sh);
@@ -300,6 +302,10 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
             tmem_ld_wait();
             store_units<false>(acc, act, 0, row);         // colour input rows 0..15 = density output
             sigma_half = pack2(__uint_as_float(acc[0]), 0.f) & 0xffffu;
+        }
+        if (sh_from_ray) {
+            sh0 = __ldg(ray_sh + 2 * (size_t)ray);
+            sh1 = __ldg(ray_sh + 2 * (size_t)ray + 1);
         }
         *reinterpret_cast<uint4*>(act + ((size_t)2 * 128 + row) * 16) = sh0;   // rows 16..31 = SH
         *reinterpret_cast<uint4*>(act + ((size_t)3 * 128 + row) * 16) = sh1;
@@ -333,7 +339,7 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
             if (s < n) {
                 const uint32_t rg = pack2(__uint_as_float(acc[0]), __uint_as_float(acc[1]));
                 const uint32_t bs = (pack2(__uint_as_float(acc[2]), 0.f) & 0xffffu) | (sigma_half << 16);
-                if (shaded) {
+                if (FRAME || shaded) {
                     // frame path: activations evaluated here, on the fp16-rounded network outputs
                     const __half2 h0 = *reinterpret_cast<const __half2*>(&rg), h1 = *reinterpret_cast<const __half2*>(&bs);
                     const float raw[4] = {__low2float(h0), __high2float(h0), __low2float(h1), __high2float(h1)};
@@ -361,12 +367,14 @@ void launch_field_network_tc(const NetMeta& net, const __half* table, const __ha
                              const uint32_t* n_chunks_dev, uint32_t ray_shift, const uint4* ray_sh) {
     if (n == 0 && !n_chunks_dev) return;
     // per device and cheap: set on every launch rather than cached per process
-    cudaFuncSetAttribute(k_field_network_tc<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmTotal);
-    cudaFuncSetAttribute(k_field_network_tc<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmTotal);
     // no more shared memory than the CTA needs: the rest of the unified array serves the gathers as L1
     constexpr int kCarveout = (kSmTotal * 100 + 228 * 1024 - 1) / (228 * 1024);
-    cudaFuncSetAttribute(k_field_network_tc<2>, cudaFuncAttributePreferredSharedMemoryCarveout, kCarveout);
-    cudaFuncSetAttribute(k_field_network_tc<4>, cudaFuncAttributePreferredSharedMemoryCarveout, kCarveout);
+    const void* kernels[4] = {(const void*)k_field_network_tc<2, true>, (const void*)k_field_network_tc<2, false>,
+                              (const void*)k_field_network_tc<4, true>, (const void*)k_field_network_tc<4, false>};
+    for (const void* k : kernels) {
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmTotal);
+        cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, kCarveout);
+    }
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -377,10 +385,13 @@ void launch_field_network_tc(const NetMeta& net, const __half* table, const __ha
     memset(&g0, 0, sizeof(g0)); memset(&v0, 0, sizeof(v0));
     if (g) g0 = *g;
     if (v) v0 = *v;
-    if (net.n_features == 2)
-        k_field_network_tc<2><<<grid, kTcBlock, kSmTotal, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0, error_flags, n_chunks_dev, ray_shift, ray_sh);
-    else
-        k_field_network_tc<4><<<grid, kTcBlock, kSmTotal, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0, error_flags, n_chunks_dev, ray_shift, ray_sh);
+    const bool frame = shaded && ray_sh && pos_dt && sample_ray && !coords7;
+#define SRF_TC_LAUNCH(FEAT, FRAME)                                                                                          \
+    k_field_network_tc<FEAT, FRAME><<<grid, kTcBlock, kSmTotal, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, \
+        ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0, error_flags, n_chunks_dev, ray_shift, ray_sh)
+    if (net.n_features == 2) { if (frame) SRF_TC_LAUNCH(2, true); else SRF_TC_LAUNCH(2, false); }
+    else { if (frame) SRF_TC_LAUNCH(4, true); else SRF_TC_LAUNCH(4, false); }
+#undef SRF_TC_LAUNCH
 }
 
 }  // namespace srf
