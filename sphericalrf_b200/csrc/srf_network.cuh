@@ -130,7 +130,7 @@ __device__ __forceinline__ void hash_encode_range(const EncMeta* m, const __half
         }
         level_finish<F>(c, raw, l, out);
     }
-#pragma unroll 2
+#pragma unroll 3
     for (int l = l_begin > n_dense ? l_begin : n_dense; l < l_end; ++l) {
         const float scale = m->level[l].scale;
         const uint32_t mask = m->level[l].mask;
