@@ -2,7 +2,8 @@
 //
 // Same data flow as srf_field.cu (NGPNetwork::inference_mixed_precision,
 // internal/network/ngp_network.h:212-279), different engine for the five dense layers.  A CTA of
-// 1024 threads -- one per SM -- is eight independent groups of 128 threads; a group owns a tile of 128 samples: thread
+// 1024 threads -- one per SM -- is eight independent groups of 128 threads; a group owns a tile of 128
+// samples: thread
 // r gathers and interpolates the hash-grid features of sample r straight into the shared-memory
 // image of the MMA's A operand; the group's first thread issues tcgen05.mma (M = 128 samples,
 // N = 64 or 16 neurons, K = 16 per instruction) with the fp32 accumulator in tensor memory; after
@@ -18,7 +19,9 @@
 //
 // One 16 KB activation region per group is enough: each layer's output overwrites the region its
 // input was read from, which is safe once the layer's commit barrier has completed (the tensor core
-// has finished reading shared memory by then).  The spherical harmonics wait in registers.
+// has finished reading shared memory by then).  The spherical harmonics of the direction are the same for
+// every sample of a ray: on the frame path the sampler writes them once per ray and this kernel reads the 32
+// bytes when the colour network's input is assembled (stage entry points compute them per sample).
 //
 // Tensor memory: 64 columns per group (all 64 for the 64-wide layers, the first 16 for the 16-wide
 // ones): the CTA allocates all 512 columns of its SM.  Its 1024 threads at 64 registers take the whole
