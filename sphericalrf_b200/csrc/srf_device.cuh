@@ -371,6 +371,37 @@ __device__ __forceinline__ void pcg_advance(Pcg& r, uint64_t delta) {
     r.state = acc_mult * r.state + acc_plus;
 }
 
+// pcg_advance for 32-bit distances without the 32-iteration square-and-multiply loop: the jump by
+// delta = sum_k b_k * 256^k is the composition of four table jumps.  A jump by d maps state to
+// m^d * state + inc * (1 + m + ... + m^(d-1)); the table holds both factors for every d = b * 256^k
+// (they depend only on the generator's multiplier), 16 KB of constants computed at compile time.
+struct PcgJumpTable { uint64_t mult[4][256]; uint64_t geo[4][256]; };
+constexpr PcgJumpTable make_pcg_jump_table() {
+    PcgJumpTable t{};
+    for (int k = 0; k < 4; ++k)
+        for (int b = 0; b < 256; ++b) {
+            uint64_t delta = (uint64_t)b << (8 * k);
+            uint64_t cur_mult = kPcgMult, cur_plus = 1u, acc_mult = 1u, acc_plus = 0u;
+            while (delta > 0) {
+                if (delta & 1) { acc_mult *= cur_mult; acc_plus = acc_plus * cur_mult + cur_plus; }
+                cur_plus = (cur_mult + 1) * cur_plus;
+                cur_mult *= cur_mult;
+                delta >>= 1;
+            }
+            t.mult[k][b] = acc_mult;
+            t.geo[k][b] = acc_plus;
+        }
+    return t;
+}
+static __device__ const PcgJumpTable kPcgJump = make_pcg_jump_table();
+__device__ __forceinline__ void pcg_jump(Pcg& r, uint32_t delta) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t b = (delta >> (8 * k)) & 255u;
+        if (b) r.state = kPcgJump.mult[k][b] * r.state + kPcgJump.geo[k][b] * r.inc;
+    }
+}
+
 // ---- one ray ---------------------------------------------------------------------------------------
 enum RayEnd : uint32_t {
     RAY_END_EXIT = 0,       // left the box

@@ -50,7 +50,8 @@ k_refresh_sample(const DevCfg g, const NetMeta net, const __grid_constant__ Refr
     }
 
     Pcg rng = rng0;
-    pcg_advance(rng, (uint64_t)i * 4u);
+    if (i < (1u << 30)) pcg_jump(rng, i * 4u);             // rng.advance(i*4), :125
+    else pcg_advance(rng, (uint64_t)i * 4u);
     const uint32_t nc = g.n_cascades, N = g.grid_size;
     const uint32_t level = (uint32_t)(pcg_next_float(rng) * (float)nc) % nc;
     uint32_t idx = 0;

@@ -80,7 +80,7 @@ __device__ __forceinline__ TrainRay train_ray_setup(const DevCfg& g, const Train
     TrainRay r;
     r.valid = false;
     const uint32_t img = (((n_rays_shift + i) * tv.n_images) / n_rays) % tv.n_images;      // u32 arithmetic (:544)
-    pcg_advance(rng, (uint64_t)(uint32_t)(i * 8u));
+    pcg_jump(rng, i * 8u);                                  // rng.advance(i * 8) with the reference's u32 product (:551)
     float xx = pcg_next_float(rng);
     float yy = pcg_next_float(rng);
     const float rw = (float)tv.width, rh = (float)tv.height;
