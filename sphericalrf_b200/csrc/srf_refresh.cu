@@ -85,11 +85,14 @@ k_refresh_sample(const DevCfg g, const NetMeta net, const __grid_constant__ Refr
     } break;
     }
 
-    __half enc[32];
-    hash_encode<F>(&enc_meta, table, pos.x, pos.y, pos.z, enc);
+    uint32_t enc[16];
+    hash_encode_packed<F>(&enc_meta, table, pos.x, pos.y, pos.z, enc);
     float x[32];
 #pragma unroll
-    for (int k = 0; k < 32; ++k) x[k] = __half2float(enc[k]);
+    for (int k = 0; k < 16; ++k) {
+        const __half2 h = *reinterpret_cast<const __half2*>(&enc[k]);
+        x[2 * k] = __low2float(h); x[2 * k + 1] = __high2float(h);
+    }
     float out0 = 0.f;
 #pragma unroll
     for (int o = 0; o < 64; ++o) {
