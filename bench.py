@@ -299,7 +299,7 @@ def run_ours(args):
     achieved = ALG_BYTES_PER_SAMPLE * n_samples / max(n_batches, 1) / (t_field / max(n_batches, 1) * 1e-3) / 1e9 if t_field > 0 else 0.0
     roof_kernel = "k_field_network_tc (hash-grid gather + tcgen05 MLPs + shading)"
     roof_ms = t_field / max(n_batches, 1)
-    roof_traffic = 33.7 * n_samples / max(n_batches, 1)
+    roof_traffic = 33.1 * n_samples / max(n_batches, 1)
     if cfg.field_type != abi.FIELD_NETWORK:
         # sampler + compositing configurations: the sampler is the kernel of interest (28 B/sample + 80 B/ray)
         roof_kernel = "k_march_paged (single-pass sampler)"
@@ -322,7 +322,7 @@ def run_ours(args):
         "gpu_launches": int(launches_per_frame * n_views * args.steps),
         "roofline": {"kernel": roof_kernel, "bound": "hbm", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak,
-                     # DRAM bytes of one launch: 33.7 B/sample from the ncu capture of a 108 M-sample launch
+                     # DRAM bytes of one launch: 33.1 B/sample from the ncu capture of a 108 M-sample launch
                      # (profiles/field_network_tcgen05_config1_320x208.md), scaled by this launch's samples
                      "traffic": roof_traffic, "peak_kind": peak_kind,
                      "ms_per_launch": roof_ms, "launches_per_frame": int(n_batches),
