@@ -360,6 +360,14 @@ srf_status srf_dump_samples(srf_ctx* ctx, const srf_view_t* view, uint64_t ray_f
                             float* h_pos_dt, uint32_t* h_ordinal, uint32_t* h_cell,
                             uint64_t* n_total);
 
+/* Device-side error word of the context (the reference has none: its kernels cannot time out).  Bits: 1 = a
+   ray hit the march loop's iteration bound, 2 = a wait on the tensor-core commit barrier expired, 4 = the
+   sample pool ran out of chunks.  Frames enqueued without `stats` do not synchronise and therefore cannot
+   report; the word stays set across frames until one of srf_render, srf_dump_samples, a frame with `stats`
+   or this call has returned it as SRF_ERR_TIMEOUT / SRF_ERR_CAPACITY, which also clears it.  Synchronises
+   `stream`.  `flags` (may be NULL) receives the raw word. */
+srf_status srf_check_errors(srf_ctx* ctx, void* stream, uint32_t* flags);
+
 /* Upper bound of live samples the context keeps scratch for; a frame with more samples is
    rendered in several batches.  0 = grow on demand (the default). */
 srf_status srf_reserve(srf_ctx* ctx, uint64_t max_samples);

@@ -193,6 +193,7 @@ SYMBOLS = {
     "srf_render": (C.c_int, [_ctx, _P(View), _P(Post), C.c_uint32, _vp, _P(FrameStats)]),
     "srf_dump_samples": (C.c_int, [_ctx, _P(View), C.c_uint64, C.c_uint64, C.c_uint64, _vp, _vp, _vp, _vp,
                                    _P(C.c_uint64)]),
+    "srf_check_errors": (C.c_int, [_ctx, _vp, _P(C.c_uint32)]),
     "srf_reserve": (C.c_int, [_ctx, C.c_uint64]),
     "srf_set_wave_schedule": (C.c_int, [_ctx, _vp, C.c_uint32]),
     "srf_sampler_init": (C.c_int, [_ctx, _P(TrainViews), C.c_int, C.c_uint64, _vp]),

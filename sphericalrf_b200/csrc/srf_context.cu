@@ -11,6 +11,7 @@
 // the stage entry points and the parity tap, which need the compact ray-major layout.
 #include <algorithm>
 #include <cmath>
+#include <cstddef>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -333,6 +334,34 @@ srf_status ensure_sample_buffers(srf_ctx* ctx, uint64_t n_samples) {
     return SRF_OK;
 }
 
+// Zeroes the per-frame counters.  The error word behind them is NOT cleared here: it stays set until a
+// call that synchronises anyway (srf_render, srf_dump_samples, a frame with stats, srf_check_errors) has
+// reported it, so a truncated frame whose caller asked for no statistics cannot pass for a good one.
+cudaError_t reset_frame_counters(srf_ctx* ctx, cudaStream_t s) {
+    return cudaMemsetAsync(ctx->d_counters, 0, offsetof(FrameCounters, error_flags), s);
+}
+
+// Turns the device error word into a status and clears it (the caller has synchronised `s` after copying
+// the word to ctx->h_counters->error_flags).
+srf_status report_error_flags(srf_ctx* ctx, uint32_t flags, cudaStream_t s) {
+    if (!flags) return SRF_OK;
+    cudaMemsetAsync(&ctx->d_counters->error_flags, 0, sizeof(unsigned int), s);
+    if (flags & 1u) return fail(ctx, SRF_ERR_TIMEOUT, "a ray hit the march loop's iteration bound");
+    if (flags & 2u) return fail(ctx, SRF_ERR_TIMEOUT, "a wait on the tensor-core commit barrier expired");
+    if (flags & 4u) return fail(ctx, SRF_ERR_CAPACITY, "the sample pool ran out of chunks");
+    return fail(ctx, SRF_ERR_CUDA, "unknown device error flag");
+}
+
+// Reads the error word back (synchronises `s`) and reports it.
+srf_status check_error_flags(srf_ctx* ctx, cudaStream_t s, uint32_t* flags_out) {
+    SRF_CK(ctx, cudaMemcpyAsync(&ctx->h_counters->error_flags, &ctx->d_counters->error_flags, sizeof(unsigned int),
+                                cudaMemcpyDeviceToHost, s));
+    SRF_CK(ctx, cudaStreamSynchronize(s));
+    const uint32_t flags = ctx->h_counters->error_flags;
+    if (flags_out) *flags_out = flags;
+    return report_error_flags(ctx, flags, s);
+}
+
 srf_status check_ready(srf_ctx* ctx) {
     if (ctx->cfg.field_type == SRF_FIELD_NETWORK && !ctx->have_net)
         return fail(ctx, SRF_ERR_STATE, "network parameters were not uploaded (srf_upload_network)");
@@ -345,7 +374,7 @@ srf_status check_ready(srf_ctx* ctx) {
 srf_status count_and_scan(srf_ctx* ctx, const DevView& v, cudaStream_t s) {
     srf_status st = ensure_ray_buffers(ctx, v.n_rays);
     if (st != SRF_OK) return st;
-    SRF_CK(ctx, cudaMemsetAsync(ctx->d_counters, 0, sizeof(FrameCounters), s));
+    SRF_CK(ctx, reset_frame_counters(ctx, s));
     launch_ray_count(ctx->g, v, ctx->cfg.use_grid ? ctx->bits : nullptr, (float4*)ctx->ray_dir_t.p, (uint8_t*)ctx->ray_end.p,
                      (uint32_t*)ctx->counts.p, ctx->d_counters, s);
     launch_scan((const uint32_t*)ctx->counts.p, v.n_rays, (uint64_t*)ctx->offsets.p, ctx->scan_scratch.p, s);
@@ -467,6 +496,7 @@ srf_status srf_create(const srf_config_t* cfg, int device, srf_ctx** out) {
         CK_CREATE(cudaMalloc((void**)&ctx->w_rgb, (64 * 32 + 64 * 64 + 16 * 64) * sizeof(__half)));
     }
     CK_CREATE(cudaMalloc((void**)&ctx->d_counters, sizeof(FrameCounters)));
+    CK_CREATE(cudaMemset(ctx->d_counters, 0, sizeof(FrameCounters)));
     CK_CREATE(cudaMalloc((void**)&ctx->d_chunk_cursor, sizeof(uint32_t)));
     CK_CREATE(cudaMallocHost((void**)&ctx->h_counters, sizeof(FrameCounters)));
     for (int i = 0; i < 8; ++i) CK_CREATE(cudaEventCreate(&ctx->ev[i]));
@@ -808,7 +838,7 @@ srf_status srf_sample_count(srf_ctx* ctx, const srf_view_t* view, uint32_t* d_co
     DeviceGuard guard(ctx->device);
     cudaStream_t s = (cudaStream_t)stream;
     if ((st = ensure_ray_buffers(ctx, v.n_rays)) != SRF_OK) return st;
-    SRF_CK(ctx, cudaMemsetAsync(ctx->d_counters, 0, sizeof(FrameCounters), s));
+    SRF_CK(ctx, reset_frame_counters(ctx, s));
     launch_ray_count(ctx->g, v, ctx->cfg.use_grid ? ctx->bits : nullptr, (float4*)ctx->ray_dir_t.p, (uint8_t*)ctx->ray_end.p,
                      d_counts, ctx->d_counters, s);
     SRF_CK(ctx, cudaGetLastError());
@@ -938,7 +968,7 @@ static srf_status render_frame_impl(srf_ctx* ctx, const srf_view_t* view, const 
     if ((st = ensure(ctx, ctx->pool_shaded, pool_slots * sizeof(float4))) != SRF_OK) return st;
     if ((st = ensure(ctx, ctx->chunk_ray, (size_t)pool_chunks * sizeof(uint32_t))) != SRF_OK) return st;
     if ((st = ensure(ctx, ctx->chunk_next, (size_t)pool_chunks * sizeof(uint32_t))) != SRF_OK) return st;
-    SRF_CK(ctx, cudaMemsetAsync(ctx->d_counters, 0, sizeof(FrameCounters), s));
+    SRF_CK(ctx, reset_frame_counters(ctx, s));
 
     const bool blobs = ctx->cfg.field_type == SRF_FIELD_BLOBS;
     const uint8_t* bits = ctx->cfg.use_grid ? ctx->bits : nullptr;
@@ -1018,9 +1048,7 @@ static srf_status render_frame_impl(srf_ctx* ctx, const srf_view_t* view, const 
         stats->n_waves = n_waves;
         stats->error_flags = ctx->h_counters->error_flags;
         stats->ms_sampler = ms_sampler; stats->ms_field = ms_field; stats->ms_composite = ms_comp; stats->ms_post = 0.f;
-        if (stats->error_flags & 1u) return fail(ctx, SRF_ERR_TIMEOUT, "a ray hit the march loop's iteration bound");
-        if (stats->error_flags & 2u) return fail(ctx, SRF_ERR_TIMEOUT, "a wait on the tensor-core commit barrier expired");
-        if (stats->error_flags & 4u) return fail(ctx, SRF_ERR_CAPACITY, "the sample pool ran out of chunks");
+        if ((st = report_error_flags(ctx, stats->error_flags, s)) != SRF_OK) return st;
     }
     return SRF_OK;
 }
@@ -1065,6 +1093,7 @@ srf_status srf_render(srf_ctx* ctx, const srf_view_t* view, const srf_post_t* po
         if (st != SRF_OK) return st;
     }
     SRF_CK(ctx, cudaMemcpy(h_image, ctx->img_out.p, n * sizeof(float4), cudaMemcpyDeviceToHost));   // :30-38
+    if (!stats && (st = check_error_flags(ctx, nullptr, nullptr)) != SRF_OK) return st;   // with stats the last pass reported
     return SRF_OK;
 }
 
@@ -1100,7 +1129,13 @@ srf_status srf_dump_samples(srf_ctx* ctx, const srf_view_t* view, uint64_t ray_f
     cudaFree(ord.p);
     cudaFree(cell.p);
     if (e != cudaSuccess) { ctx->err = std::string("srf_dump_samples: ") + cudaGetErrorString(e); return SRF_ERR_CUDA; }
-    return SRF_OK;
+    return check_error_flags(ctx, s, nullptr);
+}
+
+srf_status srf_check_errors(srf_ctx* ctx, void* stream, uint32_t* flags) {
+    if (!ctx) return SRF_ERR_ARG;
+    DeviceGuard guard(ctx->device);
+    return check_error_flags(ctx, (cudaStream_t)stream, flags);
 }
 
 srf_status srf_reserve(srf_ctx* ctx, uint64_t max_samples) {

@@ -108,7 +108,10 @@ __device__ __forceinline__ void hash_encode_range(const EncMeta* m, const __half
         const uint32_t y0 = c.iy * L.res, z0 = c.iz * L.r2;
         const uint32_t xy[4] = {c.ix + y0, c.ix + 1u + y0, c.ix + y0 + L.res, c.ix + 1u + y0 + L.res};
         uint32_t raw[8][F / 2];
-        if (xy[3] + z0 + L.r2 < L.size) {        // the largest of the eight indices: no corner wraps (almost always)
+        // Fast path when the largest of the eight indices is inside the level (almost always).  The test must hold in
+        // exact arithmetic, not modulo 2^32: a position far outside [0,1] gives cell coordinates near 2^32 whose sum
+        // wraps back below the level size; cell coordinates below 4096 cannot wrap (dense levels have res <= 256).
+        if ((c.ix | c.iy | c.iz) < 4096u && xy[3] + z0 + L.r2 < L.size) {
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
                 const uint32_t* e = base + (size_t)(xy[k & 3] + ((k & 4) ? z0 + L.r2 : z0)) * (F / 2);

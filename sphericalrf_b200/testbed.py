@@ -101,6 +101,10 @@ class Renderer:
     def reserve(self, max_samples):
         self._ck(self.lib.srf_reserve(self.ctx, max_samples))
 
+    def check_errors(self, stream=None):
+        """srf_check_errors: raises if a frame enqueued since the last check was cut short on the device."""
+        self._ck(self.lib.srf_check_errors(self.ctx, stream, None))
+
     def set_timing(self, on=True):
         self._ck(self.lib.srf_set_timing(self.ctx, 1 if on else 0))
 
