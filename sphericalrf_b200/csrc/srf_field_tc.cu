@@ -35,6 +35,7 @@
 //
 // Every wait on a commit barrier is bounded; on expiry the group raises an error flag and leaves its
 // tile loop; the CTA frees its tensor memory and returns.
+#include <cstdlib>
 #include <cstring>
 #include "srf_network.cuh"
 
@@ -58,10 +59,12 @@ constexpr int kSmAct = kSmW_C3 + 8 * 16 * 16;     // kGroups x [8][128][8]: the 
 constexpr int kActBytes = 8 * 128 * 16;
 constexpr int kSmBar = kSmAct + kGroups * kActBytes;   // kGroups mbarriers + tensor-memory base (4 B)
 constexpr int kSmEnc = kSmBar + kGroups * 8 + 16;  // per-level constants of the encoding
-constexpr int kSmTotal = kSmEnc + (int)sizeof(EncMeta);
+constexpr int kSmStage = (kSmEnc + (int)sizeof(EncMeta) + 15) / 16 * 16;   // coarse levels of the hash table (optional, dynamic size)
+constexpr int kSmTotal = kSmStage;                // without staged levels
+constexpr int kSmLimit = 227 * 1024;
 static_assert(kTmemCols == 512, "the CTA owns the SM's tensor memory");
 static_assert(kSmTotal > 227 * 1024 / 2, "a second CTA must not fit: it would wait for tensor memory forever");
-static_assert(kSmTotal <= 227 * 1024, "shared memory of one SM");
+static_assert(kSmTotal <= kSmLimit, "shared memory of one SM");
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -173,7 +176,7 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
                    const float* __restrict__ coords7, uint64_t n, uint2* __restrict__ rgbsigma,
                    float4* __restrict__ shaded, const DevCfg g, const DevView v,
                    unsigned int* __restrict__ error_flags, const uint32_t* __restrict__ n_chunks_dev, uint32_t ray_shift,
-                   const uint4* __restrict__ ray_sh) {
+                   const uint4* __restrict__ ray_sh, int n_staged) {
     if (n_chunks_dev) n = (uint64_t)(*n_chunks_dev) * kChunkSamples;        // frame path: the sampler's chunk count
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, warp = tid >> 5;
@@ -201,6 +204,21 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    if (n_staged > 0) {
+        // Coarse dense levels are read by every sample and are small: copy them into shared memory once per CTA and
+        // point the level table there.
+        uint32_t* stage = reinterpret_cast<uint32_t*>(smem + kSmStage);
+        uint32_t off = 0;
+        for (int l = 0; l < n_staged; ++l) {
+            const uint32_t words = net.level[l].size * (F / 2);
+            const uint32_t* src = reinterpret_cast<const uint32_t*>(table) + (size_t)net.level[l].offset * (F / 2);
+            for (uint32_t i = tid; i < words; i += kTcBlock) stage[off + i] = __ldg(src + i);
+            if (tid == 0) enc_meta->level[l].base = stage + off;
+            off += words;
+        }
+        if (tid == 0) enc_meta->n_staged = n_staged;
+        __syncthreads();
+    }
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_group = tmem_base + (uint32_t)group * 64u;                      // this group's columns
     const uint32_t tmem_row = tmem_group + ((uint32_t)((warp & 3) * 32) << 16);          // this warp's quarter of the lanes
@@ -246,7 +264,8 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
         return !group_any(group, expired);
     };
     const uint64_t n_tiles = (n + kGroup - 1) / kGroup;
-    for (uint64_t tile = (uint64_t)blockIdx.x * kGroups + group; tile < n_tiles; tile += (uint64_t)gridDim.x * kGroups) {
+    const uint64_t tile_stride = (uint64_t)gridDim.x * kGroups;
+    for (uint64_t tile = (uint64_t)blockIdx.x * kGroups + group; tile < n_tiles; tile += tile_stride) {
         const uint64_t s = tile * kGroup + row;
         // ---- encode: one thread per sample, written as 16-byte units of the A image ----
         float x = 0.f, y = 0.f, z = 0.f, dx = 0.5f, dy = 0.5f, dz = 0.5f;
@@ -288,6 +307,13 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
 
         // ---- density layer 1: 32 -> 64, ReLU ----
         issue_layer(wD1, 64, 2, kIdesc64);
+        if (FRAME) {                                  // hint only: bring the next tile's records into L2
+            const uint64_t sn = s + tile_stride * kGroup;
+            if (sn < n) {
+                asm volatile("prefetch.global.L2 [%0];" :: "l"(pos_dt + sn));
+                if ((row & 15) == 0) asm volatile("prefetch.global.L2 [%0];" :: "l"(sample_ray + (sn >> ray_shift)));
+            }
+        }
         if (!wait_layer()) { failed = true; break; }
         tc_fence_after();
         hidden_epilogue();
@@ -346,8 +372,10 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
                     // frame path: activations evaluated here, on the fp16-rounded network outputs
                     const __half2 h0 = *reinterpret_cast<const __half2*>(&rg), h1 = *reinterpret_cast<const __half2*>(&bs);
                     const float raw[4] = {__low2float(h0), __high2float(h0), __low2float(h1), __high2float(h1)};
-                    const float4 p = pos_dt[s];                      // re-read (L2) instead of holding four registers
-                    shaded[s] = shade_sample(g, v, raw, p.w, mk3(p.x, p.y, p.z));
+                    {
+                        const float4 p = pos_dt[s];                  // re-read (L2) instead of holding four registers
+                        shaded[s] = shade_sample(g, v, raw, p.w, mk3(p.x, p.y, p.z));
+                    }
                 } else {
                     rgbsigma[s] = make_uint2(rg, bs);
                 }
@@ -369,14 +397,25 @@ void launch_field_network_tc(const NetMeta& net, const __half* table, const __ha
                              const DevView* v, unsigned int* error_flags, cudaStream_t stream,
                              const uint32_t* n_chunks_dev, uint32_t ray_shift, const uint4* ray_sh) {
     if (n == 0 && !n_chunks_dev) return;
+    // Staged levels: as many leading dense levels as fit into `stage_budget` bytes of shared memory (default: none).
+    // Shared memory taken here is L1 taken from the gathers of the other levels.
+    static const long stage_budget = [] { const char* e = getenv("SRF_B200_STAGE_BYTES"); return e ? atol(e) : 0l; }();
+    int n_staged = 0;
+    size_t stage_bytes = 0;
+    for (uint32_t l = 0; l < net.n_levels && net.level[l].dense; ++l) {
+        const size_t b = (size_t)net.level[l].size * net.n_features * sizeof(__half);
+        if ((long)(stage_bytes + b) > stage_budget || kSmTotal + stage_bytes + b > (size_t)kSmLimit) break;
+        stage_bytes += b; ++n_staged;
+    }
+    const int smem_bytes = kSmTotal + (int)stage_bytes;
     // per device and cheap: set on every launch rather than cached per process
     // no more shared memory than the CTA needs: the rest of the unified array serves the gathers as L1
-    constexpr int kCarveout = (kSmTotal * 100 + 228 * 1024 - 1) / (228 * 1024);
+    const int carveout = (smem_bytes * 100 + 228 * 1024 - 1) / (228 * 1024);
     const void* kernels[4] = {(const void*)k_field_network_tc<2, true>, (const void*)k_field_network_tc<2, false>,
                               (const void*)k_field_network_tc<4, true>, (const void*)k_field_network_tc<4, false>};
     for (const void* k : kernels) {
-        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmTotal);
-        cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, kCarveout);
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+        cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, carveout);
     }
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
@@ -390,8 +429,8 @@ void launch_field_network_tc(const NetMeta& net, const __half* table, const __ha
     if (v) v0 = *v;
     const bool frame = shaded && ray_sh && pos_dt && sample_ray && !coords7;
 #define SRF_TC_LAUNCH(FEAT, FRAME)                                                                                          \
-    k_field_network_tc<FEAT, FRAME><<<grid, kTcBlock, kSmTotal, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, \
-        ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0, error_flags, n_chunks_dev, ray_shift, ray_sh)
+    k_field_network_tc<FEAT, FRAME><<<grid, kTcBlock, smem_bytes, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, \
+        ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0, error_flags, n_chunks_dev, ray_shift, ray_sh, n_staged)
     if (net.n_features == 2) { if (frame) SRF_TC_LAUNCH(2, true); else SRF_TC_LAUNCH(2, false); }
     else { if (frame) SRF_TC_LAUNCH(4, true); else SRF_TC_LAUNCH(4, false); }
 #undef SRF_TC_LAUNCH

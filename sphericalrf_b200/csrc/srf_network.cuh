@@ -28,6 +28,7 @@ struct EncLevel {
 struct EncMeta {
     EncLevel level[kMaxLevels];
     int n_levels, n_dense;               // levels [0, n_dense) are dense, the rest hashed
+    int n_staged;                        // levels [0, n_staged) were copied to shared memory (their base points there)
 };
 
 // Filled once per CTA (all threads call it, followed by a barrier the caller provides).
@@ -45,6 +46,7 @@ __device__ __forceinline__ void prepare_enc_meta(const NetMeta& net, const __hal
         while (d < (int)net.n_levels && net.level[d].dense) ++d;
         m->n_levels = (int)net.n_levels;
         m->n_dense = d;
+        m->n_staged = 0;
     }
 }
 
@@ -91,6 +93,42 @@ __device__ __forceinline__ void level_finish(const LevelCell& c, const uint32_t 
     }
 }
 
+// One dense level.  STAGED: the level's entries were copied to shared memory and `base` points there (plain loads);
+// otherwise they are read from global memory through the read-only path.
+template <int F, bool STAGED>
+__device__ __forceinline__ void dense_level(const EncMeta* m, int l, float x, float y, float z, uint32_t (&out)[16]) {
+    const EncLevel L = m->level[l];
+    const uint32_t* base = L.base;
+    const LevelCell c = level_cell(L.scale, x, y, z);
+    const uint32_t y0 = c.iy * L.res, z0 = c.iz * L.r2;
+    const uint32_t xy[4] = {c.ix + y0, c.ix + 1u + y0, c.ix + y0 + L.res, c.ix + 1u + y0 + L.res};
+    uint32_t raw[8][F / 2];
+    // Fast path when the largest of the eight indices is inside the level (almost always).  The test must hold in
+    // exact arithmetic, not modulo 2^32: a position far outside [0,1] gives cell coordinates near 2^32 whose sum
+    // wraps back below the level size; cell coordinates below 4096 cannot wrap (dense levels have res <= 256).
+    if ((c.ix | c.iy | c.iz) < 4096u && xy[3] + z0 + L.r2 < L.size) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t* e = base + (size_t)(xy[k & 3] + ((k & 4) ? z0 + L.r2 : z0)) * (F / 2);
+#pragma unroll
+            for (int f = 0; f < F / 2; ++f) raw[k][f] = STAGED ? e[f] : __ldg(e + f);
+        }
+    } else {                                 // cells touching the upper faces of a dense level
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            uint32_t i = xy[k & 3] + ((k & 4) ? z0 + L.r2 : z0);
+            if (i >= L.size) {
+                i -= L.size;
+                if (i >= L.size) i %= L.size;
+            }
+            const uint32_t* e = base + (size_t)i * (F / 2);
+#pragma unroll
+            for (int f = 0; f < F / 2; ++f) raw[k][f] = STAGED ? e[f] : __ldg(e + f);
+        }
+    }
+    level_finish<F>(c, raw, l, out);
+}
+
 // Encodes levels [l_begin, l_end) of one position into the packed pairs out[l*F/2 ...] (pair i = features
 // 2i, 2i+1 of the 32-half encoding).  `m` lives in shared memory (prepare_enc_meta).  Callers that want to
 // interleave the encoding with other work call it on successive level ranges.
@@ -100,39 +138,11 @@ __device__ __forceinline__ void hash_encode_range(const EncMeta* m, const __half
     (void)table;                                  // the level bases in `m` were derived from it
     const int n_dense = m->n_dense;
     const int dense_end = l_end < n_dense ? l_end : n_dense;
+    const int staged_end = dense_end < m->n_staged ? dense_end : m->n_staged;
 #pragma unroll 1
-    for (int l = l_begin; l < dense_end; ++l) {
-        const EncLevel L = m->level[l];
-        const uint32_t* base = L.base;
-        const LevelCell c = level_cell(L.scale, x, y, z);
-        const uint32_t y0 = c.iy * L.res, z0 = c.iz * L.r2;
-        const uint32_t xy[4] = {c.ix + y0, c.ix + 1u + y0, c.ix + y0 + L.res, c.ix + 1u + y0 + L.res};
-        uint32_t raw[8][F / 2];
-        // Fast path when the largest of the eight indices is inside the level (almost always).  The test must hold in
-        // exact arithmetic, not modulo 2^32: a position far outside [0,1] gives cell coordinates near 2^32 whose sum
-        // wraps back below the level size; cell coordinates below 4096 cannot wrap (dense levels have res <= 256).
-        if ((c.ix | c.iy | c.iz) < 4096u && xy[3] + z0 + L.r2 < L.size) {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const uint32_t* e = base + (size_t)(xy[k & 3] + ((k & 4) ? z0 + L.r2 : z0)) * (F / 2);
-#pragma unroll
-                for (int f = 0; f < F / 2; ++f) raw[k][f] = __ldg(e + f);
-            }
-        } else {                                 // cells touching the upper faces of a dense level
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                uint32_t i = xy[k & 3] + ((k & 4) ? z0 + L.r2 : z0);
-                if (i >= L.size) {
-                    i -= L.size;
-                    if (i >= L.size) i %= L.size;
-                }
-                const uint32_t* e = base + (size_t)i * (F / 2);
-#pragma unroll
-                for (int f = 0; f < F / 2; ++f) raw[k][f] = __ldg(e + f);
-            }
-        }
-        level_finish<F>(c, raw, l, out);
-    }
+    for (int l = l_begin; l < staged_end; ++l) dense_level<F, true>(m, l, x, y, z, out);
+#pragma unroll 1
+    for (int l = l_begin > staged_end ? l_begin : staged_end; l < dense_end; ++l) dense_level<F, false>(m, l, x, y, z, out);
 #pragma unroll 3
     for (int l = l_begin > n_dense ? l_begin : n_dense; l < l_end; ++l) {
         const float scale = m->level[l].scale;
@@ -151,6 +161,26 @@ __device__ __forceinline__ void hash_encode_range(const EncMeta* m, const __half
         }
         level_finish<F>(c, raw, l, out);
     }
+}
+
+// One hashed level (the level holds 2^k entries).
+template <int F>
+__device__ __forceinline__ void hashed_level(const EncMeta* m, int l, float x, float y, float z, uint32_t (&out)[16]) {
+    const float scale = m->level[l].scale;
+    const uint32_t mask = m->level[l].mask;
+    const uint32_t* base = m->level[l].base;
+    const LevelCell c = level_cell(scale, x, y, z);
+    const uint32_t y0 = c.iy * 2654435761u, y1 = y0 + 2654435761u;
+    const uint32_t z0 = c.iz * 805459861u, z1 = z0 + 805459861u;
+    const uint32_t xy[4] = {c.ix ^ y0, (c.ix + 1u) ^ y0, c.ix ^ y1, (c.ix + 1u) ^ y1};
+    uint32_t raw[8][F / 2];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const uint32_t* e = base + (size_t)((xy[k & 3] ^ ((k & 4) ? z1 : z0)) & mask) * (F / 2);
+#pragma unroll
+        for (int f = 0; f < F / 2; ++f) raw[k][f] = __ldg(e + f);
+    }
+    level_finish<F>(c, raw, l, out);
 }
 
 // Encodes one position into 32 halves, returned as 16 packed pairs.
