@@ -58,6 +58,24 @@ SRF_HD int srf_f2i_rz(float f) {
 #endif
 }
 
+/*
+ * SRF_CANON_PLAIN (host builds of the test oracle only): every fused multiply-add written in this header and in
+ * the including file becomes a separate multiply and add, and the elementary functions below become the C
+ * library's.  That is the arithmetic a host compile of the reference's own source performs
+ * (-ffp-contract=off), so a test oracle built this way can be compared bit for bit with such a compile:
+ * a check of that test oracle's control flow, statement order and association order, independent of the
+ * elementary-function definitions.
+ */
+#if defined(SRF_CANON_PLAIN)
+#if defined(__CUDACC__)
+#error "SRF_CANON_PLAIN is a host-only test mode"
+#endif
+static inline float srf_plain_fmaf(float a, float b, float c) { return a * b + c; }
+static inline double srf_plain_fma(double a, double b, double c) { return a * b + c; }
+#define fmaf(a, b, c) srf_plain_fmaf((a), (b), (c))
+#define fma(a, b, c) srf_plain_fma((a), (b), (c))
+#endif
+
 /* atan(a) for a in [0,1]: a + a*s*P(s), s = a*a, P of degree 8. */
 SRF_HD float srf_atan_unit(float a) {
     const float s = a * a;
@@ -188,12 +206,72 @@ SRF_HD float srf_logf(float x) {
     return fmaf((float)e, 0.693147182f, r);
 }
 
+/*
+ * SRF_CANON_CUDA_MATH (a test-only build of the kernels, never the shipped library): the canonical names map to the
+ * CUDA math library's functions the reference calls -- atan2f, asinf, sinf, cosf, and the fast intrinsics __expf /
+ * __logf -- so that, compiled with nvcc's default -fmad=true, the kernels compute what a CUDA build of the
+ * reference's expressions computes.  The tests measure how far the shipped (canonical) results are from that.
+ */
+#if defined(SRF_CANON_CUDA_MATH) && defined(__CUDACC__)
+static __host__ __device__ __forceinline__ float srf_cm_atan2f(float y, float x) { return atan2f(y, x); }
+static __host__ __device__ __forceinline__ float srf_cm_asinf(float x) { return asinf(x); }
+static __host__ __device__ __forceinline__ float srf_cm_sinf(float x) { return sinf(x); }
+static __host__ __device__ __forceinline__ float srf_cm_cosf(float x) { return cosf(x); }
+static __host__ __device__ __forceinline__ void srf_cm_sincosf(float x, float* s, float* c) { *s = sinf(x); *c = cosf(x); }
+static __host__ __device__ __forceinline__ float srf_cm_expf(float x) {
+#if defined(__CUDA_ARCH__)
+    return __expf(x);
+#else
+    return expf(x);
+#endif
+}
+static __host__ __device__ __forceinline__ float srf_cm_logf(float x) {
+#if defined(__CUDA_ARCH__)
+    return __logf(x);
+#else
+    return logf(x);
+#endif
+}
+#define srf_atan2f srf_cm_atan2f
+#define srf_asinf srf_cm_asinf
+#define srf_sinf srf_cm_sinf
+#define srf_cosf srf_cm_cosf
+#define srf_sincosf srf_cm_sincosf
+#define srf_expf srf_cm_expf
+#define srf_logf srf_cm_logf
+#endif
+
+#if defined(SRF_CANON_PLAIN)
+/* the C library's functions under the canonical names (the definitions above stay compiled but unused) */
+static inline float srf_plain_atan2f(float y, float x) { return atan2f(y, x); }
+static inline float srf_plain_asinf(float x) { return asinf(x); }
+static inline float srf_plain_sinf(float x) { return sinf(x); }
+static inline float srf_plain_cosf(float x) { return cosf(x); }
+static inline void srf_plain_sincosf(float x, float* s, float* c) { *s = sinf(x); *c = cosf(x); }
+static inline float srf_plain_expf(float x) { return expf(x); }
+static inline float srf_plain_logf(float x) { return logf(x); }
+#define srf_atan2f srf_plain_atan2f
+#define srf_asinf srf_plain_asinf
+#define srf_sinf srf_plain_sinf
+#define srf_cosf srf_plain_cosf
+#define srf_sincosf srf_plain_sincosf
+#define srf_expf srf_plain_expf
+#define srf_logf srf_plain_logf
+#endif
+
 /* 1 / (1 + exp(-x)), the shape of tiny-cuda-nn's logistic(). */
 SRF_HD float srf_logisticf(float x) { return 1.0f / (1.0f + srf_expf(-x)); }
 
-/* Euclidean length with a fixed evaluation order: sqrt(fma(z,z,fma(y,y,x*x))). */
+/* Dot product of two 3-vectors the way Eigen reduces three terms, t0 + (t1 + t2), with both additions fused
+ * into multiply-adds: fma(a0,b0, fma(a1,b1, a2*b2)).  The reference's dot(), norm(), normalized() and 3x3
+ * matrix-vector products all reduce in this order (Eigen's unrolled scalar reduction splits [0,n) into
+ * [0,n/2) and [n/2,n)). */
+SRF_HD float srf_dot3f(float a0, float b0, float a1, float b1, float a2, float b2) {
+    return fmaf(a0, b0, fmaf(a1, b1, a2 * b2));
+}
+/* Euclidean length: sqrt of the dot product above. */
 SRF_HD float srf_norm3f(float x, float y, float z) {
-    return sqrtf(fmaf(z, z, fmaf(y, y, x * x)));
+    return sqrtf(srf_dot3f(x, x, y, y, z, z));
 }
 
 #endif /* SRF_CANON_MATH_H_ */

@@ -9,9 +9,10 @@
  *
  *   [M] CUDA math library (atan2f, asinf, cosf, sinf, __expf, __logf, powf): replaced by the
  *       correctly-rounded-primitive definitions of include/srf_canon_math.h.
- *   [E] Eigen (version unpinned): dot/norm/matrix-vector products are evaluated left to
- *       right with the multiply-add pairs fused (what nvcc's default contraction makes of
- *       them): a*b + c*d + e*f  ->  fma(e,f, fma(c,d, a*b)).
+ *   [E] Eigen (version unpinned): dot/norm/matrix-vector products of three terms reduce as
+ *       Eigen's unrolled scalar reduction does, t0 + (t1 + t2), with the additions fused into
+ *       multiply-adds (what nvcc's default contraction makes of them):
+ *       a*b + (c*d + e*f)  ->  fma(a,b, fma(c,d, e*f))   (srf_dot3f).
  *   [T] tiny-cuda-nn (revision unpinned): multiresolution hash encoding, spherical harmonics
  *       and the fully fused MLP are restated from the Instant-NGP paper (Mueller et al. 2022):
  *       fp16 parameters and activations, fp32 accumulation in index order, one rounding to
@@ -183,9 +184,9 @@ inline void pixel_to_ray(const srf_view_t& v, bool snap, uint32_t px, uint32_t p
     const float dz = 1.0f;
     const float* m = v.camera;                                       /* row-major 3x4 */
     *o = v3(m[3], m[7], m[11]);                                      /* :155 */
-    const float rx = fmaf(m[2], dz, fmaf(m[1], dy, m[0] * dx));      /* :161 [E] */
-    const float ry = fmaf(m[6], dz, fmaf(m[5], dy, m[4] * dx));
-    const float rz = fmaf(m[10], dz, fmaf(m[9], dy, m[8] * dx));
+    const float rx = srf_dot3f(m[0], dx, m[1], dy, m[2], dz);        /* :161 [E] */
+    const float ry = srf_dot3f(m[4], dx, m[5], dy, m[6], dz);
+    const float rz = srf_dot3f(m[8], dx, m[9], dy, m[10], dz);
     const float n = srf_norm3f(rx, ry, rz);                          /* :162 [E] */
     *d = v3(rx / n, ry / n, rz / n);
 }
@@ -693,7 +694,11 @@ inline float network_to_density(float v, int act) {
 }
 
 /* ---- colour: internal/utils/common_device.h:70-88 [M] ------------------------------------------- */
+#if defined(SRF_CANON_PLAIN)
+inline float srf_powf(float x, float y) { return powf(x, y); }       /* the C library's, as a host compile of the reference uses */
+#else
 inline float srf_powf(float x, float y) { return x > 0.f ? srf_expf(y * srf_logf(x)) : 0.f; }
+#endif
 inline float srgb_to_linear(float s) { return s <= 0.04045f ? s / 12.92f : srf_powf((s + 0.055f) / 1.055f, 2.4f); }
 inline float linear_to_srgb(float l) { return l < 0.0031308f ? 12.92f * l : 1.055f * srf_powf(l, 0.41666f) - 0.055f; }
 
@@ -713,7 +718,7 @@ void tonemap3(float* x, int curve) {
         const float whiteScale = denom / nom;
         k0 = 4.0f * k0 * whiteScale; k1 = 2.0f * k1 * whiteScale; k2 = k2 * whiteScale; k3 = 4.0f * k3; k4 = 2.0f * k4;
     } else {
-        const float Y = fmaf(0.0722f, x[2], fmaf(0.7152f, x[1], 0.2126f * x[0]));
+        const float Y = srf_dot3f(0.2126f, x[0], 0.7152f, x[1], 0.0722f, x[2]);
         const float s = 1.f / (Y + 1.0f);
         for (int i = 0; i < 3; ++i) x[i] = x[i] * s;
         return;
@@ -874,6 +879,25 @@ int srfo_warp_position(const srf_config_t* cfg, const float* pos, float* out, si
 
 uint64_t srfo_shard_ray_count(const srf_view_t* view) { return shard_rows_total(*view) * view->width; }
 
+/* taps for the known-answer tests: one reference function each, on arrays */
+int srfo_calc_dt(const srf_config_t* cfg, const float* t, float* dt, size_t n) {
+    const Cfg g = resolve(cfg);
+    for (size_t i = 0; i < n; ++i) dt[i] = calc_dt(g, t[i]);
+    return 0;
+}
+int srfo_grid_index(const srf_config_t* cfg, const float* pos, uint32_t* level_out, uint32_t* idx_out, size_t n) {
+    const Cfg g = resolve(cfg);
+    for (size_t i = 0; i < n; ++i) {
+        const V3 p = v3(pos[3 * i], pos[3 * i + 1], pos[3 * i + 2]);
+        const V3 w = warp_position(g, p);
+        const uint32_t level = level_from_pos(g, p, w);
+        level_out[i] = level;
+        idx_out[i] = cascaded_grid_idx_at(g, p, w, level);
+    }
+    return 0;
+}
+void srfo_pixel_offset(uint32_t spp, float* out2) { ld_random_pixel_offset(spp, &out2[0], &out2[1]); }
+
 /* ---- training compositor: internal/render/ray_marcher.cu:9-202, internal/utils/loss.cu:18-101 ---- */
 namespace {
 inline float rgb_derivative(float v, int act) {                      /* common_device.h:331-340 */
@@ -912,6 +936,23 @@ inline void loss_channel(int type, float target, float pred, float* loss, float*
     }
 }
 }  // namespace
+
+int srfo_tonemap(const float* rgb, float* out, size_t n, int curve) {
+    for (size_t i = 0; i < n; ++i) {
+        float c[3] = {rgb[3 * i], rgb[3 * i + 1], rgb[3 * i + 2]};
+        tonemap3(c, curve);
+        out[3 * i] = c[0]; out[3 * i + 1] = c[1]; out[3 * i + 2] = c[2];
+    }
+    return 0;
+}
+int srfo_srgb(const float* in, float* out, size_t n, int to_linear) {
+    for (size_t i = 0; i < n; ++i) out[i] = to_linear ? srgb_to_linear(in[i]) : linear_to_srgb(in[i]);
+    return 0;
+}
+int srfo_loss(const float* target, const float* prediction, float* loss, float* gradient, size_t n, int loss_type) {
+    for (size_t i = 0; i < 3 * n; ++i) loss_channel(loss_type, target[i], prediction[i], &loss[i], &gradient[i]);
+    return 0;
+}
 
 /* All pointers are HOST pointers.  `mean_density` is the grid mean the sampler holds (update_grid_bitfield). */
 int srfo_volume_rendering_loss(const srf_config_t* cfg, const srf_loss_params_t* p, uint32_t n_rays_kept,
@@ -965,7 +1006,7 @@ int srfo_volume_rendering_loss(const srf_config_t* cfg, const srf_loss_params_t*
         float loss[3], grad[3];
         for (int c = 0; c < 3; ++c) loss_channel(p->loss_type, target[c], rgb_ray[c], &loss[c], &grad[c]);   /* :129 */
         const float n_rays_f = (float)p->n_rays;
-        if (loss_output) loss_output[i] = ((loss[0] + loss[1]) + loss[2]) / 3.0f / n_rays_f;   /* :131-132 */
+        if (loss_output) loss_output[i] = (loss[0] + (loss[1] + loss[2])) / 3.0f / n_rays_f;   /* :131-132; [E] mean() reduces as t0 + (t1 + t2) */
         const float loss_scale = p->loss_scale / n_rays_f;           /* :134 */
         const float output_l2_reg = cfg->rgb_activation == SRF_ACT_EXPONENTIAL ? 1e-4f : 0.0f;
         const float output_l1_reg_density = (cfg->use_grid && (mean_density < cfg->min_optical_thickness)) ? 1e-4f : 0.0f;
@@ -1002,7 +1043,7 @@ int srfo_volume_rendering_loss(const srf_config_t* cfg, const srf_loss_params_t*
                 out[k] = loss_scale * (dloss_by_drgb * rgb_derivative(raw[k], cfg->rgb_activation) + fmaxf(0.0f, output_l2_reg * raw[k]));
                 v[k] = T * rgb[k] - (rgb_ray[k] - r2[k]);
             }
-            const float dot = fmaf(grad[2], v[2], fmaf(grad[1], v[1], grad[0] * v[0]));   /* [E] dot */
+            const float dot = srf_dot3f(grad[0], v[0], grad[1], v[1], grad[2], v[2]);   /* [E] dot */
             const float dloss_by_dmlp = density_derivative(raw[3], cfg->density_activation) * (dt * dot);
             out[3] = loss_scale * dloss_by_dmlp + (raw[3] < 0.f ? -output_l1_reg_density : 0.0f);
             for (int k = 0; k < 4; ++k) dl[(size_t)j * p->padded_output_width + k] = f2h(out[k]);
@@ -1056,9 +1097,9 @@ int srfo_mark_untrained(const srf_config_t* cfg, const srf_train_views_t* tv, fl
         for (uint32_t j = 0; j < tv->n_images && !seen; ++j) {       /* :84-99 */
             const float* m = tv->d_xforms + (size_t)j * 12;          /* column-major 3x4 */
             const V3 ploc = v3(pos.x - m[9], pos.y - m[10], pos.z - m[11]);
-            const float cx = fmaf(ploc.z, m[2], fmaf(ploc.y, m[1], ploc.x * m[0]));   /* [E] dot */
-            const float cy = fmaf(ploc.z, m[5], fmaf(ploc.y, m[4], ploc.x * m[3]));
-            const float cz = fmaf(ploc.z, m[8], fmaf(ploc.y, m[7], ploc.x * m[6]));
+            const float cx = srf_dot3f(ploc.x, m[0], ploc.y, m[1], ploc.z, m[2]);     /* [E] dot */
+            const float cy = srf_dot3f(ploc.x, m[3], ploc.y, m[4], ploc.z, m[5]);
+            const float cz = srf_dot3f(ploc.x, m[6], ploc.y, m[7], ploc.z, m[8]);
             if (cz > 0.f)
                 seen = fabsf(cx) - voxel_radius < cz / tv->focal_length[0] * half_resx &&
                        fabsf(cy) - voxel_radius < cz / tv->focal_length[1] * half_resy;
@@ -1098,9 +1139,9 @@ int srfo_sample_training_rays(const srf_config_t* cfg, const srf_train_views_t* 
         const V3 o = v3(m[9], m[10], m[11]);                         /* :576 */
         const float dx = (xx - tv->principal_point[0]) * rw / tv->focal_length[0];   /* :577-581 */
         const float dy = (yy - tv->principal_point[1]) * rh / tv->focal_length[1];
-        const float rx = fmaf(m[6], 1.0f, fmaf(m[3], dy, m[0] * dx));                /* :582 [E] */
-        const float ry = fmaf(m[7], 1.0f, fmaf(m[4], dy, m[1] * dx));
-        const float rz = fmaf(m[8], 1.0f, fmaf(m[5], dy, m[2] * dx));
+        const float rx = srf_dot3f(m[0], dx, m[3], dy, m[6], 1.0f);                  /* :582 [E] */
+        const float ry = srf_dot3f(m[1], dx, m[4], dy, m[7], 1.0f);
+        const float rz = srf_dot3f(m[2], dx, m[5], dy, m[8], 1.0f);
         const float nrm = srf_norm3f(rx, ry, rz);
         const V3 d = v3(rx / nrm, ry / nrm, rz / nrm);
         const float t0 = fmaxf(box_ray_tmin(g.box, o, d), cfg->near_distance);       /* :585-587 */
@@ -1288,7 +1329,7 @@ int srfo_render_frame(const srf_config_t* cfg, const srf_view_t* view, const srf
                     const V3 p = unwarp_position(g, s.w);
                     const float dx = p.x - r.o.x, dy = p.y - r.o.y, dz = p.z - r.o.z;
                     float zz;
-                    if (view->render_mode == SRF_MODE_DEPTH) zz = fmaf(cam_fwd.z, dz, fmaf(cam_fwd.y, dy, cam_fwd.x * dx)) * view->depth_scale;   /* :258 */
+                    if (view->render_mode == SRF_MODE_DEPTH) zz = srf_dot3f(cam_fwd.x, dx, cam_fwd.y, dy, cam_fwd.z, dz) * view->depth_scale;   /* :258 */
                     else zz = srf_norm3f(dx, dy, dz) * view->depth_scale;   /* :261 */
                     rgb[0] = rgb[1] = rgb[2] = zz;
                 } else if (view->render_mode == SRF_MODE_AO) {

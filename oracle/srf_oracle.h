@@ -36,6 +36,13 @@ int srfo_hashgrid_layout(const srf_config_t* cfg, uint32_t* offsets, uint32_t* r
 int srfo_eval_math(int op, const float* a, const float* b, float* out, size_t n);
 int srfo_warp_position(const srf_config_t* cfg, const float* pos, float* out, size_t n, int inverse);
 uint64_t srfo_shard_ray_count(const srf_view_t* view);
+/* one reference function each, on arrays (known-answer taps) */
+int srfo_calc_dt(const srf_config_t* cfg, const float* t, float* dt, size_t n);
+int srfo_grid_index(const srf_config_t* cfg, const float* pos, uint32_t* level_out, uint32_t* idx_out, size_t n);
+void srfo_pixel_offset(uint32_t spp, float* out2);
+int srfo_tonemap(const float* rgb, float* out, size_t n, int curve);
+int srfo_srgb(const float* in, float* out, size_t n, int to_linear);
+int srfo_loss(const float* target, const float* prediction, float* loss, float* gradient, size_t n, int loss_type);
 
 int srfo_generate_rays(const srf_config_t* cfg, const srf_view_t* view, const uint8_t* bitfield,
                        float* dir, float* t, uint8_t* alive, uint32_t* pixel);

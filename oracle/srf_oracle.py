@@ -26,24 +26,47 @@ class Rng(C.Structure):
     _fields_ = [("state", C.c_uint64), ("inc", C.c_uint64)]
 
 
+LIB_PLAIN = HERE / "libsrf_oracle_plain.so"
+
+
 def build(force=False):
-    srcs = [HERE / "srf_oracle.cpp", HERE / "srf_oracle.h", HERE.parent / "include" / "srf_abi.h",
+    srcs = [HERE / "srf_oracle.cpp", HERE / "srf_oracle.h", HERE / "Makefile", HERE.parent / "include" / "srf_abi.h",
             HERE.parent / "include" / "srf_canon_math.h"]
-    if force or not LIB.exists() or any(s.stat().st_mtime > LIB.stat().st_mtime for s in srcs):
-        subprocess.run(["make", "-C", str(HERE)], check=True, capture_output=True)
+    for target in (LIB, LIB_PLAIN):
+        if force or not target.exists() or any(s.stat().st_mtime > target.stat().st_mtime for s in srcs):
+            subprocess.run(["make", "-C", str(HERE)] + (["-B"] if force else []), check=True, capture_output=True)
+            break
     return LIB
 
 
-_lib = None
+_libs = {}
+_plain = False
 
 
 def lib():
-    global _lib
-    if _lib is None:
+    """The oracle library: the canonical one, or inside `plain_arithmetic()` the build with the C library's
+    elementary functions and no fused multiply-adds (comparable bit for bit with oracle/srf_ref.py)."""
+    if _plain not in _libs:
         build()
-        _lib = C.CDLL(str(LIB))
-        _lib.srfo_shard_ray_count.restype = C.c_uint64
-    return _lib
+        l = C.CDLL(str(LIB_PLAIN if _plain else LIB))
+        l.srfo_shard_ray_count.restype = C.c_uint64
+        _libs[_plain] = l
+    return _libs[_plain]
+
+
+class plain_arithmetic:
+    """Context manager: every oracle call inside runs in the plain-arithmetic build."""
+
+    def __enter__(self):
+        global _plain
+        self._old = _plain
+        _plain = True
+        return self
+
+    def __exit__(self, *exc):
+        global _plain
+        _plain = self._old
+        return False
 
 
 def _p(a):
@@ -161,6 +184,47 @@ def warp_position(cfg, pos, inverse=False):
     out = np.zeros_like(pos)
     lib().srfo_warp_position(C.byref(cfg), _p(pos), _p(out), C.c_size_t(pos.shape[0]), C.c_int(1 if inverse else 0))
     return out
+
+
+def calc_dt(cfg, t):
+    t = np.ascontiguousarray(t, np.float32)
+    out = np.zeros_like(t)
+    lib().srfo_calc_dt(C.byref(cfg), _p(t), _p(out), C.c_size_t(t.size))
+    return out
+
+
+def grid_index(cfg, pos):
+    pos = np.ascontiguousarray(pos, np.float32)
+    level = np.zeros(pos.shape[0], np.uint32); idx = np.zeros(pos.shape[0], np.uint32)
+    lib().srfo_grid_index(C.byref(cfg), _p(pos), _p(level), _p(idx), C.c_size_t(pos.shape[0]))
+    return level, idx
+
+
+def pixel_offset(spp):
+    out = np.zeros(2, np.float32)
+    lib().srfo_pixel_offset(C.c_uint32(spp), _p(out))
+    return out
+
+
+def tonemap(rgb, curve):
+    rgb = np.ascontiguousarray(rgb, np.float32)
+    out = np.zeros_like(rgb)
+    lib().srfo_tonemap(_p(rgb), _p(out), C.c_size_t(rgb.shape[0]), C.c_int(curve))
+    return out
+
+
+def srgb(x, to_linear):
+    x = np.ascontiguousarray(x, np.float32)
+    out = np.zeros_like(x)
+    lib().srfo_srgb(_p(x), _p(out), C.c_size_t(x.size), C.c_int(1 if to_linear else 0))
+    return out
+
+
+def loss(target, prediction, loss_type):
+    t = np.ascontiguousarray(target, np.float32); p = np.ascontiguousarray(prediction, np.float32)
+    l = np.zeros_like(t); g = np.zeros_like(t)
+    lib().srfo_loss(_p(t), _p(p), _p(l), _p(g), C.c_size_t(t.shape[0]), C.c_int(loss_type))
+    return l, g
 
 
 def hashgrid_layout(cfg):

@@ -213,6 +213,16 @@ def lib_path() -> Path:
     return Path(override) if override else Path(__file__).resolve().parent / LIB_NAME
 
 
+def load_from(path):
+    """Loads a build of the C-ABI library from `path` and types every declared symbol."""
+    lib = C.CDLL(str(path))
+    for name, (restype, argtypes) in SYMBOLS.items():
+        fn = getattr(lib, name)   # AttributeError if the symbol is not exported
+        fn.restype = restype
+        fn.argtypes = argtypes
+    return lib
+
+
 def load():
     """Loads libsrf_b200.so and types every declared symbol.  Raises if anything is missing."""
     global _lib
@@ -222,13 +232,8 @@ def load():
     if not path.exists():
         raise RuntimeError(f"{path} is missing: build it with `python __graft_entry__.py build` "
                            "(nvcc, sm_100a). There is no fallback path.")
-    lib = C.CDLL(str(path))
-    for name, (restype, argtypes) in SYMBOLS.items():
-        fn = getattr(lib, name)   # AttributeError if the symbol is not exported
-        fn.restype = restype
-        fn.argtypes = argtypes
-    _lib = lib
-    return lib
+    _lib = load_from(path)
+    return _lib
 
 
 class SrfError(RuntimeError):

@@ -35,7 +35,7 @@ __device__ void tonemap3(float* x, int curve) {
         const float whiteScale = denom / nom;
         k0 = 4.0f * k0 * whiteScale; k1 = 2.0f * k1 * whiteScale; k2 = k2 * whiteScale; k3 = 4.0f * k3; k4 = 2.0f * k4;
     } else {
-        const float Y = fmaf(0.0722f, x[2], fmaf(0.7152f, x[1], 0.2126f * x[0]));
+        const float Y = srf_dot3f(0.2126f, x[0], 0.7152f, x[1], 0.0722f, x[2]);
         const float s = 1.f / (Y + 1.0f);
         for (int i = 0; i < 3; ++i) x[i] = x[i] * s;
         return;

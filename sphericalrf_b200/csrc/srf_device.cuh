@@ -164,9 +164,9 @@ __device__ __forceinline__ void pixel_to_ray(const DevView& v, uint32_t px, uint
     const float dy = (yy - v.ppy) * v.rh / v.fy;
     const float* m = v.cam;
     *o = mk3(m[3], m[7], m[11]);
-    const float rx = fmaf(m[2], 1.0f, fmaf(m[1], dy, m[0] * dx));
-    const float ry = fmaf(m[6], 1.0f, fmaf(m[5], dy, m[4] * dx));
-    const float rz = fmaf(m[10], 1.0f, fmaf(m[9], dy, m[8] * dx));
+    const float rx = srf_dot3f(m[0], dx, m[1], dy, m[2], 1.0f);
+    const float ry = srf_dot3f(m[4], dx, m[5], dy, m[6], 1.0f);
+    const float rz = srf_dot3f(m[8], dx, m[9], dy, m[10], 1.0f);
     const float n = srf_norm3f(rx, ry, rz);
     *d = mk3(rx / n, ry / n, rz / n);
 }
@@ -573,7 +573,11 @@ __device__ __forceinline__ float network_to_density_derivative(float v, int act)
     }
 }
 
+#if defined(SRF_CANON_CUDA_MATH)
+__device__ __forceinline__ float srf_powf(float x, float y) { return powf(x, y); }      // test-only build: see srf_canon_math.h
+#else
 __device__ __forceinline__ float srf_powf(float x, float y) { return x > 0.f ? srf_expf(y * srf_logf(x)) : 0.f; }
+#endif
 __device__ __forceinline__ float srgb_to_linear(float s) {
     return s <= 0.04045f ? s / 12.92f : srf_powf((s + 0.055f) / 1.055f, 2.4f);
 }
@@ -593,7 +597,7 @@ __device__ __forceinline__ float4 shade_sample(const DevCfg& g, const DevView& v
         const V3 p = unwarp_position(g, w);
         const float dx = p.x - v.cam[3], dy = p.y - v.cam[7], dz = p.z - v.cam[11];
         float zz;
-        if (v.render_mode == SRF_MODE_DEPTH) zz = fmaf(v.cam[10], dz, fmaf(v.cam[6], dy, v.cam[2] * dx)) * v.depth_scale;
+        if (v.render_mode == SRF_MODE_DEPTH) zz = srf_dot3f(v.cam[2], dx, v.cam[6], dy, v.cam[10], dz) * v.depth_scale;
         else zz = srf_norm3f(dx, dy, dz) * v.depth_scale;
         cr = cg = cb = zz;
     } else if (v.render_mode == SRF_MODE_AO) {

@@ -145,7 +145,7 @@ k_loss_backward(const DevCfg g, const LossParams lp, const uint32_t* __restrict_
     float loss[3], grad[3];
     for (int c = 0; c < 3; ++c) loss_channel(lp.loss_type, target[c], rgb_ray[c], &loss[c], &grad[c]);
     const float n_rays_f = (float)lp.n_rays;
-    if (loss_output && lane == 0) loss_output[i] = ((loss[0] + loss[1]) + loss[2]) / 3.0f / n_rays_f;
+    if (loss_output && lane == 0) loss_output[i] = (loss[0] + (loss[1] + loss[2])) / 3.0f / n_rays_f;   // Eigen reduces three terms as t0 + (t1 + t2)
     const float loss_scale = lp.loss_scale / n_rays_f;
     const float output_l2_reg = g.rgb_activation == SRF_ACT_EXPONENTIAL ? 1e-4f : 0.0f;
     const float output_l1_reg_density = (g.use_grid && (*mean_density < lp.min_optical_thickness)) ? 1e-4f : 0.0f;
@@ -201,7 +201,7 @@ k_loss_backward(const DevCfg g, const LossParams lp, const uint32_t* __restrict_
                 out[c] = loss_scale * (dloss_by_drgb * network_to_rgb_derivative(raw[c], g.rgb_activation) + fmaxf(0.0f, output_l2_reg * raw[c]));
                 v[c] = my_T * rgb[c] - (rgb_ray[c] - my_r2[c]);                               // T * rgb - suffix
             }
-            const float dot = fmaf(grad[2], v[2], fmaf(grad[1], v[1], grad[0] * v[0]));
+            const float dot = srf_dot3f(grad[0], v[0], grad[1], v[1], grad[2], v[2]);
             const float dloss_by_dmlp = network_to_density_derivative(o.s, g.density_activation) * (dt * dot);
             out[3] = loss_scale * dloss_by_dmlp + (o.s < 0.f ? -output_l1_reg_density : 0.0f);
             __half* d = dloss_doutput + ((uint64_t)compacted_base + j_mine) * lp.padded_output_width;

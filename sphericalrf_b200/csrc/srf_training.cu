@@ -16,7 +16,7 @@ namespace {
 
 
 __device__ __forceinline__ float dot3(const V3& a, const float* b) {
-    return fmaf(a.z, b[2], fmaf(a.y, b[1], a.x * b[0]));
+    return srf_dot3f(a.x, b[0], a.y, b[1], a.z, b[2]);
 }
 
 __global__ void __launch_bounds__(256)
@@ -95,9 +95,9 @@ __device__ __forceinline__ TrainRay train_ray_setup(const DevCfg& g, const Train
     r.o = mk3(m[9], m[10], m[11]);
     const float dx = (xx - tv.pp_x) * rw / tv.focal_x;
     const float dy = (yy - tv.pp_y) * rh / tv.focal_y;
-    const float rx = fmaf(m[6], 1.0f, fmaf(m[3], dy, m[0] * dx));
-    const float ry = fmaf(m[7], 1.0f, fmaf(m[4], dy, m[1] * dx));
-    const float rz = fmaf(m[8], 1.0f, fmaf(m[5], dy, m[2] * dx));
+    const float rx = srf_dot3f(m[0], dx, m[3], dy, m[6], 1.0f);
+    const float ry = srf_dot3f(m[1], dx, m[4], dy, m[7], 1.0f);
+    const float rz = srf_dot3f(m[2], dx, m[5], dy, m[8], 1.0f);
     const float n = srf_norm3f(rx, ry, rz);
     r.d = mk3(rx / n, ry / n, rz / n);
     const float t0 = fmaxf(box_ray_tmin(g, r.o, r.d), g.near_distance);

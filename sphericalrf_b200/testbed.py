@@ -26,8 +26,8 @@ def _np_ptr(a):
 class Renderer:
     """One library context on one GPU."""
 
-    def __init__(self, cfg: abi.Config, device: int = 0):
-        self.lib = abi.load()
+    def __init__(self, cfg: abi.Config, device: int = 0, lib=None):
+        self.lib = abi.load() if lib is None else lib      # `lib`: another build of the same C-ABI (tests)
         self.cfg = cfg
         self.device = device
         self.ctx = C.c_void_p()

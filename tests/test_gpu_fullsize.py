@@ -77,28 +77,39 @@ def test_config1_full_frame(built_lib, oracle_mod):
     assert st["n_rays"] == 1027125 and st["n_samples"] == int(a["n_samples"].astype(np.int64).sum())
     assert st["n_batches"] >= 1 and st["error_flags"] == 0
     orc = _oracle(oracle_mod, sc, r.download_bitfield())
-    for first in (0, 1245 * 412 + 600):
-        n = 24
+    # 16 windows of 256 consecutive rays spread over the image (4 096 rays, ~6.6 M samples through the oracle)
+    n = 256
+    for k in range(16):
+        first = (825 * k // 16 + 25) * 1245 + (k * 61) % (1245 - n)
         ref = orc.render_frame(view, post, first, n)
         sl = slice(first, first + n)
-        assert np.abs(ref["rgba_raw"][sl] - a["rgba_raw"][sl]).max() <= 1e-3
-        assert np.abs(ref["out"][sl] - a["out"][sl]).max() <= 1e-3
-        counts, *_ = orc.march(view, first, n, 1 << 22)
-        assert np.array_equal(counts, a["n_samples"][sl])
+        assert np.abs(ref["rgba_raw"][sl] - a["rgba_raw"][sl]).max() <= 1e-3, f"window {k}"
+        assert np.abs(ref["out"][sl] - a["out"][sl]).max() <= 1e-3, f"window {k}"
+        assert np.array_equal(orc.march(view, first, n, 1 << 23)[0], a["n_samples"][sl]), f"window {k}: per-ray sample counts"
 
 
-def test_config2_orbit_views_and_host_image(built_lib):
-    """Two views of the 32-view orbit through srf_render (host image): shapes, finiteness, distinct views."""
-    sc = synth.scene_config1(n_views=32, width=311, height=206)      # quarter resolution of the orbit frames
+def test_config2_all_orbit_views_against_the_oracle(built_lib, oracle_mod):
+    """All 32 views of the 360-degree orbit at the full 1245x825 through srf_render (host image): a window of 64 rays of
+    every view against the oracle (counts exact, pixels within 1e-3), opaque background, distinct views."""
+    sc = synth.scene_config1(n_views=32)
     r = _renderer(sc)
-    imgs = []
-    for k in (0, 9):
-        view = abi.make_view(sc["cameras"][k], 311, 206, sc["rfl"])
-        img = r.render(view, abi.default_post(), spp=1)
-        assert img.shape == (206, 311, 4) and np.isfinite(img).all()
+    orc = _oracle(oracle_mod, sc, r.download_bitfield())
+    post = abi.default_post()
+    prev = None
+    for k in range(32):
+        view = abi.make_view(sc["cameras"][k], 1245, 825, sc["rfl"])
+        img = r.render(view, post, spp=1)
+        assert img.shape == (825, 1245, 4) and np.isfinite(img).all()
         assert np.allclose(img[..., 3], 1.0, atol=1e-6)                  # opaque background
-        imgs.append(img)
-    assert np.abs(imgs[0] - imgs[1]).max() > 1e-3
+        first = ((37 * k) % 800 + 10) * 1245 + (101 * k) % 1100
+        ref = orc.render_frame(view, post, first, 64)
+        flat = img.reshape(-1, 4)
+        assert np.abs(ref["out"][first:first + 64] - flat[first:first + 64]).max() <= 1e-3, f"view {k}"
+        counts = r.dump_samples(view, first, 64, 1 << 20)[0]
+        assert np.array_equal(counts, orc.march(view, first, 64, 1 << 21)[0]), f"view {k}: per-ray sample counts"
+        if prev is not None:
+            assert np.abs(img - prev).max() > 1e-3
+        prev = img
 
 
 def test_config3_full_grid_refresh(built_lib, oracle_mod):
@@ -121,7 +132,7 @@ def test_config3_full_grid_refresh(built_lib, oracle_mod):
     assert 0.0 < np.unpackbits(bits).mean() < 1.0
 
 
-def test_config4_high_resolution_shard(built_lib):
+def test_config4_high_resolution_shard(built_lib, oracle_mod):
     """One of eight shards of a 3840x2160 view of the dense scene, with the opt-in 2048-sample cap."""
     sc = synth.scene_config4()
     r = _renderer(sc)
@@ -133,3 +144,13 @@ def test_config4_high_resolution_shard(built_lib):
     assert np.isfinite(a["out"]).all()
     b = r.render_frame(view, abi.default_post())
     assert np.array_equal(a["out"].view(np.uint32), b["out"].view(np.uint32))
+    # three windows of the shard against the oracle, with the cap in force
+    orc = _oracle(oracle_mod, sc, r.download_bitfield())
+    n_local = r.n_rays(view)
+    a = r.render_frame(view, abi.default_post(), want_raw=True, want_counts=True)
+    for first in (5 * 3840 + 100, n_local // 2 + 1700, n_local - 3840 - 500):
+        ref = orc.render_frame(view, abi.default_post(), first, 48)
+        sl = slice(first, first + 48)
+        assert np.array_equal(orc.march(view, first, 48, 1 << 21)[0], a["n_samples"][sl])
+        assert np.abs(ref["rgba_raw"][sl] - a["rgba_raw"][sl]).max() <= 1e-3
+        assert np.abs(ref["out"][sl] - a["out"][sl]).max() <= 1e-3
