@@ -219,14 +219,14 @@ static __host__ __device__ __forceinline__ float srf_cm_sinf(float x) { return s
 static __host__ __device__ __forceinline__ float srf_cm_cosf(float x) { return cosf(x); }
 static __host__ __device__ __forceinline__ void srf_cm_sincosf(float x, float* s, float* c) { *s = sinf(x); *c = cosf(x); }
 static __host__ __device__ __forceinline__ float srf_cm_expf(float x) {
-#if defined(__CUDA_ARCH__)
-    return __expf(x);
+#if defined(__CUDA_ARCH__) && !defined(SRF_CANON_CUDA_MATH_ACCURATE_EXP)
+    return __expf(x);      /* the reference's choice; SRF_CANON_CUDA_MATH_ACCURATE_EXP swaps in expf to isolate its effect */
 #else
     return expf(x);
 #endif
 }
 static __host__ __device__ __forceinline__ float srf_cm_logf(float x) {
-#if defined(__CUDA_ARCH__)
+#if defined(__CUDA_ARCH__) && !defined(SRF_CANON_CUDA_MATH_ACCURATE_EXP)
     return __logf(x);
 #else
     return logf(x);

@@ -1,4 +1,4 @@
-"""Reader and writer of the reference's snapshot files.
+"""Test helpers for the reference's snapshot files (the reader that ships is C++: include/srf_testbed.hpp).
 
 A snapshot is the model configuration (the JSON of `load_model_config`) serialised as msgpack with one extra
 section, written by Testbed::save_snapshot and read by Testbed::load_snapshot (internal/testbed.cu:135-171):
@@ -28,24 +28,6 @@ DENSITY_MLP_PARAMS = 64 * 32 + 16 * 64
 RGB_MLP_PARAMS = 64 * 32 + 64 * 64 + 16 * 64
 
 
-def _msgpack():
-    try:
-        import msgpack
-    except ImportError as e:                                   # pragma: no cover
-        raise RuntimeError("snapshot files need the `msgpack` Python package") from e
-    return msgpack
-
-
-def _binary(obj) -> bytes:
-    """A msgpack `bin` value, or the {"bytes": [...]} object some JSON libraries write for binary."""
-    if isinstance(obj, (bytes, bytearray, memoryview)):
-        return bytes(obj)
-    if isinstance(obj, dict) and "bytes" in obj:
-        b = obj["bytes"]
-        return bytes(b) if not isinstance(b, (bytes, bytearray)) else bytes(b)
-    raise RuntimeError("ERROR in loading snapshot.")
-
-
 def table_entries(cfg: abi.Config) -> int:
     """Number of hash-grid parameters (halves) of a configuration."""
     from .synth import hashgrid_layout
@@ -54,18 +36,18 @@ def table_entries(cfg: abi.Config) -> int:
 
 
 def read_snapshot(path: str) -> dict:
-    """Parses a snapshot file into dict(model_config, scene_scale, scene_offset, density_grid,
-    density_mlp, rgb_mlp, hash_table) with fp32 grid and fp16 parameters.  Raises the reference's
-    "ERROR in loading snapshot." when the section is missing."""
-    msgpack = _msgpack()
+    """Parses a snapshot file with the C++ host's msgpack reader into dict(model_config, scene_scale, scene_offset,
+    density_grid, density_mlp, rgb_mlp, hash_table) with fp32 grid and fp16 parameters: a test helper that mirrors
+    srf_host::parse_snapshot (include/srf_testbed.hpp), which is what `pyngp.Testbed.load_snapshot` runs."""
+    from . import pyngp
     with open(path, "rb") as f:
-        model_config = msgpack.unpackb(f.read(), raw=False, strict_map_key=False)
+        model_config = pyngp.parse_msgpack(f.read())
     if not isinstance(model_config, dict) or "snapshot" not in model_config:
         raise RuntimeError("ERROR in loading snapshot.")
     snap = model_config["snapshot"]
-    grid = np.frombuffer(_binary(snap["density_grid"]), dtype=np.float32).copy()
+    grid = np.frombuffer(snap["density_grid"], dtype=np.float32).copy()
     ptype = snap.get("params_type", "__half")
-    raw = _binary(snap["params_binary"])
+    raw = snap["params_binary"]
     if ptype == "float":
         params = np.frombuffer(raw, dtype=np.float32).astype(np.float16)
     elif ptype == "__half":
@@ -87,7 +69,7 @@ def read_snapshot(path: str) -> dict:
 def write_snapshot(path: str, model_config: dict, density_grid, density_mlp, rgb_mlp, hash_table,
                    scene_scale=1.0, scene_offset=(0.5, 0.5, 0.5), full_precision=False):
     """Writes the structure Testbed::save_snapshot writes (no optimizer state)."""
-    msgpack = _msgpack()
+    from . import pyngp
     params = np.concatenate([np.asarray(density_mlp, np.float16).reshape(-1), np.asarray(rgb_mlp, np.float16).reshape(-1),
                              np.asarray(hash_table, np.float16).reshape(-1)])
     doc = dict(model_config)
@@ -100,4 +82,4 @@ def write_snapshot(path: str, model_config: dict, density_grid, density_mlp, rgb
         "scene_offset": [float(x) for x in scene_offset],
     }
     with open(path, "wb") as f:
-        f.write(msgpack.packb(doc, use_bin_type=True))
+        f.write(pyngp.write_msgpack(doc))

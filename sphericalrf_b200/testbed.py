@@ -1,18 +1,13 @@
-"""Host-side mirror of the reference's Python surface, on top of the C-ABI.
+"""ctypes helpers above the C-ABI for tests and the benchmark.
 
-`Renderer` is a thin, explicit wrapper (numpy / torch in and out) used by tests and the benchmark.
-`Testbed` mirrors the parts of `pyngp.Testbed` the reference's drivers use for inference
-(internal/python_api.cu:84-133; experiment/*/python/run.py:128-250): `load_model_config`,
-`render`, `set_nerf_camera_matrix`, `fov`, `fov_xy`, `background_color`, `color_space`,
-`density_activation`, `rgb_activation`, `rendering_buffer.*`.  All arithmetic happens in
-libsrf_b200.so on the GPU; torch is used for device memory and streams only.
+`Renderer` is a thin, explicit wrapper of one library context (numpy / torch in and out).  The reference's Python
+surface (`pyngp.Testbed`: internal/python_api.cu:84-133) is the compiled module `sphericalrf_b200.pyngp`, built from
+the C++ host in include/srf_testbed.hpp; nothing of it lives here.  All arithmetic happens in libsrf_b200.so on the
+GPU; torch is used for device memory and streams only.
 """
 from __future__ import annotations
 
 import ctypes as C
-import json
-import math
-from pathlib import Path
 
 import numpy as np
 
@@ -262,189 +257,8 @@ def eval_math(op, a, b=None, device=0):
     return out
 
 
-# ---- configuration parsing (the reference's JSON keys, including the "samlper" spelling) --------
-_WARPS = {"ngp": abi.WARP_NGP, "mipnerf360": abi.WARP_MIPNERF360, "donerf": abi.WARP_DONERF, "sigmoid": abi.WARP_SIGMOID,
-          "erp": abi.WARP_ERP, "sinusoidalprojection": abi.WARP_SINUSOIDAL}
-_SAMPLINGS = {"original": abi.SAMPLING_ORIGINAL, "disparity": abi.SAMPLING_DISPARITY, "log": abi.SAMPLING_LOG}
-_GRIDS = {"warpedspace_exp": abi.GRID_WARPED_EXP, "warpedspace_reciprocal": abi.GRID_WARPED_RECIPROCAL,
-          "metricspace_exp": abi.GRID_METRIC_EXP, "metricspace_reciprocal": abi.GRID_METRIC_RECIPROCAL}
-
-
 def config_from_json(model_config: dict) -> abi.Config:
-    """Reads the sections the reference reads (internal/testbed.cu:65-76) with its defaults
-    (internal/sampler/occupancy_sampler.cu:909-944, internal/render/ray_marcher.cu:294-301,
-    internal/network/ngp_network.h:597-637) and its error messages."""
-    c = abi.default_config()
-    s = model_config["samlper"]
-    try:
-        c.warping_type = _WARPS[str(s.get("warping_type", "NGP")).lower()]
-    except KeyError:
-        raise RuntimeError("Unknown warping type.")
-    c.aabb_scale = int(s.get("aabb_scale", 1))
-    c.use_grid = 1 if s.get("use_grid", True) else 0
-    if c.use_grid:
-        c.grid_size = int(s.get("grid_size", 128))
-        c.num_cascades = int(s.get("num_cascades", 1))
-        c.ema_decay = float(s.get("ema_decay", 0.95))
-        try:
-            c.grid_distribution_type = _GRIDS[str(s.get("grid_distribution_type", "Exp")).lower()]
-        except KeyError:
-            raise RuntimeError("Unknown grid distribution type.")   # the reference's default "Exp" throws as well
-    c.maximum_marching_steps = int(s.get("maximum_marching_steps", 1024))
-    c.cone_angle_constant = float(s.get("cone_angle_constant", 0.0))
-    c.min_cone_stepsize = float(s.get("min_cone_stepsize", 0.0))
-    c.max_cone_stepsize = float(s.get("max_cone_stepsize", 0.0))
-    c.near_distance = float(s.get("near_distance", 0.2))
-    c.far_distance = float(s.get("far_distance", 100.0))
-    try:
-        c.sampling_type = _SAMPLINGS[str(s.get("sampling_type", "Original")).lower()]
-    except KeyError:
-        raise RuntimeError("Unknown sampling type.")
-    c.snap_to_pixel_centers_in_rendering = 1 if s.get("snap_to_pixel_centers_in_rendering", True) else 0
-    c.min_optical_thickness = float(s.get("min_optical_thickness", 0.01))
-    r = model_config.get("render", {})
-    c.transmittance_threshold = float(r.get("transmittance_threshold", 1e-4))
-    c.train_in_linear_color = 1 if r.get("train_in_linear_color", False) else 0
-    enc = model_config["network"]["encoding"]
-    fpl = int(enc.get("n_features_per_level", 2))
-    n_levels = int(enc.get("n_levels", 16))
-    if enc.get("n_features", 0):
-        n_levels = int(enc["n_features"]) // fpl
-    c.n_levels, c.n_features_per_level = n_levels, fpl
-    c.log2_hashmap_size = int(enc.get("log2_hashmap_size", 15))
-    base = int(enc.get("base_resolution", 0))
-    c.base_resolution = base if base else 1 << (c.log2_hashmap_size // 3)
-    c.desired_resolution = float(enc.get("desired_resolution", 2048.0))
-    c.per_level_scale = float(enc.get("per_level_scale", 0.0))
-    for key in ("network", "rgb_network"):
-        net = model_config["network"][key]
-        if int(net.get("n_neurons", 64)) != 64:
-            raise RuntimeError("this library implements the 64-neuron MLPs every shipped config uses")
-    if int(model_config["network"]["network"].get("n_hidden_layers", 1)) != 1 or \
-       int(model_config["network"]["rgb_network"].get("n_hidden_layers", 2)) != 2:
-        raise RuntimeError("this library implements 1 hidden density layer and 2 hidden colour layers")
-    if int(model_config["network"]["dir_encoding"].get("degree", 4)) != 4:
-        raise RuntimeError("this library implements spherical harmonics of degree 4")
-    return c
-
-
-class _RenderingBuffer:
-    """Testbed::RenderingBuffer fields exposed to Python (internal/python_api.cu:123-133)."""
-
-    def __init__(self):
-        self.render_mode = abi.MODE_SHADE
-        self.tonemap_curve = abi.TONEMAP_IDENTITY
-        self.exposure = 0.0
-        self.fov_axis = 1
-        self.relative_focal_length = [1.0, 1.0]
-        self.principal_point = [0.5, 0.5]
-        self.MIN_STEPS_INBETWEEN_COMPACTION = 1   # kept for compatibility; the frame loop has no compaction rounds
-        self.MAX_STEPS_INBETWEEN_COMPACTION = 8
-
-
-class Testbed:
-    """Inference-side mirror of `pyngp.Testbed`."""
-
-    def __init__(self, device: int = 0):
-        self.device = device
-        self.renderer = None
-        self.density_activation = abi.ACT_EXPONENTIAL       # testbed.h:115-116
-        self.rgb_activation = abi.ACT_LOGISTIC
-        self.background_color = [0.0, 0.0, 0.0, 1.0]        # testbed.h:117
-        self.color_space = abi.COLOR_LINEAR
-        self.rendering_buffer = _RenderingBuffer()
-        self.scene_scale = 1.0
-        self.scene_offset = np.array([0.5, 0.5, 0.5], np.float32)
-        self._camera = np.zeros((3, 4), np.float32)
-        self.model_config = None
-        self.cfg = None
-
-    # -- configuration --
-    def load_model_config(self, config_path: str):
-        p = Path(config_path)
-        if not str(config_path) or not p.exists():
-            raise RuntimeError("The model config must exist.")
-        if p.suffix.lower() == ".msgpack":
-            from .snapshot import _msgpack
-            with open(p, "rb") as f:
-                self.load_model_config_dict(_msgpack().unpackb(f.read(), raw=False, strict_map_key=False))
-            return
-        if p.suffix.lower() != ".json":
-            raise RuntimeError("The model config must be a .json or .msgpack file.")
-        with open(p) as f:
-            text = "\n".join(line.split("//")[0] for line in f.read().splitlines())   # the reference parses with comments allowed
-        self.load_model_config_dict(json.loads(text))
-
-    def load_model_config_dict(self, model_config: dict):
-        self.model_config = model_config
-        self.cfg = config_from_json(model_config)
-        self.cfg.density_activation = self.density_activation
-        self.cfg.rgb_activation = self.rgb_activation
-        if self.renderer is not None:
-            self.renderer.close()
-        self.renderer = Renderer(self.cfg, self.device)
-
-    def load_parameters(self, hash_table, density_mlp, rgb_mlp, density_grid, scene_scale=1.0, scene_offset=(0.5, 0.5, 0.5)):
-        """What load_snapshot restores (internal/testbed.cu:151-171), from arrays: network parameters,
-        density grid (followed by update_grid_bitfield), scene scale and offset."""
-        self.renderer.upload_network(hash_table, density_mlp, rgb_mlp)
-        self.renderer.upload_density_grid(density_grid)
-        self.renderer.update_grid_bitfield()
-        self.scene_scale = float(scene_scale)
-        self.scene_offset = np.asarray(scene_offset, np.float32)
-
-    def load_snapshot(self, snapshot_path: str):
-        """Testbed::load_snapshot (internal/testbed.cu:151-171): configuration, scene scale and offset, density
-        grid (+ update_grid_bitfield) and network parameters from one .msgpack file."""
-        from . import snapshot
-        self.load_model_config(snapshot_path)
-        if "snapshot" not in self.model_config:
-            raise RuntimeError("ERROR in loading snapshot.")
-        snap = snapshot.read_snapshot(snapshot_path)
-        want = snapshot.table_entries(self.cfg)
-        if snap["hash_table"].size != want:
-            raise RuntimeError(f"snapshot holds {snap['hash_table'].size} hash-grid parameters, the configuration needs {want}")
-        self.load_parameters(snap["hash_table"], snap["density_mlp"], snap["rgb_mlp"], snap["density_grid"],
-                             snap["scene_scale"], snap["scene_offset"])
-
-    # -- camera (internal/testbed.h:73-89, internal/utils/common_device.h:105-141) --
-    @property
-    def fov(self):
-        fl = np.float32(self.rendering_buffer.relative_focal_length[self.rendering_buffer.fov_axis])
-        return float(180.0 * (2.0 / math.pi) * np.arctan(np.float32(1.0) / (fl * np.float32(2.0))))   # degrees
-
-    @fov.setter
-    def fov(self, rad):
-        f = float(np.float32(0.5) / np.float32(math.tan(0.5 * float(rad))))                            # radians in
-        self.rendering_buffer.relative_focal_length = [f, f]
-
-    @property
-    def fov_xy(self):
-        return [float(180.0 * (2.0 / math.pi) * np.arctan(np.float32(1.0) / (np.float32(f) * np.float32(2.0))))
-                for f in self.rendering_buffer.relative_focal_length]
-
-    @fov_xy.setter
-    def fov_xy(self, rads):
-        self.rendering_buffer.relative_focal_length = [float(np.float32(0.5) / np.float32(math.tan(0.5 * float(r)))) for r in rads]
-
-    def set_nerf_camera_matrix(self, cam):
-        m = np.asarray(cam, np.float32).reshape(3, 4).copy()
-        m[:, 1] *= -1.0
-        m[:, 2] *= -1.0
-        m[:, 3] = m[:, 3] * np.float32(self.scene_scale) + self.scene_offset
-        self._camera = m
-
-    # -- rendering (internal/python_api.cu:17-41) --
-    def render(self, width=1920, height=1080, spp=1, to_srgb=True):
-        if self.renderer is None:
-            raise RuntimeError("load_model_config first")
-        rb = self.rendering_buffer
-        view = abi.make_view(self._camera, width, height, rb.relative_focal_length, rb.principal_point, 0,
-                             int(rb.render_mode), 1.0 / self.scene_scale)
-        post = abi.default_post()
-        post.exposure = float(rb.exposure)
-        post.background_color[:] = [float(x) for x in self.background_color]
-        post.color_space = int(self.color_space)
-        post.tonemap_curve = int(rb.tonemap_curve)
-        post.to_srgb = 1 if to_srgb else 0
-        return self.renderer.render(view, post, spp)
+    """The configuration structure the C++ host (include/srf_testbed.hpp, srf_host::parse_config) derives from a
+    parsed model configuration: the reference's keys, defaults and error messages."""
+    from . import pyngp
+    return abi.Config.from_buffer_copy(pyngp.parse_config(model_config))

@@ -14,7 +14,9 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent.parent
 CSRC = ROOT / "sphericalrf_b200" / "csrc"
 OUT = Path(__file__).resolve().parent / "_cudamath"
-LIB = OUT / "libsrf_b200_cudamath.so"
+# "fast": __expf/__logf as the reference writes them.  "accurate": the same build with expf/logf, to show how much of
+# the difference is the fast intrinsics' error in 1 - exp(-sigma*dt) for small sigma*dt.
+LIBS = {"fast": OUT / "libsrf_b200_cudamath.so", "accurate": OUT / "libsrf_b200_cudamath_accurate_exp.so"}
 
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-DSRF_CANON_CUDA_MATH",
          "-fmad=true", "-Xcompiler", "-fPIC,-O2"]
@@ -27,8 +29,10 @@ def _nvcc():
     return None
 
 
-def build():
+def build(variant="fast"):
     """Returns the library's path; builds it where nvcc exists, otherwise it must already be there (None if not)."""
+    LIB = LIBS[variant]
+    extra = ["-DSRF_CANON_CUDA_MATH_ACCURATE_EXP"] if variant == "accurate" else []
     nvcc = _nvcc()
     sources = sorted(CSRC.glob("*.cu"))
     headers = sorted(CSRC.glob("*.cuh")) + sorted((ROOT / "include").glob("*.h"))
@@ -41,9 +45,9 @@ def build():
     ccbin = ["-ccbin", "/usr/bin/g++"] if Path("/usr/bin/g++").exists() else []
     procs, objs = [], []
     for src in sources:
-        obj = OUT / (src.stem + ".o")
+        obj = OUT / (f"{variant}_{src.stem}.o")
         objs.append(str(obj))
-        procs.append((src, subprocess.Popen([nvcc] + ccbin + FLAGS + ["-c", str(src), "-o", str(obj)],
+        procs.append((src, subprocess.Popen([nvcc] + ccbin + FLAGS + extra + ["-c", str(src), "-o", str(obj)],
                                             stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     for src, p in procs:
         out, _ = p.communicate()
@@ -55,13 +59,14 @@ def build():
     return LIB
 
 
-def load():
+def load(variant="fast"):
     from sphericalrf_b200 import abi
-    path = build()
+    path = build(variant)
     if path is None:
         return None
     return abi.load_from(path)
 
 
 if __name__ == "__main__":
-    print(build())
+    for v in LIBS:
+        print(build(v))

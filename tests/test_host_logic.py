@@ -1,12 +1,16 @@
-"""Host-side logic above the C-ABI: configuration parsing with the reference's keys, defaults and
-error messages; the pyngp-style Testbed surface; sharding; the generators."""
+"""Host-side logic above the C-ABI: the C++ host (include/srf_testbed.hpp) through the compiled `pyngp` module --
+configuration parsing with the reference's keys, defaults and error messages, the Testbed surface, the JSON and
+msgpack readers --; sharding; the generators."""
 import math
 
 import numpy as np
 import pytest
 
 from sphericalrf_b200 import abi, sharding, synth
-from sphericalrf_b200.testbed import Testbed, config_from_json
+from sphericalrf_b200 import pyngp as ngp
+from sphericalrf_b200.testbed import config_from_json
+
+Testbed = ngp.Testbed
 
 # The structure of experiment/srf_nerfsynthetic/config/srf_lego.json (keys as the reference spells them).
 LEGO = {
@@ -47,7 +51,7 @@ def test_config_errors_use_the_reference_messages():
     bad = copy.deepcopy(LEGO); bad["samlper"]["sampling_type"] = "Linear"
     with pytest.raises(RuntimeError, match="Unknown sampling type."):
         config_from_json(bad)
-    with pytest.raises(KeyError):
+    with pytest.raises(RuntimeError, match="samlper"):
         config_from_json({"sampler": {}})         # the section is spelled "samlper"
     t = Testbed()
     with pytest.raises(RuntimeError, match="The model config must exist."):
@@ -69,7 +73,7 @@ def test_set_nerf_camera_matrix_convention():
     cam = np.array([[1, 0, 0, 0.1], [0, 1, 0, 0.2], [0, 0, 1, 0.3]], np.float32)
     t.set_nerf_camera_matrix(cam)
     want = np.array([[1, 0, 0, 0.6], [0, -1, 0, 0.7], [0, 0, -1, 0.8]], np.float32)
-    assert np.allclose(t._camera, want)
+    assert np.allclose(t.camera_matrix, want)
     m = synth.orbit_camera(0.5, 15.0, 40.0)
     assert np.allclose(np.linalg.norm(m[:, 3] - 0.5), 0.5, atol=1e-6)
     fwd = m[:, 2]                                   # camera looks along +z of the converted matrix
@@ -111,3 +115,42 @@ def test_generators_are_deterministic_and_shaped():
     assert np.abs(t.astype(np.float32)).max() <= 1e-4 + 1e-7
     grid, reach = synth.density_grid_from_blobs(cfg, a)
     assert grid.shape == (16 ** 3,) and grid.dtype == np.float32 and 0.3 < reach.mean() < 0.9
+
+
+def test_cpp_json_reader_accepts_what_the_reference_configs_contain(tmp_path):
+    text = r"""
+    // comment lines, as the shipped configs have them
+    { "samlper": { "warping_type": "ERP", /* inline */ "aabb_scale": 2000000, "use_grid": true, "grid_size": 64,
+                   "grid_distribution_type": "WarpedSpace_Exp", "near_distance": 1e-1, "far_distance": 1.0E6,
+                   "sampling_type": "Disparity", "note": "unicode \u00e9 and escapes \"\\ \n" },
+      "network": { "encoding": {"n_levels": 16, "n_features_per_level": 2, "log2_hashmap_size": 19, "base_resolution": 16},
+                   "network": {"n_neurons": 64, "n_hidden_layers": 1}, "dir_encoding": {"degree": 4},
+                   "rgb_network": {"n_neurons": 64, "n_hidden_layers": 2} },
+      "render": {}, "loss": "SmoothL1", "envmap": null, "list": [1, -2, 3.5, false] }
+    """
+    doc = ngp.parse_json(text)
+    assert doc["samlper"]["aabb_scale"] == 2000000 and doc["samlper"]["far_distance"] == 1e6 and doc["envmap"] is None
+    assert doc["list"] == [1, -2, 3.5, False] and doc["samlper"]["note"] == 'unicode \u00e9 and escapes "\\ \n'
+    c = config_from_json(doc)
+    assert c.sampling_type == abi.SAMPLING_DISPARITY and c.grid_size == 64 and abs(c.near_distance - 0.1) < 1e-7
+    p = tmp_path / "cfg.json"
+    p.write_text(text)
+    t = Testbed()
+    try:
+        t.load_model_config(str(p))            # parses, then needs a GPU for the context
+    except RuntimeError as e:
+        assert "CUDA" in str(e) or "sm_100" in str(e)
+    with pytest.raises(RuntimeError, match="JSON parse error"):
+        ngp.parse_json('{"a": }')
+
+
+def test_cpp_msgpack_round_trip():
+    doc = {"a": 1, "b": -7, "c": 3.25, "d": "text", "e": b"\x00\x01\xff", "f": [True, None, {"g": 2 ** 40}], "h": {}}
+    blob = ngp.write_msgpack(doc)
+    assert ngp.parse_msgpack(blob) == doc
+    try:
+        import msgpack
+    except ImportError:
+        return
+    assert msgpack.unpackb(blob, raw=False) == doc                           # what the C++ writer writes, a standard reader reads
+    assert ngp.parse_msgpack(msgpack.packb(doc, use_bin_type=True)) == doc   # and the other way round (compact encodings)

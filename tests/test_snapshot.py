@@ -1,4 +1,4 @@
-"""Snapshot files (.msgpack) and the `pyngp` stand-in module: structure, round trip, error messages (CPU);
+"""Snapshot files (.msgpack) and the compiled `pyngp` module: structure, round trip, error messages (CPU);
 a snapshot rendered through `pyngp.Testbed` equals the same parameters rendered through the C-ABI (GPU)."""
 import copy
 
@@ -35,12 +35,11 @@ def _scene():
 
 
 def test_snapshot_round_trip_and_structure(tmp_path):
-    import msgpack
     cfg, table, dmlp, rmlp, grid = _scene()
     for full in (False, True):
         path = tmp_path / f"s{int(full)}.msgpack"
         snapshot.write_snapshot(str(path), SMALL, grid, dmlp, rmlp, table, 0.33, (0.5, 0.25, 0.75), full_precision=full)
-        doc = msgpack.unpackb(path.read_bytes(), raw=False)
+        doc = ngp.parse_msgpack(path.read_bytes())
         assert set(SMALL) <= set(doc) and doc["samlper"]["grid_size"] == 32
         s = doc["snapshot"]
         assert s["params_type"] == ("float" if full else "__half")
@@ -57,15 +56,14 @@ def test_snapshot_round_trip_and_structure(tmp_path):
 
 
 def test_snapshot_errors(tmp_path):
-    import msgpack
     p = tmp_path / "plain.msgpack"
-    p.write_bytes(msgpack.packb(SMALL, use_bin_type=True))
+    p.write_bytes(ngp.write_msgpack(SMALL))
     with pytest.raises(RuntimeError, match="ERROR in loading snapshot."):
         snapshot.read_snapshot(str(p))
     bad = copy.deepcopy(SMALL)
     bad["snapshot"] = {"n_params": 4, "params_type": "__half", "params_binary": b"\0" * 8, "density_grid": b"",
                        "scene_scale": 1.0, "scene_offset": [0, 0, 0]}
-    p.write_bytes(msgpack.packb(bad, use_bin_type=True))
+    p.write_bytes(ngp.write_msgpack(bad))
     with pytest.raises(RuntimeError, match="shorter"):
         snapshot.read_snapshot(str(p))
     t = ngp.Testbed()
@@ -77,10 +75,14 @@ def test_snapshot_errors(tmp_path):
 
 def test_pyngp_names_match_the_reference_module():
     # internal/python_api.cu:46-82: enum members in the reference's order, exported at module level
-    assert [m.name for m in ngp.RenderMode] == ["AO", "Shade", "Normals", "Depth", "Distance", "Cost"]
-    assert [m.name for m in ngp.Activation] == ["None", "ReLU", "Logistic", "Exponential"]
-    assert [m.name for m in ngp.TonemapCurve] == ["Identity", "ACES", "Hable", "Reinhard"]
-    assert ngp.Depth is ngp.RenderMode.Depth and ngp.SRGB is ngp.ColorSpace.SRGB and ngp.SmoothL1 is ngp.LossType.SmoothL1
+    assert ngp.__file__.endswith(".so"), "pyngp is the compiled extension"
+    names = lambda e: [k for k, _ in sorted(e.__members__.items(), key=lambda kv: int(kv[1]))]
+    assert names(ngp.RenderMode) == ["AO", "Shade", "Normals", "Depth", "Distance", "Cost"]
+    assert names(ngp.Activation) == ["None", "ReLU", "Logistic", "Exponential"]
+    assert names(ngp.TonemapCurve) == ["Identity", "ACES", "Hable", "Reinhard"]
+    assert names(ngp.ColorSpace) == ["Linear", "SRGB"]
+    assert names(ngp.LossType) == ["L2", "L1", "Mape", "Smape", "SmoothL1", "LogL1", "RelativeL2"]
+    assert ngp.Depth == ngp.RenderMode.Depth and ngp.SRGB == ngp.ColorSpace.SRGB and ngp.SmoothL1 == ngp.LossType.SmoothL1
     t = ngp.Testbed()
     for name in ("load_model_config", "load_snapshot", "save_snapshot", "load_training_data", "train", "render",
                  "set_nerf_camera_matrix", "fov", "fov_xy", "background_color", "color_space", "density_activation",
@@ -117,7 +119,7 @@ def test_snapshot_renders_like_uploaded_parameters(built_lib, oracle_mod, tmp_pa
     r.upload_network(table, dmlp, rmlp)
     r.upload_density_grid(grid)
     r.update_grid_bitfield()
-    view = abi.make_view(testbed._camera, W, H, testbed.rendering_buffer.relative_focal_length, [0.5, 0.5], 0, abi.MODE_SHADE, 1.0)
+    view = abi.make_view(testbed.camera_matrix, W, H, testbed.rendering_buffer.relative_focal_length, [0.5, 0.5], 0, abi.MODE_SHADE, 1.0)
     post = abi.default_post()
     post.background_color[:] = [1.0, 1.0, 1.0, 1.0]
     post.to_srgb = 0
