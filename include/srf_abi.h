@@ -336,6 +336,30 @@ srf_status srf_render_frame(srf_ctx* ctx, const srf_view_t* view, const srf_post
 srf_status srf_render_frame_scatter(srf_ctx* ctx, const srf_view_t* view, const srf_post_t* post, float* d_image,
                                     float* d_accum, srf_frame_stats_t* stats, void* stream);
 
+/* ---- several GPUs of one box, driven by one host process ------------------------------------------------------
+   The reference renders on one GPU (internal/testbed.cu:479-606 loops over one device); its rays are independent
+   (state = RayPayload + rgba, outputs keyed by payload.idx, :476), so a frame's rays shard.  The caller creates one
+   context per device with the same configuration and uploads the same parameters and grid to each (replication).
+   srf_comm_init enables peer access from every device to the first context's device and creates one stream per
+   device.  No collective library is involved. */
+typedef struct srf_comm srf_comm;
+srf_status srf_comm_init(srf_ctx* const* ctx, uint32_t n, srf_comm** out);
+void srf_comm_destroy(srf_comm* comm);
+const char* srf_comm_last_error(const srf_comm* comm);   /* comm may be NULL: creation errors */
+
+/* Testbed::render for n_views views of one resolution, each view's rays cut into blocks of shard_rows image rows that
+   are dealt round-robin to the contexts (views[k].shard_count / shard_rank are set here).  Every context runs spp passes
+   of srf_render_frame_scatter on its own device and stream and stores its finished pixels straight into the images on
+   the first context's device (peer stores); stream events order those stores before the copy to the host.
+   d_images: device buffer on the first context's device, n_views * height * width * 4 floats, or NULL to use an
+   internal one.  h_images (may be NULL): the same, in host memory (pinned memory makes the copy asynchronous).
+   stats (may be NULL): n entries, the counters of each context's last frame.  Synchronises. */
+srf_status srf_render_frames_sharded(srf_comm* comm, const srf_view_t* views, uint32_t n_views, const srf_post_t* post,
+                                     uint32_t spp, float* d_images, float* h_images, srf_frame_stats_t* stats);
+/* Device time of the last srf_render_frames_sharded call on each context's stream (CUDA events), in ms: the time of
+   the call is their maximum.  The reference times with std::chrono around its calls (internal/testbed.cu:179-196). */
+srf_status srf_get_timings(const srf_comm* comm, float* ms_per_context, uint32_t n);
+
 /* How srf_render_frame schedules a frame.  The reference alternates rounds of <= 8 march steps per ray with
    network evaluation, compositing and compaction of finished rays (internal/testbed.cu:523-583), so samples behind
    the point where a ray saturates are never evaluated.  Here a frame runs in a few large waves: wave k takes every

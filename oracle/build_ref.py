@@ -66,7 +66,7 @@ def build(fma: bool = False, force: bool = False):
                 raise RuntimeError(f"{rel}:{first}-{last} does not hold the expected text; the reference tree differs")
             (Path(tmp) / name).write_text("\n".join(cut) + "\n")
         cxx = "/usr/bin/g++" if Path("/usr/bin/g++").exists() else "g++"
-        cmd = [cxx, "-std=c++17", "-O2", "-fPIC", "-shared", "-fno-fast-math", "-w",
+        cmd = [cxx, "-std=c++17", "-O2", "-fPIC", "-shared", "-fno-fast-math", "-fopenmp", "-w",
                "-ffp-contract=fast" if fma else "-ffp-contract=off"] + (["-mfma"] if fma else []) + [
                "-I", str(HERE / "ref_stub"), "-I", "/usr/local/cuda/include", "-I", str(REFERENCE_ROOT), "-I", tmp,
                str(HERE / "ref_harness.cpp"), "-o", str(out)]

@@ -19,6 +19,9 @@
 // Only the host loops below (the launch sequences of Testbed::render_frame, OccupancySampler::update_grid...,
 // written here from the reference's host code, cited per function) are this repository's code.
 #include "srf_cuda_on_host.h"
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 thread_local SrfThreadIndex threadIdx, blockIdx, blockDim, gridDim;
 
@@ -35,13 +38,27 @@ thread_local SrfThreadIndex threadIdx, blockIdx, blockDim, gridDim;
 
 namespace {
 
-// linear_kernel(...) of tiny-cuda-nn: one thread per element, 128 threads per block.
+// linear_kernel(...) of tiny-cuda-nn: one thread per element, 128 threads per block.  "Threads" run in index order
+// on one host thread: kernels that take slots from atomic counters then behave like a serial execution.
 template <typename K, typename... Args>
 void run_linear(K kernel, uint32_t n_elements, Args... args) {
     blockDim.x = 128; blockDim.y = blockDim.z = 1;
     for (uint32_t i = 0; i < n_elements; ++i) {
         blockIdx.x = i / 128; blockIdx.y = blockIdx.z = 0;
         threadIdx.x = i % 128; threadIdx.y = threadIdx.z = 0;
+        kernel(n_elements, args...);
+    }
+}
+
+// The same for kernels whose threads touch disjoint data (no counters): spread over the host cores with OpenMP.
+// threadIdx / blockIdx are thread_local, so every host thread has its own.
+template <typename K, typename... Args>
+void run_linear_parallel(K kernel, uint32_t n_elements, Args... args) {
+#pragma omp parallel for schedule(dynamic, 64)
+    for (int64_t i = 0; i < (int64_t)n_elements; ++i) {
+        blockDim.x = 128; blockDim.y = blockDim.z = 1;
+        blockIdx.x = (uint32_t)i / 128; blockIdx.y = blockIdx.z = 0;
+        threadIdx.x = (uint32_t)i % 128; threadIdx.y = threadIdx.z = 0;
         kernel(n_elements, args...);
     }
 }
@@ -109,6 +126,18 @@ Eigen::Matrix<float, 3, 4> camera_of(const float* row_major12) {
 }  // namespace
 
 extern "C" {
+
+// OpenMP threads of the per-ray kernels (n <= 0: one per available core); returns the count in force.
+int refh_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n <= 0) n = omp_get_num_procs();
+    omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
 
 // The field a frame queries: Coordinate records (n x 7 floats) -> n x 4 halves (r, g, b, sigma raw).  Same
 // signature as the oracle's srfo_network_inference, so that function can be passed directly.
@@ -245,7 +274,7 @@ int refh_render_frame(const srf_config_t* cfg, const srf_view_t* view, const srf
     // generate_rays_from_camera_matrix
     run_image(init_rays_with_payload_kernel_nerf, (int)view->width, (int)view->height, resolution, focal, pp, cam, view->spp_index,
               s.snap_rendering, s.aabb, pay[0].data());
-    run_linear(advance_pos_nerf, n_pixels, view->spp_index, pay[0].data(), s.warping_type, s.aabb, s.n_grid_size, s.n_cascades,
+    run_linear_parallel(advance_pos_nerf, n_pixels, view->spp_index, pay[0].data(), s.warping_type, s.aabb, s.n_grid_size, s.n_cascades,
                s.griddist_type, s.use_grid ? bitfield : (const uint8_t*)nullptr, s.n_max_steps, s.cone_angle_constant,
                s.min_cone_stepsize, s.max_cone_stepsize, s.near_distance, s.far_distance, s.sampling_type);
     // rays that never entered the box carry no pixel index; give them one so the per-pixel taps stay aligned
@@ -271,7 +300,7 @@ int refh_render_frame(const srf_config_t* cfg, const srf_view_t* view, const srf
         if (n_alive == 0) break;
         const uint32_t n_steps = tcnn::clamp(n_pixels / n_alive, kMinSteps, kMaxSteps);
         if (getenv("SRF_REF_DEBUG")) fprintf(stderr, "round %llu alive %u n_steps %u offset %u\n", (unsigned long long)n_rounds, n_alive, n_steps, i_steps_offset);
-        run_linear(generate_coords_from_rays_regularly_kernel, n_alive, n_steps, s.warping_type, s.aabb, s.n_grid_size, s.n_cascades,
+        run_linear_parallel(generate_coords_from_rays_regularly_kernel, n_alive, n_steps, s.warping_type, s.aabb, s.n_grid_size, s.n_cascades,
                    s.griddist_type, s.use_grid ? bitfield : (const uint8_t*)nullptr, s.n_max_steps, s.cone_angle_constant,
                    s.min_cone_stepsize, s.max_cone_stepsize, s.near_distance, s.far_distance, s.sampling_type, cur_p.data(),
                    (Coordinate*)coords.data());
@@ -287,7 +316,7 @@ int refh_render_frame(const srf_config_t* cfg, const srf_view_t* view, const srf
         }
         const uint32_t n_net = tcnn::next_multiple(n_alive * n_steps, BATCH_SIZE_MULTIPLE);
         if (field(field_cfg, field_model, coords.data(), n_net, rgbsigma.data()) != 0) return 2;
-        run_linear(volume_rendering_kernel, n_alive, n_steps, i_steps_offset, cur_p.data(), cur_c.data(), (const Coordinate*)coords.data(),
+        run_linear_parallel(volume_rendering_kernel, n_alive, n_steps, i_steps_offset, cur_p.data(), cur_c.data(), (const Coordinate*)coords.data(),
                    (const precision_t*)rgbsigma.data(), padded_output_width, (EActivation)cfg->density_activation,
                    (EActivation)cfg->rgb_activation, render_mode, s.warping_type, s.aabb, s.n_cascades, s.min_cone_stepsize, cam,
                    view->depth_scale, cfg->transmittance_threshold);

@@ -8,25 +8,25 @@ struct pcg32 {
     static constexpr uint64_t kDefaultState = 0x853c49e6748fea9bULL, kDefaultStream = 0xda3e39cb94b95bdbULL,
                               kMult = 0x5851f42d4c957f2dULL;
     uint64_t state, inc;
-    pcg32() : state(kDefaultState), inc(kDefaultStream) {}
-    pcg32(uint64_t initstate, uint64_t initseq = 1u) { seed(initstate, initseq); }
-    void seed(uint64_t initstate, uint64_t initseq = 1) {
+    SRF_TCNN_HD pcg32() : state(kDefaultState), inc(kDefaultStream) {}
+    SRF_TCNN_HD pcg32(uint64_t initstate, uint64_t initseq = 1u) { seed(initstate, initseq); }
+    SRF_TCNN_HD void seed(uint64_t initstate, uint64_t initseq = 1) {
         state = 0u; inc = (initseq << 1u) | 1u;
         next_uint(); state += initstate; next_uint();
     }
-    uint32_t next_uint() {
+    SRF_TCNN_HD uint32_t next_uint() {
         const uint64_t oldstate = state;
         state = oldstate * kMult + inc;
         const uint32_t xorshifted = (uint32_t)(((oldstate >> 18u) ^ oldstate) >> 27u);
         const uint32_t rot = (uint32_t)(oldstate >> 59u);
         return (xorshifted >> rot) | (xorshifted << ((~rot + 1u) & 31));
     }
-    float next_float() {
+    SRF_TCNN_HD float next_float() {
         union { uint32_t u; float f; } x;
         x.u = (next_uint() >> 9) | 0x3f800000u;
         return x.f - 1.0f;
     }
-    void advance(int64_t delta_ = (1ll << 32)) {
+    SRF_TCNN_HD void advance(int64_t delta_ = (1ll << 32)) {
         uint64_t cur_mult = kMult, cur_plus = inc, acc_mult = 1u, acc_plus = 0u;
         uint64_t delta = (uint64_t)delta_;
         while (delta > 0) {

@@ -840,6 +840,16 @@ int srfo_num_threads(void) {
 #endif
 }
 
+/* Sets the OpenMP thread count (launchers such as torchrun export OMP_NUM_THREADS=1); n <= 0: one per available core. */
+void srfo_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n <= 0) n = omp_get_num_procs();
+    omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int srfo_hashgrid_layout(const srf_config_t* cfg, uint32_t* offsets, uint32_t* resolutions, float* scales) {
     const Cfg g = resolve(cfg);
     const GridLayout L = grid_layout(g);

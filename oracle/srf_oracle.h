@@ -32,6 +32,7 @@ typedef struct srfo_model_t {
 typedef struct srfo_rng_t { uint64_t state, inc; } srfo_rng_t;
 
 int srfo_num_threads(void);
+void srfo_set_num_threads(int n);   /* n <= 0: one per available core */
 int srfo_hashgrid_layout(const srf_config_t* cfg, uint32_t* offsets, uint32_t* resolutions, float* scales);
 int srfo_eval_math(int op, const float* a, const float* b, float* out, size_t n);
 int srfo_warp_position(const srf_config_t* cfg, const float* pos, float* out, size_t n, int inverse);

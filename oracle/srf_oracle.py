@@ -238,6 +238,15 @@ def num_threads():
     return int(lib().srfo_num_threads())
 
 
+def set_num_threads(n=0):
+    """OpenMP threads of the oracle (0: one per core this process may run on)."""
+    import os
+    if n <= 0:
+        n = len(os.sched_getaffinity(0))
+    lib().srfo_set_num_threads(C.c_int(n))
+    return num_threads()
+
+
 def _host_views(views: dict):
     """srf_train_views_t with host pointers from dict(n_images, width, height, focal_length, principal_point,
     xforms (n,12) float32 column-major, images (n,H,W,4) float16 or None, sampling_probability (n,H,W) float16 or

@@ -44,6 +44,14 @@ def _p(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
 
 
+def set_num_threads(n=0):
+    """OpenMP threads of the per-ray kernels (0: one per core this process may run on); returns the count in force."""
+    import os
+    if n <= 0:
+        n = len(os.sched_getaffinity(0))
+    return int(lib().refh_set_num_threads(C.c_int(n)))
+
+
 def ld_random_val(index, seed, dim, fma=False):
     return np.float32(lib(fma).refh_ld_random_val(index, seed, dim))
 

@@ -194,6 +194,11 @@ SYMBOLS = {
     "srf_dump_samples": (C.c_int, [_ctx, _P(View), C.c_uint64, C.c_uint64, C.c_uint64, _vp, _vp, _vp, _vp,
                                    _P(C.c_uint64)]),
     "srf_check_errors": (C.c_int, [_ctx, _vp, _P(C.c_uint32)]),
+    "srf_comm_init": (C.c_int, [_P(_ctx), C.c_uint32, _P(C.c_void_p)]),
+    "srf_comm_destroy": (None, [C.c_void_p]),
+    "srf_comm_last_error": (C.c_char_p, [C.c_void_p]),
+    "srf_render_frames_sharded": (C.c_int, [C.c_void_p, _P(View), C.c_uint32, _P(Post), C.c_uint32, _vp, _vp, _P(FrameStats)]),
+    "srf_get_timings": (C.c_int, [C.c_void_p, _P(C.c_float), C.c_uint32]),
     "srf_reserve": (C.c_int, [_ctx, C.c_uint64]),
     "srf_set_wave_schedule": (C.c_int, [_ctx, _vp, C.c_uint32]),
     "srf_sampler_init": (C.c_int, [_ctx, _P(TrainViews), C.c_int, C.c_uint64, _vp]),

@@ -1097,6 +1097,171 @@ srf_status srf_render(srf_ctx* ctx, const srf_view_t* view, const srf_post_t* po
     return SRF_OK;
 }
 
+// ---- several GPUs of one box, one host process ---------------------------------------------------------------------------
+// Rays shard, everything else is replicated: the caller creates one context per device and uploads the same arrays to
+// each.  A frame's row blocks are dealt round-robin to the contexts; every context's output stage stores its pixels straight
+// into the image on the first context's device (plain 16-byte peer stores over NVLink from k_composite_rays; no collective,
+// no staging tile).  Hand-off is by stream events: every device's stream records an event when its part is enqueued, the
+// first device's stream waits for all of them before the image is copied out.  No device-side waiting anywhere.
+struct srf_comm {
+    std::vector<srf_ctx*> ctx;
+    std::vector<cudaStream_t> stream;
+    std::vector<cudaEvent_t> begin, done;
+    cudaEvent_t go = nullptr;                 // recorded on the first device; every stream starts after it
+    float* d_images = nullptr;                // on the first device, when the caller passes none
+    size_t d_images_bytes = 0;
+    std::vector<float> ms;                    // device time of the last call, per context
+    std::string err;
+};
+
+static srf_status comm_fail(srf_comm* c, srf_status st, const std::string& msg) {
+    if (c) c->err = msg;
+    g_create_error = msg;
+    return st;
+}
+
+srf_status srf_comm_init(srf_ctx* const* ctx, uint32_t n, srf_comm** out) {
+    if (!out) return comm_fail(nullptr, SRF_ERR_ARG, "out is NULL");
+    *out = nullptr;
+    if (!ctx || n == 0) return comm_fail(nullptr, SRF_ERR_ARG, "no contexts");
+    for (uint32_t i = 0; i < n; ++i) {
+        if (!ctx[i]) return comm_fail(nullptr, SRF_ERR_ARG, "a context is NULL");
+        for (uint32_t j = 0; j < i; ++j)
+            if (ctx[j]->device == ctx[i]->device) return comm_fail(nullptr, SRF_ERR_ARG, "two contexts share a device: one context per GPU");
+        if (memcmp(&ctx[i]->cfg, &ctx[0]->cfg, sizeof(srf_config_t)) != 0)
+            return comm_fail(nullptr, SRF_ERR_ARG, "the contexts were created with different configurations");
+    }
+    srf_comm* c = new (std::nothrow) srf_comm();
+    if (!c) return comm_fail(nullptr, SRF_ERR_CUDA, "out of host memory");
+    c->ctx.assign(ctx, ctx + n);
+    c->stream.assign(n, nullptr); c->begin.assign(n, nullptr); c->done.assign(n, nullptr); c->ms.assign(n, 0.f);
+    const int root = ctx[0]->device;
+    for (uint32_t i = 0; i < n; ++i) {
+        DeviceGuard guard(ctx[i]->device);
+        cudaError_t e = cudaSuccess;
+        if (i > 0) {
+            int can = 0;
+            e = cudaDeviceCanAccessPeer(&can, ctx[i]->device, root);
+            if (e == cudaSuccess && !can) { srf_comm_destroy(c); return comm_fail(nullptr, SRF_ERR_CUDA, "a device cannot access the first device's memory (no peer access)"); }
+            if (e == cudaSuccess) {
+                e = cudaDeviceEnablePeerAccess(root, 0);
+                if (e == cudaErrorPeerAccessAlreadyEnabled) { cudaGetLastError(); e = cudaSuccess; }
+            }
+        }
+        if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->stream[i], cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaEventCreate(&c->begin[i]);
+        if (e == cudaSuccess) e = cudaEventCreate(&c->done[i]);
+        if (e == cudaSuccess && i == 0) e = cudaEventCreateWithFlags(&c->go, cudaEventDisableTiming);
+        if (e != cudaSuccess) {
+            const std::string msg = std::string("srf_comm_init: ") + cudaGetErrorString(e);
+            srf_comm_destroy(c);
+            return comm_fail(nullptr, SRF_ERR_CUDA, msg);
+        }
+    }
+    *out = c;
+    return SRF_OK;
+}
+
+void srf_comm_destroy(srf_comm* c) {
+    if (!c) return;
+    for (size_t i = 0; i < c->ctx.size(); ++i) {
+        DeviceGuard guard(c->ctx[i]->device);
+        if (c->stream[i]) { cudaStreamSynchronize(c->stream[i]); cudaStreamDestroy(c->stream[i]); }
+        if (c->begin[i]) cudaEventDestroy(c->begin[i]);
+        if (c->done[i]) cudaEventDestroy(c->done[i]);
+        if (i == 0) {
+            if (c->go) cudaEventDestroy(c->go);
+            if (c->d_images) cudaFree(c->d_images);
+        }
+    }
+    delete c;
+}
+
+const char* srf_comm_last_error(const srf_comm* c) { return c ? c->err.c_str() : g_create_error.c_str(); }
+
+srf_status srf_render_frames_sharded(srf_comm* c, const srf_view_t* views, uint32_t n_views, const srf_post_t* post, uint32_t spp,
+                                     float* d_images, float* h_images, srf_frame_stats_t* stats) {
+    if (!c || !views || n_views == 0) return comm_fail(c, SRF_ERR_ARG, "no views");
+    if (spp == 0) return comm_fail(c, SRF_ERR_ARG, "spp must be positive");
+    const uint32_t n = (uint32_t)c->ctx.size();
+    const size_t px = (size_t)views[0].width * views[0].height;
+    for (uint32_t k = 0; k < n_views; ++k)
+        if (views[k].width != views[0].width || views[k].height != views[0].height)
+            return comm_fail(c, SRF_ERR_ARG, "the views of one call share a resolution");
+    const size_t bytes = px * n_views * sizeof(float4);
+    srf_ctx* root = c->ctx[0];
+    if (!d_images) {
+        DeviceGuard guard(root->device);
+        if (bytes > c->d_images_bytes) {
+            if (c->d_images) cudaFree(c->d_images);
+            c->d_images = nullptr; c->d_images_bytes = 0;
+            if (cudaMalloc((void**)&c->d_images, bytes) != cudaSuccess) { cudaGetLastError(); return comm_fail(c, SRF_ERR_CUDA, "cannot allocate the image buffer"); }
+            c->d_images_bytes = bytes;
+        }
+        d_images = c->d_images;
+    }
+    {   // every stream starts after this point of the first device's stream
+        DeviceGuard guard(root->device);
+        if (cudaEventRecord(c->go, c->stream[0]) != cudaSuccess) return comm_fail(c, SRF_ERR_CUDA, "cudaEventRecord failed");
+    }
+    for (uint32_t r = 0; r < n; ++r) {
+        srf_ctx* ctx = c->ctx[r];
+        DeviceGuard guard(ctx->device);
+        if (r > 0 && cudaStreamWaitEvent(c->stream[r], c->go, 0) != cudaSuccess) return comm_fail(c, SRF_ERR_CUDA, "cudaStreamWaitEvent failed");
+        cudaEventRecord(c->begin[r], c->stream[r]);
+        for (uint32_t k = 0; k < n_views; ++k) {
+            srf_view_t v = views[k];
+            v.shard_rows = v.shard_rows ? v.shard_rows : 8;
+            v.shard_count = n;
+            v.shard_rank = r;
+            const uint64_t n_local = shard_rows_total(v) * v.width;
+            srf_status st = ensure(ctx, ctx->img_accum, (size_t)std::max<uint64_t>(n_local, 1) * sizeof(float4));
+            if (st != SRF_OK) return comm_fail(c, st, ctx->err);
+            for (uint32_t i = 0; i < spp; ++i) {
+                v.spp_index = i;
+                st = srf_render_frame_scatter(ctx, &v, post, d_images + (size_t)k * px * 4, (float*)ctx->img_accum.p, nullptr, c->stream[r]);
+                if (st != SRF_OK) return comm_fail(c, st, ctx->err);
+            }
+        }
+        cudaEventRecord(c->done[r], c->stream[r]);
+    }
+    {   // the image is complete when every device's part is: the first device's stream waits for all of them
+        DeviceGuard guard(root->device);
+        for (uint32_t r = 1; r < n; ++r)
+            if (cudaStreamWaitEvent(c->stream[0], c->done[r], 0) != cudaSuccess) return comm_fail(c, SRF_ERR_CUDA, "cudaStreamWaitEvent failed");
+        if (h_images && cudaMemcpyAsync(h_images, d_images, bytes, cudaMemcpyDeviceToHost, c->stream[0]) != cudaSuccess)
+            return comm_fail(c, SRF_ERR_CUDA, "copy of the image to the host failed");
+        const cudaError_t e = cudaStreamSynchronize(c->stream[0]);
+        if (e != cudaSuccess) return comm_fail(c, SRF_ERR_CUDA, std::string("srf_render_frames_sharded: ") + cudaGetErrorString(e));
+    }
+    for (uint32_t r = 0; r < n; ++r) {
+        srf_ctx* ctx = c->ctx[r];
+        DeviceGuard guard(ctx->device);
+        cudaEventSynchronize(c->done[r]);
+        cudaEventElapsedTime(&c->ms[r], c->begin[r], c->done[r]);
+        uint32_t flags = 0;
+        const srf_status st = check_error_flags(ctx, c->stream[r], &flags);
+        if (stats) {
+            // counters of the context's last frame (its shard of the last view and pass)
+            memset(&stats[r], 0, sizeof(srf_frame_stats_t));
+            if (cudaMemcpy(ctx->h_counters, ctx->d_counters, offsetof(FrameCounters, error_flags), cudaMemcpyDeviceToHost) == cudaSuccess) {
+                stats[r].n_rays_alive = ctx->h_counters->n_alive; stats[r].n_march_steps = ctx->h_counters->n_march_steps;
+                stats[r].n_samples = ctx->h_counters->n_samples; stats[r].n_samples_composited = ctx->h_counters->n_composited;
+                stats[r].n_rays_hit = ctx->h_counters->n_hit;
+            }
+            stats[r].error_flags = flags;
+        }
+        if (st != SRF_OK) return comm_fail(c, st, ctx->err);
+    }
+    return SRF_OK;
+}
+
+srf_status srf_get_timings(const srf_comm* c, float* ms_per_context, uint32_t n) {
+    if (!c || !ms_per_context) return SRF_ERR_ARG;
+    for (uint32_t r = 0; r < n && r < c->ms.size(); ++r) ms_per_context[r] = c->ms[r];
+    return SRF_OK;
+}
+
 srf_status srf_dump_samples(srf_ctx* ctx, const srf_view_t* view, uint64_t ray_first, uint64_t ray_count, uint64_t capacity,
                             uint32_t* h_counts, float* h_pos_dt, uint32_t* h_ordinal, uint32_t* h_cell, uint64_t* n_total) {
     if (!ctx || !h_counts) return SRF_ERR_ARG;

@@ -248,6 +248,58 @@ class Renderer:
         return counts, pos_dt[:n], ordinal[:n], cell[:n]
 
 
+class Comm:
+    """srf_comm over several Renderers of one process (one per GPU, same configuration and uploads)."""
+
+    def __init__(self, renderers):
+        self.renderers = list(renderers)
+        self.lib = self.renderers[0].lib
+        arr = (C.c_void_p * len(self.renderers))(*[r.ctx for r in self.renderers])
+        self.comm = C.c_void_p()
+        st = self.lib.srf_comm_init(arr, len(self.renderers), C.byref(self.comm))
+        if st != abi.OK:
+            msg = self.lib.srf_comm_last_error(None)
+            raise abi.SrfError(st, msg.decode() if msg else "")
+
+    def close(self):
+        if getattr(self, "comm", None):
+            self.lib.srf_comm_destroy(self.comm)
+            self.comm = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def render(self, views, post, spp=1, host_images=None, want_stats=False, device_images=None):
+        """srf_render_frames_sharded: images (n_views, H, W, 4) float32 in host memory (a pinned torch tensor may be
+        passed as `host_images`; it is filled and returned as numpy)."""
+        n = len(views)
+        arr = (abi.View * n)(*views)
+        h, w = views[0].height, views[0].width
+        if host_images is False:                       # leave the images on the first GPU
+            out, hp = None, None
+        elif host_images is None:
+            out = np.zeros((n, h, w, 4), np.float32)
+            hp = _np_ptr(out)
+        else:
+            out = host_images
+            hp = C.c_void_p(host_images.data_ptr())
+        stats = (abi.FrameStats * len(self.renderers))() if want_stats else None
+        st = self.lib.srf_render_frames_sharded(self.comm, arr, n, C.byref(post), spp,
+                                                None if device_images is None else C.c_void_p(device_images.data_ptr()), hp, stats)
+        if st != abi.OK:
+            msg = self.lib.srf_comm_last_error(self.comm)
+            raise abi.SrfError(st, msg.decode() if msg else "")
+        return (out, [s.as_dict() for s in stats]) if want_stats else out
+
+    def timings(self):
+        ms = (C.c_float * len(self.renderers))()
+        self.lib.srf_get_timings(self.comm, ms, len(self.renderers))
+        return [float(x) for x in ms]
+
+
 def eval_math(op, a, b=None, device=0):
     lib = abi.load()
     a = np.ascontiguousarray(a, np.float32)
