@@ -518,6 +518,73 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_refgpu(args):
+    """The reference's own CUDA kernels (ray generation, marching, compaction, compositing, shading, accumulation,
+    tonemapping; compiled for sm_100a from its sources by baseline/build_refgpu.py) in the reference's host loop on one
+    GPU, with this library's srf_network_inference where the reference calls tiny-cuda-nn.  A same-GPU baseline for the
+    frame time; not the library, and not the reference's network."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    from baseline import refgpu
+    from sphericalrf_b200 import abi
+    from sphericalrf_b200.testbed import Renderer
+    if not refgpu.available():
+        print(json.dumps({"impl": "refgpu", "unavailable": "baseline/_ref/libsrf_refgpu.so is missing and the reference is not mounted to build it"}), flush=True)
+        return
+    sc = build_scene()
+    if sc["cfg"].field_type != abi.FIELD_NETWORK:
+        print(json.dumps({"impl": "refgpu", "unavailable": "the analytic stand-in field has no counterpart in the reference's pipeline"}), flush=True)
+        return
+    r = Renderer(sc["cfg"], 0)
+    upload_scene(r, sc)
+    ref = refgpu.RefGpu(r)
+    dev = torch.device("cuda", 0)
+    n_views = FIXED_VIEWS.get(WORKLOAD, 1)
+    cams = sc["cameras"]
+    views = [abi.make_view(cams[k % len(cams)], WIDTH, HEIGHT, sc["rfl"]) for k in range(n_views)]
+    post = abi.default_post()
+    out = torch.zeros((HEIGHT * WIDTH, 4), device=dev); acc = torch.zeros((HEIGHT * WIDTH, 4), device=dev)
+    host = torch.zeros((HEIGHT * WIDTH, 4)).pin_memory()
+
+    def step(copy):
+        ms = 0.0
+        for v in views:
+            ref.render_frame_device(v, post, out, acc)
+            ms += ref.last_ms()
+            if copy:
+                host.copy_(out, non_blocking=True); torch.cuda.synchronize()
+        return ms
+
+    for _ in range(args.warmup):
+        step(False)
+    sampler = ClockSampler(0); sampler.start()
+    ms = sum(step(False) for _ in range(args.steps))
+    clocks = sampler.stop()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step(True)
+    wall = time.perf_counter() - t0
+    rays = WIDTH * HEIGHT * n_views * args.steps
+    import ctypes as Cc
+    rounds = int(refgpu.lib().refgpu_last_rounds(ref.ctx)); slots = int(refgpu.lib().refgpu_last_network_samples(ref.ctx))
+    line = {
+        "impl": "refgpu", "metric": "render throughput", "value": rays / (ms * 1e-3) / 1e6, "unit": "Mrays/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "strong" if WORKLOAD in FIXED_VIEWS else "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": workload_name(), "frames_per_step": n_views, "rays_per_frame": WIDTH * HEIGHT,
+                   "pipeline": "the reference's CUDA kernels and host loop (one alive-counter read-back per round, <= 8 samples per ray "
+                               "per round) + this library's network stage entry in place of tiny-cuda-nn",
+                   "rounds_per_frame": rounds, "network_slots_per_frame": slots},
+        "frames_per_s": n_views * args.steps / (ms * 1e-3), "clocks": clocks,
+        "e2e": {"value": rays / wall / 1e6, "unit": "Mrays/s", "h2d_bytes_per_step": int(C.sizeof(abi.View) + C.sizeof(abi.Post)) * n_views,
+                "d2h_bytes_per_step": int(HEIGHT * WIDTH * 16 * n_views)},
+        "gpu_launches": None,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def run_single_process(args):
     """N GPUs of the box driven by this one process through the C-ABI's srf_comm_init / srf_render_frames_sharded:
     no torch.distributed, no NCCL.  Device time of a step = the slowest GPU's stream (CUDA events inside the library)."""
@@ -577,7 +644,8 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "refgpu"],
+                    help="ours: the library; reference: the reference's CPU-side logic on the host cores; refgpu: the reference's CUDA kernels on one GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"], help="N > 1: how tiles reach rank 0")
     ap.add_argument("--single-process", action="store_true", help="drive --gpus N devices from this one process (srf_comm), no torchrun")
@@ -595,6 +663,8 @@ def main():
         WIDTH, HEIGHT = (int(x) for x in args.res.lower().split("x"))
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "refgpu":
+        run_refgpu(args)
     elif args.single_process:
         run_single_process(args)
     else:

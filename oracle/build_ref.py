@@ -47,6 +47,17 @@ def lib_path(fma: bool = False) -> Path:
     return OUT_DIR / ("libsrf_ref_fma.so" if fma else "libsrf_ref.so")
 
 
+def extract(tmp: Path) -> None:
+    """Writes the kernel extracts (*.inc) of the mounted reference into the temporary directory `tmp`."""
+    for rel, first, last, name in RANGES:
+        lines = (REFERENCE_ROOT / "internal" / rel).read_text().splitlines()
+        cut = lines[first - 1:last]
+        head, tail = EXPECT[name]
+        if not cut or not cut[0].strip().startswith(head) or cut[-1].strip() != tail:
+            raise RuntimeError(f"{rel}:{first}-{last} does not hold the expected text; the reference tree differs")
+        (tmp / name).write_text("\n".join(cut) + "\n")
+
+
 def build(fma: bool = False, force: bool = False):
     """Returns the path of the shared object, or None when the reference is not mounted and no earlier build exists."""
     out = lib_path(fma)
@@ -58,13 +69,7 @@ def build(fma: bool = False, force: bool = False):
         return out
     OUT_DIR.mkdir(exist_ok=True)
     with tempfile.TemporaryDirectory(prefix="srf_ref_") as tmp:
-        for rel, first, last, name in RANGES:
-            lines = (REFERENCE_ROOT / "internal" / rel).read_text().splitlines()
-            cut = lines[first - 1:last]
-            head, tail = EXPECT[name]
-            if not cut or not cut[0].strip().startswith(head) or cut[-1].strip() != tail:
-                raise RuntimeError(f"{rel}:{first}-{last} does not hold the expected text; the reference tree differs")
-            (Path(tmp) / name).write_text("\n".join(cut) + "\n")
+        extract(Path(tmp))
         cxx = "/usr/bin/g++" if Path("/usr/bin/g++").exists() else "g++"
         cmd = [cxx, "-std=c++17", "-O2", "-fPIC", "-shared", "-fno-fast-math", "-fopenmp", "-w",
                "-ffp-contract=fast" if fma else "-ffp-contract=off"] + (["-mfma"] if fma else []) + [
