@@ -74,6 +74,9 @@ struct srf_ctx {
     DevBuf pos_dt, sample_ray, rgbs;
     DevBuf pool_pos, pool_shaded, chunk_ray, chunk_next, ray_head;   // paged frame path
     uint32_t* d_chunk_cursor = nullptr;
+    unsigned int* d_ticket = nullptr;        // last-block ticket of the fused refresh (zero between launches)
+    bool fused_refresh = true;               // SRF_B200_FUSED_REFRESH=0 keeps the multi-launch path (tests compare the two)
+    bool grid_may_hold_masked_cells = false; // a negative cell was uploaded or written by the never-seen mask
     DevBuf img_out, img_accum;
     FrameCounters* d_counters = nullptr;
     FrameCounters* h_counters = nullptr;     // pinned
@@ -349,6 +352,7 @@ srf_status report_error_flags(srf_ctx* ctx, uint32_t flags, cudaStream_t s) {
     if (flags & 1u) return fail(ctx, SRF_ERR_TIMEOUT, "a ray hit the march loop's iteration bound");
     if (flags & 2u) return fail(ctx, SRF_ERR_TIMEOUT, "a wait on the tensor-core commit barrier expired");
     if (flags & 4u) return fail(ctx, SRF_ERR_CAPACITY, "the sample pool ran out of chunks");
+    if (flags & 8u) return fail(ctx, SRF_ERR_STATE, "the fused grid refresh met a masked cell (the grid was changed behind the context)");
     return fail(ctx, SRF_ERR_CUDA, "unknown device error flag");
 }
 
@@ -498,6 +502,9 @@ srf_status srf_create(const srf_config_t* cfg, int device, srf_ctx** out) {
     CK_CREATE(cudaMalloc((void**)&ctx->d_counters, sizeof(FrameCounters)));
     CK_CREATE(cudaMemset(ctx->d_counters, 0, sizeof(FrameCounters)));
     CK_CREATE(cudaMalloc((void**)&ctx->d_chunk_cursor, sizeof(uint32_t)));
+    CK_CREATE(cudaMalloc((void**)&ctx->d_ticket, sizeof(unsigned int)));
+    CK_CREATE(cudaMemset(ctx->d_ticket, 0, sizeof(unsigned int)));
+    if (const char* e = getenv("SRF_B200_FUSED_REFRESH")) ctx->fused_refresh = std::string(e) != "0";
     CK_CREATE(cudaMallocHost((void**)&ctx->h_counters, sizeof(FrameCounters)));
     for (int i = 0; i < 8; ++i) CK_CREATE(cudaEventCreate(&ctx->ev[i]));
 #undef CK_CREATE
@@ -515,7 +522,7 @@ void srf_destroy(srf_ctx* ctx) {
                     ctx->w_density, ctx->w_rgb, ctx->skip_shell, ctx->skip_yz, ctx->train_flags.p, ctx->train_rank.p, ctx->loss_rgb.p, ctx->ray_sh.p, ctx->ray_ordinal.p, ctx->ray_total.p, ctx->ray_rgba.p, ctx->ray_ncomp.p, ctx->blobs, ctx->cmap, ctx->d_counters, ctx->ray_dir_t.p, ctx->ray_end.p,
                     ctx->counts.p, ctx->offsets.p, ctx->scan_scratch.p, ctx->pos_dt.p, ctx->sample_ray.p, ctx->rgbs.p,
                     ctx->img_out.p, ctx->img_accum.p, ctx->pool_pos.p, ctx->pool_shaded.p, ctx->chunk_ray.p, ctx->chunk_next.p,
-                    ctx->ray_head.p, ctx->d_chunk_cursor};
+                    ctx->ray_head.p, ctx->d_chunk_cursor, ctx->d_ticket};
     for (void* p : ptrs) if (p) cudaFree(p);
     if (ctx->h_counters) cudaFreeHost(ctx->h_counters);
     if (ctx->h_coarse) cudaFreeHost(ctx->h_coarse);
@@ -582,6 +589,9 @@ srf_status srf_upload_density_grid(srf_ctx* ctx, const float* h, size_t n, void*
     DeviceGuard guard(ctx->device);
     SRF_CK(ctx, cudaMemcpyAsync(ctx->grid, h, n * sizeof(float), cudaMemcpyHostToDevice, (cudaStream_t)stream));
     SRF_CK(ctx, cudaStreamSynchronize((cudaStream_t)stream));
+    bool masked = false;
+    for (size_t i = 0; i < n && !masked; ++i) masked = !(h[i] > -0.01f);
+    ctx->grid_may_hold_masked_cells = masked;
     return SRF_OK;
 }
 srf_status srf_download_density_grid(srf_ctx* ctx, float* h, size_t n, void* stream) {
@@ -663,6 +673,22 @@ srf_status srf_refresh_grid(srf_ctx* ctx, uint32_t training_step, void* stream) 
     const uint32_t total = ctx->g.cells * ctx->g.n_cascades;
     const uint32_t n_uniform = training_step >= 256 ? total / 4 : total;          // testbed.cu:206
     const uint32_t n_nonuniform = training_step >= 256 ? total / 4 : 0;           // testbed.cu:207
+    // One kernel for sample -> encode -> MLP -> splat -> max-decay -> mean, one for the bits, where the cell map is a
+    // bijection with a single writer per cell: every cell sampled once, one cascade, power-of-two cell count, no cell
+    // masked as never seen (a masked cell's sample is redirected to another cell).
+    const bool fused = ctx->fused_refresh && n_nonuniform == 0 && ctx->g.n_cascades == 1 && (ctx->g.cells & (ctx->g.cells - 1u)) == 0 &&
+                       !ctx->grid_may_hold_masked_cells;
+    if (fused) {
+        launch_refresh_fused(ctx->g, ctx->net, ctx->table, ctx->refresh_w, ctx->grid, ctx->refresh_step, ctx->rng, (float)-0.01,
+                             ctx->cfg.aabb_scale, ctx->cfg.ema_decay, ctx->partial_a, ctx->partial_b, ctx->mean, ctx->d_ticket, ctx->bits,
+                             ctx->min_optical_thickness, ctx->skip_capable ? ctx->skip_shell : nullptr,
+                             ctx->skip_capable ? ctx->skip_yz : nullptr, &ctx->d_counters->error_flags, s);
+        host_pcg_advance(ctx->rng, 1ull << 32);                                    // rng.advance() after each of the two
+        host_pcg_advance(ctx->rng, 1ull << 32);                                    // sampling launches, :1009,1028
+        ++ctx->refresh_step;
+        SRF_CK(ctx, cudaGetLastError());
+        return SRF_OK;
+    }
     SRF_CK(ctx, cudaMemsetAsync(ctx->grid_current, 0, (size_t)total * sizeof(float), s));   // occupancy_sampler.cu:1039
     launch_refresh_sample(ctx->g, ctx->net, ctx->table, ctx->refresh_w, ctx->grid, ctx->grid_current, n_uniform,
                           ctx->refresh_step, ctx->rng, (float)-0.01, ctx->cfg.aabb_scale, s);
@@ -708,8 +734,10 @@ srf_status srf_sampler_init(srf_ctx* ctx, const srf_train_views_t* views, int in
         if (st != SRF_OK) return st;
         launch_mark_untrained(ctx->g, ctx->cfg.aabb_scale, tv, ctx->grid, s);
         SRF_CK(ctx, cudaGetLastError());
+        ctx->grid_may_hold_masked_cells = true;
     } else {
         SRF_CK(ctx, cudaMemsetAsync(ctx->grid, 0, total * sizeof(float), s));
+        ctx->grid_may_hold_masked_cells = false;
     }
     return SRF_OK;
 }

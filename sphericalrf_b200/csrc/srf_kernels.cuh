@@ -141,6 +141,11 @@ struct RefreshWeights { float w1[64 * 32]; float w2[64]; };
 void launch_refresh_sample(const DevCfg& g, const NetMeta& net, const __half* table, const RefreshWeights& w,
                            const float* grid, float* grid_current, uint32_t n_elements, uint32_t step, RefreshRng rng,
                            float thresh, uint32_t aabb_scale, cudaStream_t stream);
+// The whole refresh in two launches when every cell is sampled once, there is one cascade and no cell is masked.
+void launch_refresh_fused(const DevCfg& g, const NetMeta& net, const __half* table, const RefreshWeights& w, float* grid,
+                          uint32_t step, RefreshRng rng, float thresh, uint32_t aabb_scale, float decay, float* partial_a,
+                          float* partial_b, float* mean, unsigned int* ticket, uint8_t* bits, float min_optical_thickness,
+                          uint32_t* skip_shell, uint32_t* skip_yz, unsigned int* error_flags, cudaStream_t stream);
 // Max-decay of every cell (when do_decay) and the mean of max(v,0) over the first `cells` entries.
 void launch_decay_and_mean(float* grid, const float* grid_current, uint32_t total, uint32_t cells, float decay,
                            int do_decay, float* partial_a, float* partial_b, float* mean, cudaStream_t stream);

@@ -21,34 +21,13 @@ namespace {
 
 constexpr int kRefreshBlock = 128;
 
-// generate_grid_samples_nerf_nonuniform (:104-185) + hash encoding + density MLP output 0 +
-// splat_grid_samples_nerf_max_nearest_neighbor (:187-212) for one of the two sampling passes.
+// generate_grid_samples_nerf_nonuniform (:104-185) + hash encoding + density MLP output 0 for sample index i of one
+// sampling pass: returns the optical thickness the splat (:187-212) writes and, in *idx_out, the cell it goes to.
 template <int F>
-__global__ void __launch_bounds__(kRefreshBlock)
-k_refresh_sample(const DevCfg g, const NetMeta net, const __grid_constant__ RefreshWeights W, const __half* __restrict__ table,
-                 const float* __restrict__ grid_in, float* __restrict__ grid_current, uint32_t n_elements,
-                 uint32_t step, Pcg rng0, float thresh, uint32_t aabb_scale, uint32_t inv_mult) {
-    // The 2 112 weights the MLP needs arrive in the kernel's parameter block (constant bank): with the loops
-    // below fully unrolled every multiply-add names its weight as a constant operand, so the layer costs no
-    // load instructions at all (a shared-memory copy of the matrix made this kernel L1/shared-memory bound).
-    __shared__ EncMeta enc_meta;
-    prepare_enc_meta(net, table, &enc_meta);
-    __syncthreads();
-    const uint32_t tid = blockIdx.x * kRefreshBlock + threadIdx.x;
-    if (tid >= n_elements) return;
-    // Which sample index i this thread takes.  The reference gives thread i the cell
-    // ((i + step*n) * 56924617 + 96925573) mod cells: a pseudo-random cell, so neighbouring threads gather from
-    // unrelated table lines.  The result does not depend on which thread handles which i (the splat is an
-    // atomic max), so when the map is a bijection (power-of-two cell count, n a multiple of it: inv_mult != 0)
-    // thread t takes the i whose first-try cell is t: neighbouring threads then work on neighbouring Morton cells
-    // and their gathers share lines.
-    uint32_t i = tid;
-    if (inv_mult) {
-        const uint32_t q = tid / g.cells, c = tid % g.cells;
-        const uint32_t v = (c - 96925573u) * inv_mult;                    // (i + step*n) mod cells
-        i = q * g.cells + ((v - step * n_elements) & (g.cells - 1u));
-    }
-
+__device__ __forceinline__ float refresh_sample(const DevCfg& g, const EncMeta* enc_meta, const RefreshWeights& W,
+                                                const __half* __restrict__ table, const float* __restrict__ grid_in, uint32_t i,
+                                                uint32_t n_elements, uint32_t step, const Pcg& rng0, float thresh,
+                                                uint32_t aabb_scale, uint32_t* idx_out) {
     Pcg rng = rng0;
     if (i < (1u << 30)) pcg_jump(rng, i * 4u);             // rng.advance(i*4), :125
     else pcg_advance(rng, (uint64_t)i * 4u);
@@ -60,6 +39,7 @@ k_refresh_sample(const DevCfg g, const NetMeta net, const __grid_constant__ Refr
         idx += level * g.cells;
         if (grid_in[idx] > thresh) break;
     }
+    *idx_out = idx;
     const uint32_t pos_idx = idx % g.cells;
     const uint32_t cx = morton3D_invert(pos_idx >> 0), cy = morton3D_invert(pos_idx >> 1), cz = morton3D_invert(pos_idx >> 2);
     const float u0 = pcg_next_float(rng), u1 = pcg_next_float(rng), u2 = pcg_next_float(rng);
@@ -86,13 +66,16 @@ k_refresh_sample(const DevCfg g, const NetMeta net, const __grid_constant__ Refr
     }
 
     uint32_t enc[16];
-    hash_encode_packed<F>(&enc_meta, table, pos.x, pos.y, pos.z, enc);
+    hash_encode_packed<F>(enc_meta, table, pos.x, pos.y, pos.z, enc);
     float x[32];
 #pragma unroll
     for (int k = 0; k < 16; ++k) {
         const __half2 h = *reinterpret_cast<const __half2*>(&enc[k]);
         x[2 * k] = __low2float(h); x[2 * k + 1] = __high2float(h);
     }
+    // The 2 112 weights the MLP needs arrive in the kernel's parameter block (constant bank): with the loops
+    // below fully unrolled every multiply-add names its weight as a constant operand, so the layer costs no
+    // load instructions at all (a shared-memory copy of the matrix made this kernel L1/shared-memory bound).
     float out0 = 0.f;
 #pragma unroll
     for (int o = 0; o < 64; ++o) {
@@ -104,7 +87,35 @@ k_refresh_sample(const DevCfg g, const NetMeta net, const __grid_constant__ Refr
         out0 = fmaf(W.w2[o], h, out0);
     }
     const float raw = __half2float(__float2half_rn(out0));
-    const float thickness = network_to_density(raw, g.density_activation) * g.min_step;
+    return network_to_density(raw, g.density_activation) * g.min_step;
+}
+
+// Which sample index lands, at its first try, in cell c: the reference gives thread i the cell
+// ((i + step*n) * 56924617 + 96925573) mod cells, a bijection of [0, cells) when the cell count is a power of two and n
+// a multiple of it; inv_mult is the inverse of 56924617 modulo 2^32.
+__device__ __forceinline__ uint32_t sample_index_of_cell(uint32_t tid, uint32_t cells, uint32_t n_elements, uint32_t step, uint32_t inv_mult) {
+    const uint32_t q = tid / cells, c = tid % cells;
+    const uint32_t v = (c - 96925573u) * inv_mult;                    // (i + step*n) mod cells
+    return q * cells + ((v - step * n_elements) & (cells - 1u));
+}
+
+// One of the two sampling passes followed by splat_grid_samples_nerf_max_nearest_neighbor (:187-212).
+template <int F>
+__global__ void __launch_bounds__(kRefreshBlock)
+k_refresh_sample(const DevCfg g, const NetMeta net, const __grid_constant__ RefreshWeights W, const __half* __restrict__ table,
+                 const float* __restrict__ grid_in, float* __restrict__ grid_current, uint32_t n_elements,
+                 uint32_t step, Pcg rng0, float thresh, uint32_t aabb_scale, uint32_t inv_mult) {
+    __shared__ EncMeta enc_meta;
+    prepare_enc_meta(net, table, &enc_meta);
+    __syncthreads();
+    const uint32_t tid = blockIdx.x * kRefreshBlock + threadIdx.x;
+    if (tid >= n_elements) return;
+    // The result does not depend on which thread handles which sample index (the splat is an atomic max), so when the
+    // cell map is a bijection thread t takes the index whose first-try cell is t: neighbouring threads then work on
+    // neighbouring Morton cells and their gathers share table lines.
+    const uint32_t i = inv_mult ? sample_index_of_cell(tid, g.cells, n_elements, step, inv_mult) : tid;
+    uint32_t idx;
+    const float thickness = refresh_sample<F>(g, &enc_meta, W, table, grid_in, i, n_elements, step, rng0, thresh, aabb_scale, &idx);
     // positive floats order like their bit patterns (:209-211)
     atomicMax(reinterpret_cast<unsigned int*>(grid_current + idx), __float_as_uint(thickness));
 }
@@ -127,6 +138,139 @@ __device__ __forceinline__ float block_tree_sum_1024(float v, float* smem /* 102
         }
     }
     return x;
+}
+
+// The stride-halving sum of 1024 values in shared memory by a block of kRefreshBlock threads: the same additions in the
+// same order as block_tree_sum_1024 (within a stride every addition is independent), so the same bits.  Result in smem[0].
+__device__ __forceinline__ void tree_sum_1024_by_128(float* smem /* 1024, filled, synchronised */) {
+    const int t = threadIdx.x;
+    for (int h = 512; h >= 1; h >>= 1) {
+        for (int k = t; k < h; k += kRefreshBlock) smem[k] = smem[k] + smem[k + h];
+        __syncthreads();
+    }
+}
+
+// The whole refresh in one kernel for the common case -- every cell sampled once (the first 256 training steps),
+// one cascade, no cell masked as never seen: then the reference's pseudo-random cell map is a bijection, the sample whose
+// first try is cell c is the only writer of cell c, and sample -> encode -> MLP -> splat -> max-decay collapse into
+// "compute, compare with the decayed old value, store" with no atomics, no scratch grid and no separate decay pass
+// (generate_grid_samples_nerf_nonuniform, splat_grid_samples_nerf_max_nearest_neighbor, ema_grid_samples_nerf:
+// internal/sampler/occupancy_sampler.cu:104-238).  A block owns a chunk of 1024 Morton-consecutive cells and leaves the
+// chunk's term of the mean's summation tree; the block that finishes last (a ticket from one atomic counter: no block
+// ever waits for another) folds the upper levels of the tree and writes the mean.  Block 0 also clears the sampler's
+// skip tables, which the bit-packing kernel that follows fills.
+template <int F>
+__global__ void __launch_bounds__(kRefreshBlock)
+k_refresh_fused(const DevCfg g, const NetMeta net, const __grid_constant__ RefreshWeights W, const __half* __restrict__ table,
+                float* __restrict__ grid, uint32_t step, Pcg rng0, float thresh, uint32_t aabb_scale, uint32_t inv_mult, float decay,
+                float* __restrict__ partial_a, float* __restrict__ partial_b, float* __restrict__ mean, unsigned int* __restrict__ ticket,
+                uint32_t* __restrict__ skip_shell, uint32_t* __restrict__ skip_yz, unsigned int* __restrict__ error_flags) {
+    __shared__ EncMeta enc_meta;
+    __shared__ float smem[1024];
+    __shared__ unsigned int s_last;
+    prepare_enc_meta(net, table, &enc_meta);
+    __syncthreads();
+    const uint32_t cells = g.cells;
+    if (blockIdx.x == 0 && skip_shell) {
+        const uint32_t N = g.grid_size;
+        for (uint32_t k = threadIdx.x; k < (N + 31) / 32; k += kRefreshBlock) skip_shell[k] = 0u;
+        for (uint32_t k = threadIdx.x; k < (N * N + 31) / 32; k += kRefreshBlock) skip_yz[k] = 0u;
+    }
+    const uint32_t chunk0 = blockIdx.x * 1024u;
+    bool masked = false;
+#pragma unroll 1
+    for (uint32_t it = 0; it < 1024u / kRefreshBlock; ++it) {
+        const uint32_t c = chunk0 + it * kRefreshBlock + threadIdx.x;
+        float contrib = 0.f;
+        if (c < cells) {
+            const float prev = grid[c];
+            masked |= !(prev > thresh);                    // such a cell's sample goes elsewhere: the host must not pick this path
+            const uint32_t i = sample_index_of_cell(c, cells, cells, step, inv_mult);
+            uint32_t idx;
+            const float thickness = refresh_sample<F>(g, &enc_meta, W, table, grid, i, cells, step, rng0, thresh, aabb_scale, &idx);
+            const float v = (prev < 0.f) ? prev : fmaxf(prev * decay, thickness);      // ema_grid_samples_nerf, :235-237
+            grid[c] = v;
+            contrib = fmaxf(v, 0.f) / (float)cells;
+        }
+        smem[it * kRefreshBlock + threadIdx.x] = contrib;
+    }
+    if (masked && error_flags) atomicOr(error_flags, 8u);
+    __syncthreads();
+    tree_sum_1024_by_128(smem);
+    if (threadIdx.x == 0) {
+        partial_a[blockIdx.x] = smem[0];
+        __threadfence();
+        s_last = atomicAdd(ticket, 1u) == gridDim.x - 1u ? 1u : 0u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    // last block: the upper levels of the tree (chunks of 1024 partial sums, zero padded), as k_tree_sum runs them
+    __threadfence();
+    uint32_t n = gridDim.x;
+    const float* in = partial_a;
+    float* out = partial_b;
+    for (;;) {
+        const uint32_t nb = (n + 1023u) / 1024u;
+        for (uint32_t b = 0; b < nb; ++b) {
+            for (uint32_t k = threadIdx.x; k < 1024u; k += kRefreshBlock) {
+                const uint32_t j = b * 1024u + k;
+                smem[k] = j < n ? __ldcg(in + j) : 0.f;
+            }
+            __syncthreads();
+            tree_sum_1024_by_128(smem);
+            if (threadIdx.x == 0) (nb == 1 ? mean : out)[b] = smem[0];
+            __syncthreads();
+        }
+        if (nb == 1) break;
+        n = nb;
+        const float* t = in; in = out; out = const_cast<float*>(t);
+        __threadfence_block();
+    }
+    if (threadIdx.x == 0) *ticket = 0u;                     // ready for the next refresh
+}
+
+// grid_to_bitfield (:240-260) for one cascade and k_build_skip_tables in one pass: a thread packs 32 Morton-consecutive
+// cells into one word of the bitfield and marks the word's radial / latitude indices in the skip tables (cleared by
+// k_refresh_fused).
+__global__ void __launch_bounds__(256)
+k_bits_and_skip(const float* __restrict__ grid, uint32_t* __restrict__ bits32, uint32_t n_words, uint32_t n_grid_size,
+                const float* __restrict__ mean, float min_optical_thickness, uint32_t* __restrict__ shell, uint32_t* __restrict__ yz) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_words) return;
+    const float m = *mean;
+    const float thresh = (m < min_optical_thickness) ? m : min_optical_thickness;   // std::min(min_thickness, mean)
+    const float4* p = reinterpret_cast<const float4*>(grid) + (size_t)i * 8;
+    uint32_t b = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float4 a = p[k];
+        b |= (a.x > thresh ? 1u : 0u) << (4 * k);
+        b |= (a.y > thresh ? 1u : 0u) << (4 * k + 1);
+        b |= (a.z > thresh ? 1u : 0u) << (4 * k + 2);
+        b |= (a.w > thresh ? 1u : 0u) << (4 * k + 3);
+    }
+    bits32[i] = b;
+    if (!b || !shell) return;
+    const uint32_t m0 = i * 32u;
+    const uint32_t y_base = morton3D_invert(m0 >> 1), z_base = morton3D_invert(m0 >> 2);
+#pragma unroll
+    for (uint32_t zl = 0; zl < 2; ++zl) {
+        bool any_z = false;
+#pragma unroll
+        for (uint32_t yl = 0; yl < 4; ++yl) {
+            const uint32_t o = ((yl & 1u) << 1) | (zl << 2) | ((yl >> 1) << 4);
+            const uint32_t mask = (1u << o) | (1u << (o | 1u)) | (1u << (o | 8u)) | (1u << (o | 9u));
+            if (b & mask) {
+                any_z = true;
+                const uint32_t k = (z_base + zl) * n_grid_size + (y_base + yl), kb = 1u << (k & 31u);
+                if (!(yz[k >> 5] & kb)) atomicOr(yz + (k >> 5), kb);
+            }
+        }
+        if (any_z) {
+            const uint32_t z = z_base + zl, sb = 1u << (z & 31u);
+            if (!(shell[z >> 5] & sb)) atomicOr(shell + (z >> 5), sb);
+        }
+    }
 }
 
 // ema_grid_samples_nerf (:214-238) over all cells, plus level 0 of the mean's summation tree
@@ -245,6 +389,27 @@ void launch_refresh_sample(const DevCfg& g, const NetMeta& net, const __half* ta
         k_refresh_sample<2><<<nb, kRefreshBlock, 0, stream>>>(g, net, w, table, grid, grid_current, n_elements, step, r, thresh, aabb_scale, inv_mult);
     else
         k_refresh_sample<4><<<nb, kRefreshBlock, 0, stream>>>(g, net, w, table, grid, grid_current, n_elements, step, r, thresh, aabb_scale, inv_mult);
+}
+
+// The refresh as two launches (k_refresh_fused, k_bits_and_skip).  Preconditions, checked by the caller: one cascade,
+// a power-of-two cell count, every cell sampled once, no cell of `grid` below `thresh`.
+void launch_refresh_fused(const DevCfg& g, const NetMeta& net, const __half* table, const RefreshWeights& w, float* grid,
+                          uint32_t step, RefreshRng rng, float thresh, uint32_t aabb_scale, float decay, float* partial_a,
+                          float* partial_b, float* mean, unsigned int* ticket, uint8_t* bits, float min_optical_thickness,
+                          uint32_t* skip_shell, uint32_t* skip_yz, unsigned int* error_flags, cudaStream_t stream) {
+    uint32_t inv_mult = 1;                                 // inverse of 56924617 modulo 2^32 (Newton iteration)
+    for (int it = 0; it < 6; ++it) inv_mult *= 2u - 56924617u * inv_mult;
+    const unsigned int nb = (g.cells + 1023u) / 1024u;
+    Pcg r = {rng.state, rng.inc};
+    if (net.n_features == 2)
+        k_refresh_fused<2><<<nb, kRefreshBlock, 0, stream>>>(g, net, w, table, grid, step, r, thresh, aabb_scale, inv_mult, decay, partial_a,
+                                                             partial_b, mean, ticket, skip_shell, skip_yz, error_flags);
+    else
+        k_refresh_fused<4><<<nb, kRefreshBlock, 0, stream>>>(g, net, w, table, grid, step, r, thresh, aabb_scale, inv_mult, decay, partial_a,
+                                                             partial_b, mean, ticket, skip_shell, skip_yz, error_flags);
+    const uint32_t n_words = g.cells / 32;
+    k_bits_and_skip<<<(n_words + 255) / 256, 256, 0, stream>>>(grid, reinterpret_cast<uint32_t*>(bits), n_words, g.grid_size, mean,
+                                                              min_optical_thickness, skip_shell, skip_yz);
 }
 
 // Max-decay (optional) + mean.  partial_a / partial_b: ceil(cells/1024) floats each.

@@ -252,14 +252,21 @@ def test_mlp_engines_agree_on_raw_outputs(built_lib, oracle_mod, monkeypatch):
     assert np.isfinite(outs["tcgen05"]).all()
 
 
-def test_grid_refresh_bit_exact(built_lib, oracle_mod):
-    """16 consecutive refreshes: every float of the grid and every bit after every step."""
+@pytest.mark.parametrize("path", ["masked_cells", "fused", "unfused"])
+def test_grid_refresh_bit_exact(built_lib, oracle_mod, monkeypatch, path):
+    """16 consecutive refreshes: every float of the grid and every bit after every step.  "masked_cells": a grid with
+    never-seen cells (their samples are redirected: the multi-launch path with the atomic splat).  "fused": no masked
+    cells, so the all-cells refreshes run as the two-launch fused kernel pair; "unfused" forces the multi-launch path on
+    the same grid.  The quarter/quarter refreshes at the end always take the multi-launch path."""
+    if path == "unfused":
+        monkeypatch.setenv("SRF_B200_FUSED_REFRESH", "0")
     sc = small_scene(kind="net", grid_size=32)
     cfg = sc["cfg"]
     min_step = np.float32(np.sqrt(3.0) / cfg.maximum_marching_steps)
     rng = np.random.Generator(np.random.PCG64(3000))
     prior = (sc["grid"].astype(np.float64) * min_step * rng.uniform(0.5, 1.5, sc["grid"].shape[0])).astype(np.float32)
-    prior[::97] = -1.0                       # masked cells stay negative
+    if path == "masked_cells":
+        prior[::97] = -1.0                   # masked cells stay negative
     sc["grid"] = prior
     r = make_renderer(sc)
     r.refresh_reset(3001)
@@ -276,6 +283,11 @@ def test_grid_refresh_bit_exact(built_lib, oracle_mod):
         assert np.array_equal(r.download_bitfield(), obits), f"refresh {k}: bits"
         assert _bits_equal(np.float32(r.grid_mean()), np.float32(omean)), f"refresh {k}: mean"
     assert np.unpackbits(obits).mean() > 0.0
+    r.check_errors()
+    # the sampler's skip tables follow the bitfield on every path: a frame after the refreshes marches like the oracle
+    orc2 = make_oracle(oracle_mod, sc, obits)
+    n = orc2.n_rays(sc["view"])
+    assert np.array_equal(orc2.march(sc["view"], 0, n, 1 << 22)[0], r.dump_samples(sc["view"], 0, n, 1 << 22)[0])
 
 
 def test_sharded_frame_equals_whole_frame(built_lib):
