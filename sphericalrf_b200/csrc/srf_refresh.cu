@@ -140,12 +140,25 @@ __device__ __forceinline__ float block_tree_sum_1024(float v, float* smem /* 102
     return x;
 }
 
-// The stride-halving sum of 1024 values in shared memory by a block of kRefreshBlock threads: the same additions in the
+// A chunk of 1024 cells per block of kFusedBlock threads (the chunk is the unit of the mean's summation tree, so it cannot
+// be split over blocks).  Measured on a B200, 128^3 grid, 64 refreshes: 0.637 ms with 128 threads, 0.521 with 256, 0.555
+// with 512, 0.619 with 1024 -- against 0.501 ms for the multi-launch path (memset, k_refresh_sample, k_decay_and_partial,
+// two k_tree_sum, k_grid_to_bitfield, two memsets, k_build_skip_tables).  The refresh is ~95 % the per-cell encoding and
+// MLP arithmetic; what fusing saves (an 8 MB memset, the 24 MB decay pass, seven launch gaps of a few microseconds) is
+// less than what the coarse 1024-cell work items lose to wave quantisation (2 048 blocks over 148 x 4 resident = 3.46
+// waves) and to the per-thread serial loop.  The fused pair is therefore kept as an option (SRF_B200_FUSED_REFRESH=1,
+// bit-identical, tested) and the multi-launch path stays the default.
+#ifndef SRF_FUSED_BLOCK
+#define SRF_FUSED_BLOCK 256
+#endif
+constexpr int kFusedBlock = SRF_FUSED_BLOCK;
+
+// The stride-halving sum of 1024 values in shared memory by a block of kFusedBlock threads: the same additions in the
 // same order as block_tree_sum_1024 (within a stride every addition is independent), so the same bits.  Result in smem[0].
-__device__ __forceinline__ void tree_sum_1024_by_128(float* smem /* 1024, filled, synchronised */) {
+__device__ __forceinline__ void tree_sum_1024_by_block(float* smem /* 1024, filled, synchronised */) {
     const int t = threadIdx.x;
     for (int h = 512; h >= 1; h >>= 1) {
-        for (int k = t; k < h; k += kRefreshBlock) smem[k] = smem[k] + smem[k + h];
+        for (int k = t; k < h; k += kFusedBlock) smem[k] = smem[k] + smem[k + h];
         __syncthreads();
     }
 }
@@ -160,7 +173,7 @@ __device__ __forceinline__ void tree_sum_1024_by_128(float* smem /* 1024, filled
 // ever waits for another) folds the upper levels of the tree and writes the mean.  Block 0 also clears the sampler's
 // skip tables, which the bit-packing kernel that follows fills.
 template <int F>
-__global__ void __launch_bounds__(kRefreshBlock)
+__global__ void __launch_bounds__(kFusedBlock)
 k_refresh_fused(const DevCfg g, const NetMeta net, const __grid_constant__ RefreshWeights W, const __half* __restrict__ table,
                 float* __restrict__ grid, uint32_t step, Pcg rng0, float thresh, uint32_t aabb_scale, uint32_t inv_mult, float decay,
                 float* __restrict__ partial_a, float* __restrict__ partial_b, float* __restrict__ mean, unsigned int* __restrict__ ticket,
@@ -173,14 +186,14 @@ k_refresh_fused(const DevCfg g, const NetMeta net, const __grid_constant__ Refre
     const uint32_t cells = g.cells;
     if (blockIdx.x == 0 && skip_shell) {
         const uint32_t N = g.grid_size;
-        for (uint32_t k = threadIdx.x; k < (N + 31) / 32; k += kRefreshBlock) skip_shell[k] = 0u;
-        for (uint32_t k = threadIdx.x; k < (N * N + 31) / 32; k += kRefreshBlock) skip_yz[k] = 0u;
+        for (uint32_t k = threadIdx.x; k < (N + 31) / 32; k += kFusedBlock) skip_shell[k] = 0u;
+        for (uint32_t k = threadIdx.x; k < (N * N + 31) / 32; k += kFusedBlock) skip_yz[k] = 0u;
     }
     const uint32_t chunk0 = blockIdx.x * 1024u;
     bool masked = false;
 #pragma unroll 1
-    for (uint32_t it = 0; it < 1024u / kRefreshBlock; ++it) {
-        const uint32_t c = chunk0 + it * kRefreshBlock + threadIdx.x;
+    for (uint32_t it = 0; it < 1024u / kFusedBlock; ++it) {
+        const uint32_t c = chunk0 + it * kFusedBlock + threadIdx.x;
         float contrib = 0.f;
         if (c < cells) {
             const float prev = grid[c];
@@ -192,11 +205,11 @@ k_refresh_fused(const DevCfg g, const NetMeta net, const __grid_constant__ Refre
             grid[c] = v;
             contrib = fmaxf(v, 0.f) / (float)cells;
         }
-        smem[it * kRefreshBlock + threadIdx.x] = contrib;
+        smem[it * kFusedBlock + threadIdx.x] = contrib;
     }
     if (masked && error_flags) atomicOr(error_flags, 8u);
     __syncthreads();
-    tree_sum_1024_by_128(smem);
+    tree_sum_1024_by_block(smem);
     if (threadIdx.x == 0) {
         partial_a[blockIdx.x] = smem[0];
         __threadfence();
@@ -212,12 +225,12 @@ k_refresh_fused(const DevCfg g, const NetMeta net, const __grid_constant__ Refre
     for (;;) {
         const uint32_t nb = (n + 1023u) / 1024u;
         for (uint32_t b = 0; b < nb; ++b) {
-            for (uint32_t k = threadIdx.x; k < 1024u; k += kRefreshBlock) {
+            for (uint32_t k = threadIdx.x; k < 1024u; k += kFusedBlock) {
                 const uint32_t j = b * 1024u + k;
                 smem[k] = j < n ? __ldcg(in + j) : 0.f;
             }
             __syncthreads();
-            tree_sum_1024_by_128(smem);
+            tree_sum_1024_by_block(smem);
             if (threadIdx.x == 0) (nb == 1 ? mean : out)[b] = smem[0];
             __syncthreads();
         }
@@ -402,10 +415,10 @@ void launch_refresh_fused(const DevCfg& g, const NetMeta& net, const __half* tab
     const unsigned int nb = (g.cells + 1023u) / 1024u;
     Pcg r = {rng.state, rng.inc};
     if (net.n_features == 2)
-        k_refresh_fused<2><<<nb, kRefreshBlock, 0, stream>>>(g, net, w, table, grid, step, r, thresh, aabb_scale, inv_mult, decay, partial_a,
+        k_refresh_fused<2><<<nb, kFusedBlock, 0, stream>>>(g, net, w, table, grid, step, r, thresh, aabb_scale, inv_mult, decay, partial_a,
                                                              partial_b, mean, ticket, skip_shell, skip_yz, error_flags);
     else
-        k_refresh_fused<4><<<nb, kRefreshBlock, 0, stream>>>(g, net, w, table, grid, step, r, thresh, aabb_scale, inv_mult, decay, partial_a,
+        k_refresh_fused<4><<<nb, kFusedBlock, 0, stream>>>(g, net, w, table, grid, step, r, thresh, aabb_scale, inv_mult, decay, partial_a,
                                                              partial_b, mean, ticket, skip_shell, skip_yz, error_flags);
     const uint32_t n_words = g.cells / 32;
     k_bits_and_skip<<<(n_words + 255) / 256, 256, 0, stream>>>(grid, reinterpret_cast<uint32_t*>(bits), n_words, g.grid_size, mean,

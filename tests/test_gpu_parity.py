@@ -256,10 +256,9 @@ def test_mlp_engines_agree_on_raw_outputs(built_lib, oracle_mod, monkeypatch):
 def test_grid_refresh_bit_exact(built_lib, oracle_mod, monkeypatch, path):
     """16 consecutive refreshes: every float of the grid and every bit after every step.  "masked_cells": a grid with
     never-seen cells (their samples are redirected: the multi-launch path with the atomic splat).  "fused": no masked
-    cells, so the all-cells refreshes run as the two-launch fused kernel pair; "unfused" forces the multi-launch path on
-    the same grid.  The quarter/quarter refreshes at the end always take the multi-launch path."""
-    if path == "unfused":
-        monkeypatch.setenv("SRF_B200_FUSED_REFRESH", "0")
+    cells and the two-launch refresh switched on, so the all-cells refreshes run as the fused kernel pair; "unfused": the
+    default multi-launch path on the same grid.  The quarter/quarter refreshes at the end always take the multi-launch path."""
+    monkeypatch.setenv("SRF_B200_FUSED_REFRESH", "1" if path == "fused" else "0")
     sc = small_scene(kind="net", grid_size=32)
     cfg = sc["cfg"]
     min_step = np.float32(np.sqrt(3.0) / cfg.maximum_marching_steps)

@@ -136,3 +136,31 @@ def test_snapshot_renders_like_uploaded_parameters(built_lib, oracle_mod, tmp_pa
         res = orc.render_frame(v, post, 0, n, acc)
         acc = res["accum"]
     assert np.abs(res["out"].reshape(H, W, 4) - img).max() < 1e-3
+
+
+@pytest.mark.gpu
+def test_predict_driver_on_a_trajectory_file(built_lib, tmp_path):
+    """The reference's predict loop (experiment/*/python/run.py:218-250) on a snapshot and a three-frame transforms file:
+    colour + depth per frame, same pixels as calling the module by hand."""
+    from sphericalrf_b200 import predict
+    cfg, table, dmlp, rmlp, grid = _scene()
+    path = tmp_path / "scene.msgpack"
+    snapshot.write_snapshot(str(path), SMALL, grid, dmlp, rmlp, table, 1.0, (0.5, 0.5, 0.5))
+    frames = []
+    for k in range(3):
+        c, s_ = np.cos(0.7 * k), np.sin(0.7 * k)
+        frames.append({"file_path": f"./spherical/{k:03d}.png",
+                       "transform_matrix": [[c, 0, s_, 0.2 * s_], [s_, 0, -c, -0.2 * c], [0, 1, 0, 0.05], [0, 0, 0, 1]]})
+    W, H = 36, 24
+    testbed = ngp.Testbed()
+    testbed.load_snapshot(str(path))
+    res = predict.predict(testbed, {"frames": frames}, W, H, angle_x_deg=60.0, spp=2, output_dir=str(tmp_path / "out"))
+    assert len(res["images"]) == 3 and res["fps"] > 0 and all(d.shape == (H, W, 4) for d in res["depths"])
+    assert (tmp_path / "out" / "image_predict" / "001.npy").exists() and (tmp_path / "out" / "depth_predict" / "002.npy").exists()
+    again = ngp.Testbed()
+    again.load_snapshot(str(path))
+    again.background_color = [1.0, 1.0, 1.0, 1.0]
+    again.fov_xy = [np.radians(60.0), np.radians(np.degrees(np.radians(30.0) / (W / H)) * 2.0)]
+    again.set_nerf_camera_matrix(np.asarray(frames[1]["transform_matrix"], np.float32)[:-1, :])
+    assert np.array_equal(again.render(W, H, 2, False), res["images"][1])
+    assert not np.array_equal(res["images"][0], res["images"][1])
