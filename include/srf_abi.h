@@ -369,6 +369,13 @@ srf_status srf_get_timings(const srf_comm* comm, float* ms_per_context, uint32_t
    sampler counts always runs in one pass.) */
 srf_status srf_set_wave_schedule(srf_ctx* ctx, const uint32_t* steps, uint32_t n);
 
+/* Memory the frame path may spend on cell-major copies of the leading hash-grid levels (for every cell of a level,
+   the fp16 entries of its eight corners side by side: one 16*n_features_per_level-byte read per sample and level
+   instead of eight scattered ones; NGPNetwork's grid encoding, internal/network/ngp_network.h:233-248, reads the
+   entries one by one).  As many leading levels as fit are copied; the copies are rebuilt on the first frame after
+   srf_upload_network.  Default 4 GiB (10 levels of the 16 x 2^19 grid); 0 switches them off.  Results do not change. */
+srf_status srf_set_cell_table_budget(srf_ctx* ctx, uint64_t bytes);
+
 /* Testbed::render (internal/python_api.cu:17-41): spp passes of srf_render_frame and the copy
    to a host image h_image float[height*width*4] (whole image; shard_count must be 1).
    Synchronises. */

@@ -299,7 +299,6 @@ int refh_render_frame(const srf_config_t* cfg, const srf_view_t* view, const srf
         n_alive = alive_counter;
         if (n_alive == 0) break;
         const uint32_t n_steps = tcnn::clamp(n_pixels / n_alive, kMinSteps, kMaxSteps);
-        if (getenv("SRF_REF_DEBUG")) fprintf(stderr, "round %llu alive %u n_steps %u offset %u\n", (unsigned long long)n_rounds, n_alive, n_steps, i_steps_offset);
         run_linear_parallel(generate_coords_from_rays_regularly_kernel, n_alive, n_steps, s.warping_type, s.aabb, s.n_grid_size, s.n_cascades,
                    s.griddist_type, s.use_grid ? bitfield : (const uint8_t*)nullptr, s.n_max_steps, s.cone_angle_constant,
                    s.min_cone_stepsize, s.max_cone_stepsize, s.near_distance, s.far_distance, s.sampling_type, cur_p.data(),

@@ -201,6 +201,7 @@ SYMBOLS = {
     "srf_get_timings": (C.c_int, [C.c_void_p, _P(C.c_float), C.c_uint32]),
     "srf_reserve": (C.c_int, [_ctx, C.c_uint64]),
     "srf_set_wave_schedule": (C.c_int, [_ctx, _vp, C.c_uint32]),
+    "srf_set_cell_table_budget": (C.c_int, [_ctx, C.c_uint64]),
     "srf_sampler_init": (C.c_int, [_ctx, _P(TrainViews), C.c_int, C.c_uint64, _vp]),
     "srf_sample_training_rays": (C.c_int, [_ctx, _P(TrainViews), C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint64, C.c_uint64,
                                            C.c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),

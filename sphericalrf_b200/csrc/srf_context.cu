@@ -57,6 +57,13 @@ struct srf_ctx {
     uint32_t* skip_yz = nullptr;
     bool skip_capable = false;
     __half* table = nullptr;
+    float* table_f32 = nullptr;          // fp32 copy of the table for the tcgen05 field kernel (optional)
+    uint4* cell_table = nullptr;         // cell-major copies of the leading levels of the table (see CellTables)
+    int n_cell_levels = 0;               // levels the allocation covers
+    uint64_t cell_budget = 4ull << 30;   // bytes the copies may take (srf_set_cell_table_budget); 0: none
+    int cell_levels_forced = -1;         // SRF_B200_CELL_LEVELS, when set
+    bool cell_dirty = true;              // the table changed since the copies were built
+    float* act_lut = nullptr;            // both activations tabulated over all fp16 arguments
     __half* w_density = nullptr;
     __half* w_rgb = nullptr;
     bool have_net = false;
@@ -496,6 +503,17 @@ srf_status srf_create(const srf_config_t* cfg, int device, srf_ctx** out) {
         build_net_meta(*cfg, &ctx->net);
         ctx->n_table_entries = table_entries(ctx->net);
         CK_CREATE(cudaMalloc((void**)&ctx->table, (size_t)ctx->n_table_entries * cfg->n_features_per_level * sizeof(__half)));
+        if (const char* e = getenv("SRF_B200_CELL_LEVELS")) ctx->cell_levels_forced = atoi(e);
+        const char* lut_env = getenv("SRF_B200_ACT_LUT");
+        if (!lut_env || atoi(lut_env) != 0) {
+            CK_CREATE(cudaMalloc((void**)&ctx->act_lut, 2 * 65536 * sizeof(float)));
+            launch_build_activation_table(ctx->g, ctx->act_lut, 0);
+            CK_CREATE(cudaDeviceSynchronize());
+        }
+        if (const char* e = getenv("SRF_B200_TABLE_F32")) {
+            if (atoi(e) != 0)
+                CK_CREATE(cudaMalloc((void**)&ctx->table_f32, (size_t)ctx->n_table_entries * cfg->n_features_per_level * sizeof(float)));
+        }
         CK_CREATE(cudaMalloc((void**)&ctx->w_density, (64 * 32 + 16 * 64) * sizeof(__half)));
         CK_CREATE(cudaMalloc((void**)&ctx->w_rgb, (64 * 32 + 64 * 64 + 16 * 64) * sizeof(__half)));
     }
@@ -518,7 +536,7 @@ srf_status srf_create(const srf_config_t* cfg, int device, srf_ctx** out) {
 void srf_destroy(srf_ctx* ctx) {
     if (!ctx) return;
     DeviceGuard guard(ctx->device);
-    void* ptrs[] = {ctx->grid, ctx->grid_current, ctx->partial_a, ctx->partial_b, ctx->mean, ctx->bits, ctx->table,
+    void* ptrs[] = {ctx->grid, ctx->grid_current, ctx->partial_a, ctx->partial_b, ctx->mean, ctx->bits, ctx->table, ctx->table_f32, ctx->cell_table, ctx->act_lut,
                     ctx->w_density, ctx->w_rgb, ctx->skip_shell, ctx->skip_yz, ctx->train_flags.p, ctx->train_rank.p, ctx->loss_rgb.p, ctx->ray_sh.p, ctx->ray_ordinal.p, ctx->ray_total.p, ctx->ray_rgba.p, ctx->ray_ncomp.p, ctx->blobs, ctx->cmap, ctx->d_counters, ctx->ray_dir_t.p, ctx->ray_end.p,
                     ctx->counts.p, ctx->offsets.p, ctx->scan_scratch.p, ctx->pos_dt.p, ctx->sample_ray.p, ctx->rgbs.p,
                     ctx->img_out.p, ctx->img_accum.p, ctx->pool_pos.p, ctx->pool_shaded.p, ctx->chunk_ray.p, ctx->chunk_next.p,
@@ -560,6 +578,11 @@ srf_status srf_upload_network(srf_ctx* ctx, const uint16_t* h_table, size_t n_ta
     if (n_c != 64 * 32 + 64 * 64 + 16 * 64) return fail(ctx, SRF_ERR_ARG, "colour MLP must hold 64x32 + 64x64 + 16x64 halves");
     DeviceGuard guard(ctx->device);
     SRF_CK(ctx, cudaMemcpy(ctx->table, h_table, n_table * sizeof(__half), cudaMemcpyHostToDevice));
+    if (ctx->table_f32) {
+        launch_table_to_f32(ctx->table, n_table, ctx->table_f32, 0);
+        SRF_CK(ctx, cudaDeviceSynchronize());
+    }
+    ctx->cell_dirty = true;
     SRF_CK(ctx, cudaMemcpy(ctx->w_density, h_d, n_d * sizeof(__half), cudaMemcpyHostToDevice));
     SRF_CK(ctx, cudaMemcpy(ctx->w_rgb, h_c, n_c * sizeof(__half), cudaMemcpyHostToDevice));
     for (int i = 0; i < 64 * 32; ++i) ctx->refresh_w.w1[i] = __half2float(__ushort_as_half(h_d[i]));
@@ -903,15 +926,50 @@ srf_status srf_sample_emit(srf_ctx* ctx, const srf_view_t* view, const uint64_t*
     return SRF_OK;
 }
 
+// Cell-major copies of as many leading levels as the budget allows, (re)built on `stream` when the table changed.
+static srf_status ensure_cell_tables(srf_ctx* ctx, cudaStream_t stream) {
+    int want = 0;
+    if (ctx->use_tcgen05 && !ctx->table_f32) {
+        for (int l = 1; l <= (int)ctx->net.n_levels; ++l) {
+            if (ctx->cell_levels_forced >= 0 ? l > ctx->cell_levels_forced
+                                             : cell_table_units(ctx->net, l, nullptr) * sizeof(uint4) > ctx->cell_budget) break;
+            want = l;
+        }
+    }
+    if (want != ctx->n_cell_levels) {
+        if (ctx->cell_table) { SRF_CK(ctx, cudaFree(ctx->cell_table)); ctx->cell_table = nullptr; }
+        ctx->n_cell_levels = 0;
+        if (want > 0) {
+            SRF_CK(ctx, cudaMalloc((void**)&ctx->cell_table, cell_table_units(ctx->net, want, nullptr) * sizeof(uint4)));
+            ctx->n_cell_levels = want;
+            ctx->cell_dirty = true;
+        }
+    }
+    if (ctx->cell_dirty && ctx->n_cell_levels > 0) {
+        launch_build_cell_tables(ctx->net, ctx->table, ctx->n_cell_levels, ctx->cell_table, stream);
+        SRF_CK(ctx, cudaGetLastError());
+    }
+    ctx->cell_dirty = false;
+    return SRF_OK;
+}
+
+srf_status srf_set_cell_table_budget(srf_ctx* ctx, uint64_t bytes) {
+    if (!ctx) return SRF_ERR_ARG;
+    ctx->cell_budget = bytes;
+    return SRF_OK;
+}
+
 srf_status srf_network_inference(srf_ctx* ctx, const float* d_coords, uint64_t n, uint16_t* d_rgbsigma, void* stream) {
     if (!ctx || (!d_coords && n) || (!d_rgbsigma && n)) return SRF_ERR_ARG;
     if (ctx->cfg.field_type != SRF_FIELD_NETWORK) return fail(ctx, SRF_ERR_STATE, "context has no network field");
     srf_status st = check_ready(ctx);
     if (st != SRF_OK) return st;
     DeviceGuard guard(ctx->device);
+    if ((st = ensure_cell_tables(ctx, (cudaStream_t)stream)) != SRF_OK) return st;
     if (ctx->use_tcgen05)
         launch_field_network_tc(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, nullptr, nullptr, nullptr, d_coords, n,
-                                (uint2*)d_rgbsigma, nullptr, nullptr, nullptr, &ctx->d_counters->error_flags, (cudaStream_t)stream);
+                                (uint2*)d_rgbsigma, nullptr, nullptr, nullptr, &ctx->d_counters->error_flags, (cudaStream_t)stream,
+                                nullptr, 0, nullptr, ctx->table_f32, ctx->cell_table, ctx->n_cell_levels);
     else
         launch_field_network(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, nullptr, nullptr, nullptr, d_coords, n,
                              (uint2*)d_rgbsigma, nullptr, nullptr, nullptr, (cudaStream_t)stream);
@@ -1002,6 +1060,7 @@ static srf_status render_frame_impl(srf_ctx* ctx, const srf_view_t* view, const 
     const uint8_t* bits = ctx->cfg.use_grid ? ctx->bits : nullptr;
     const bool sh_per_ray = !blobs && ctx->use_tcgen05 && v.render_mode != SRF_MODE_NORMALS;
     if (sh_per_ray && (st = ensure(ctx, ctx->ray_sh, v.n_rays * 2 * sizeof(uint4))) != SRF_OK) return st;
+    if (!blobs && (st = ensure_cell_tables(ctx, s)) != SRF_OK) return st;
     uint32_t n_batches = 0;
     // Waves: the leading waves take every ray a limited number of march steps further, so that rays the compositor
     // finishes early never have the rest of their samples generated or evaluated; the last wave is unlimited.  A
@@ -1044,7 +1103,8 @@ static srf_status render_frame_impl(srf_ctx* ctx, const srf_view_t* view, const 
                 launch_field_network_tc(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, (const float4*)ctx->pool_pos.p,
                                         (const uint32_t*)ctx->chunk_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, 0, nullptr,
                                         (float4*)ctx->pool_shaded.p, &ctx->g, &v, &ctx->d_counters->error_flags, s,
-                                        ctx->d_chunk_cursor, kChunkShift, sh_per_ray ? (const uint4*)ctx->ray_sh.p : nullptr);
+                                        ctx->d_chunk_cursor, kChunkShift, sh_per_ray ? (const uint4*)ctx->ray_sh.p : nullptr,
+                                        ctx->table_f32, ctx->cell_table, ctx->n_cell_levels, ctx->act_lut);
             else
                 launch_field_network(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, (const float4*)ctx->pool_pos.p,
                                      (const uint32_t*)ctx->chunk_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, 0, nullptr,

@@ -588,11 +588,9 @@ __device__ __forceinline__ float linear_to_srgb(float l) {
 // What the compositor needs from one sample: the activated colour and the opacity of the step
 // (volume_rendering_kernel, internal/render/ray_marcher.cu:236-265).  raw = (r, g, b, sigma) as the
 // field returned them; w = warped position (for the depth modes).
-__device__ __forceinline__ float4 shade_sample(const DevCfg& g, const DevView& v, const float (&raw)[4], float dt, const V3& w) {
-    const float alpha = 1.f - srf_expf(-network_to_density(raw[3], g.density_activation) * dt);
-    float cr = network_to_rgb(raw[0], g.rgb_activation);
-    float cg = network_to_rgb(raw[1], g.rgb_activation);
-    float cb = network_to_rgb(raw[2], g.rgb_activation);
+__device__ __forceinline__ float4 shade_finish(const DevCfg& g, const DevView& v, float sigma, float cr, float cg, float cb,
+                                               float dt, const V3& w) {
+    const float alpha = 1.f - srf_expf(-sigma * dt);
     if (v.render_mode == SRF_MODE_DEPTH || v.render_mode == SRF_MODE_DISTANCE) {
         const V3 p = unwarp_position(g, w);
         const float dx = p.x - v.cam[3], dy = p.y - v.cam[7], dz = p.z - v.cam[11];
@@ -604,6 +602,17 @@ __device__ __forceinline__ float4 shade_sample(const DevCfg& g, const DevView& v
         cr = cg = cb = alpha;
     }
     return make_float4(cr, cg, cb, alpha);
+}
+__device__ __forceinline__ float4 shade_sample(const DevCfg& g, const DevView& v, const float (&raw)[4], float dt, const V3& w) {
+    return shade_finish(g, v, network_to_density(raw[3], g.density_activation), network_to_rgb(raw[0], g.rgb_activation),
+                        network_to_rgb(raw[1], g.rgb_activation), network_to_rgb(raw[2], g.rgb_activation), dt, w);
+}
+// The same with the activations read from a table.  The network's outputs are fp16 numbers, so an activation has
+// 65 536 possible arguments: lut[h] = network_to_rgb(value of the half with bits h), lut[65536 + h] =
+// network_to_density(...), filled by the functions above (the table holds exactly what they return).
+__device__ __forceinline__ float4 shade_sample_lut(const DevCfg& g, const DevView& v, const float* __restrict__ lut,
+                                                   uint32_t hr, uint32_t hg, uint32_t hb, uint32_t hs, float dt, const V3& w) {
+    return shade_finish(g, v, __ldg(lut + 65536 + hs), __ldg(lut + hr), __ldg(lut + hg), __ldg(lut + hb), dt, w);
 }
 
 }  // namespace srf

@@ -48,6 +48,10 @@ constexpr int kGroup = 128;
 constexpr int kTcBlock = kGroup * kGroups;
 constexpr uint32_t kTmemCols = 64 * kGroups;      // 64 per group: the whole tensor memory of the SM
 constexpr uint32_t kWaitLimit = 1u << 20;
+#ifndef SRF_TC_PAIR
+#define SRF_TC_PAIR 1
+#endif
+constexpr int kPair = SRF_TC_PAIR;                // groups that share one commit round trip per layer (1, 2 or 4)
 
 // shared-memory map (bytes)
 constexpr int kSmW_D1 = 0;                        // [4][64][8]
@@ -157,42 +161,45 @@ __device__ __forceinline__ void store_units(const uint32_t (&acc)[16], unsigned 
 
 // group-local named barriers 1..kGroups (id 0 is __syncthreads)
 __device__ __forceinline__ void group_sync(int group) {
-    asm volatile("bar.sync %0, 128;" :: "r"(group + 1) : "memory");
+    asm volatile("bar.sync %0, %1;" :: "r"(group / kPair + 1), "n"(128 * kPair) : "memory");
 }
 __device__ __forceinline__ bool group_any(int group, bool v) {
     uint32_t r;
-    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.or.pred q, %2, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}\n"
-                 : "=r"(r) : "r"((uint32_t)v), "r"(group + 1) : "memory");
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.or.pred q, %2, %3, p;\n\tselp.u32 %0, 1, 0, q;\n\t}\n"
+                 : "=r"(r) : "r"((uint32_t)v), "r"(group / kPair + 1), "n"(128 * kPair) : "memory");
     return r != 0;
 }
 
 // FRAME: the frame path's argument set (paged pool records in, per-ray SH table, shaded records out), fixed at compile
 // time so that the stage entry points' alternatives cost it neither branches nor registers.
-template <int F, bool FRAME>
+// T32: `table` is the fp32 copy of the hash table (one 8- or 16-byte load per corner, no conversions).
+template <int F, bool FRAME, bool T32>
 __global__ void __launch_bounds__(kTcBlock, 1)
-k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __half* __restrict__ wd,
+k_field_network_tc(const NetMeta net, const void* __restrict__ table, const __half* __restrict__ wd,
                    const __half* __restrict__ wc, const float4* __restrict__ pos_dt,
                    const uint32_t* __restrict__ sample_ray, const float4* __restrict__ ray_dir_t,
                    const float* __restrict__ coords7, uint64_t n, uint2* __restrict__ rgbsigma,
                    float4* __restrict__ shaded, const DevCfg g, const DevView v,
                    unsigned int* __restrict__ error_flags, const uint32_t* __restrict__ n_chunks_dev, uint32_t ray_shift,
-                   const uint4* __restrict__ ray_sh, int n_staged) {
+                   const uint4* __restrict__ ray_sh, int n_staged, const CellTables cells,
+                   const float* __restrict__ act_lut) {
     if (n_chunks_dev) n = (uint64_t)(*n_chunks_dev) * kChunkSamples;        // frame path: the sampler's chunk count
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, warp = tid >> 5;
     const int group = tid >> 7, row = tid & 127;
-    uint64_t* bar_ptr = reinterpret_cast<uint64_t*>(smem + kSmBar) + group;
+    uint64_t* bar_ptr = reinterpret_cast<uint64_t*>(smem + kSmBar) + group / kPair * kPair;   // the set's barrier
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kSmBar + kGroups * 8);
     const uint32_t bar = smem_u32(bar_ptr);
 
     EncMeta* enc_meta = reinterpret_cast<EncMeta*>(smem + kSmEnc);
-    prepare_enc_meta(net, table, enc_meta);
+    prepare_enc_meta(net, table, enc_meta, T32 ? F : F / 2);
+    if (!T32) attach_cell_tables(cells, enc_meta);
     load_weight_image(wd, 64, 32, smem + kSmW_D1);
     load_weight_image(wd + 64 * 32, 16, 64, smem + kSmW_D2);
     load_weight_image(wc, 64, 32, smem + kSmW_C1);
     load_weight_image(wc + 64 * 32, 64, 64, smem + kSmW_C2);
     load_weight_image(wc + 64 * 32 + 64 * 64, 16, 64, smem + kSmW_C3);
-    if (row == 0) {
+    if (row == 0 && group % kPair == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -211,7 +218,7 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
         uint32_t off = 0;
         for (int l = 0; l < n_staged; ++l) {
             const uint32_t words = net.level[l].size * (F / 2);
-            const uint32_t* src = reinterpret_cast<const uint32_t*>(table) + (size_t)net.level[l].offset * (F / 2);
+            const uint32_t* src = reinterpret_cast<const uint32_t*>(table) + (size_t)net.level[l].offset * (F / 2);   // fp16 table only
             for (uint32_t i = tid; i < words; i += kTcBlock) stage[off + i] = __ldg(src + i);
             if (tid == 0) enc_meta->level[l].base = stage + off;
             off += words;
@@ -232,13 +239,15 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
 
     // One dense layer: K/16 instructions over the A image in the activation region and a B image (n_out rows).
     auto issue_layer = [&](uint32_t b_img, uint32_t n_out, int k16, uint32_t idesc) {
-        if (row == 0) {
+        if (row == 0 && group % kPair == 0) {
             tc_fence_after();
-            for (int kk = 0; kk < k16; ++kk) {
-                const uint64_t da = make_desc(act_addr + (uint32_t)kk * 2u * kALbo, kALbo, kSbo);
-                const uint64_t db = make_desc(b_img + (uint32_t)kk * 2u * n_out * 16u, n_out * 16u, kSbo);
-                mma_f16(tmem_group, da, db, idesc, kk > 0 ? 1u : 0u);
-            }
+#pragma unroll
+            for (int u = 0; u < kPair; ++u)
+                for (int kk = 0; kk < k16; ++kk) {
+                    const uint64_t da = make_desc(act_addr + (uint32_t)u * kActBytes + (uint32_t)kk * 2u * kALbo, kALbo, kSbo);
+                    const uint64_t db = make_desc(b_img + (uint32_t)kk * 2u * n_out * 16u, n_out * 16u, kSbo);
+                    mma_f16(tmem_group + (uint32_t)u * 64u, da, db, idesc, kk > 0 ? 1u : 0u);
+                }
             mma_commit(bar);
         }
     };
@@ -259,13 +268,15 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
     // barrier of group_any() instead of spending issue slots on a spin loop.
     auto wait_layer = [&]() -> bool {
         bool expired = false;
-        if ((warp & 3) == 0) expired = !mbar_wait(bar, phase);
+        if ((warp & (4 * kPair - 1)) == 0) expired = !mbar_wait(bar, phase);
         phase ^= 1;
         return !group_any(group, expired);
     };
     const uint64_t n_tiles = (n + kGroup - 1) / kGroup;
     const uint64_t tile_stride = (uint64_t)gridDim.x * kGroups;
-    for (uint64_t tile = (uint64_t)blockIdx.x * kGroups + group; tile < n_tiles; tile += tile_stride) {
+    // The groups of a set run the same number of rounds (a group whose tile lies past the end works on zeros).
+    for (uint64_t tile0 = (uint64_t)blockIdx.x * kGroups + group / kPair * kPair; tile0 < n_tiles; tile0 += tile_stride) {
+        const uint64_t tile = tile0 + group % kPair;
         const uint64_t s = tile * kGroup + row;
         // ---- encode: one thread per sample, written as 16-byte units of the A image ----
         float x = 0.f, y = 0.f, z = 0.f, dx = 0.5f, dy = 0.5f, dz = 0.5f;
@@ -286,7 +297,7 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
         }
         {
             uint32_t enc[16];
-            hash_encode_packed<F>(enc_meta, table, x, y, z, enc);
+            hash_encode_packed<F, T32>(enc_meta, table, x, y, z, enc);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
                 *reinterpret_cast<uint4*>(act + ((size_t)j * 128 + row) * 16) =
@@ -370,10 +381,13 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
                 const uint32_t bs = (pack2(__uint_as_float(acc[2]), 0.f) & 0xffffu) | (sigma_half << 16);
                 if (FRAME || shaded) {
                     // frame path: activations evaluated here, on the fp16-rounded network outputs
-                    const __half2 h0 = *reinterpret_cast<const __half2*>(&rg), h1 = *reinterpret_cast<const __half2*>(&bs);
-                    const float raw[4] = {__low2float(h0), __high2float(h0), __low2float(h1), __high2float(h1)};
-                    {
-                        const float4 p = pos_dt[s];                  // re-read (L2) instead of holding four registers
+                    const float4 p = pos_dt[s];                      // re-read (L2) instead of holding four registers
+                    if (act_lut) {
+                        shaded[s] = shade_sample_lut(g, v, act_lut, rg & 0xffffu, rg >> 16, bs & 0xffffu, sigma_half, p.w,
+                                                     mk3(p.x, p.y, p.z));
+                    } else {
+                        const __half2 h0 = *reinterpret_cast<const __half2*>(&rg), h1 = *reinterpret_cast<const __half2*>(&bs);
+                        const float raw[4] = {__low2float(h0), __high2float(h0), __low2float(h1), __high2float(h1)};
                         shaded[s] = shade_sample(g, v, raw, p.w, mk3(p.x, p.y, p.z));
                     }
                 } else {
@@ -389,20 +403,80 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(kTmemCols) : "memory");
 }
 
+__global__ void k_table_to_f32(const __half* __restrict__ in, size_t n, float* __restrict__ out) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = __half2float(in[i]);
+}
+
+__global__ void k_build_activation_table(const DevCfg g, float* __restrict__ lut) {
+    const uint32_t h = blockIdx.x * blockDim.x + threadIdx.x;
+    if (h >= 65536u) return;
+    const float x = __half2float(__ushort_as_half((unsigned short)h));
+    lut[h] = network_to_rgb(x, g.rgb_activation);
+    lut[65536 + h] = network_to_density(x, g.density_activation);
+}
+
+// One thread per cell of level l: the entries of the cell's eight corners, in corner order.
+template <int F>
+__global__ void k_build_cell_table(const NetMeta net, const __half* __restrict__ table, int l, uint4* __restrict__ out) {
+    const LevelMeta L = net.level[l];
+    const uint32_t* words = reinterpret_cast<const uint32_t*>(table) + (size_t)L.offset * (F / 2);
+    const uint64_t n_cells = (uint64_t)L.res * L.res * L.res;
+    for (uint64_t c = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; c < n_cells; c += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t cx = (uint32_t)(c % L.res), cy = (uint32_t)((c / L.res) % L.res), cz = (uint32_t)(c / ((uint64_t)L.res * L.res));
+        uint32_t w[8 * (F / 2)];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t i = corner_index(L, cx + (k & 1), cy + ((k >> 1) & 1), cz + (k >> 2));
+#pragma unroll
+            for (int f = 0; f < F / 2; ++f) w[k * (F / 2) + f] = words[(size_t)i * (F / 2) + f];
+        }
+#pragma unroll
+        for (int q = 0; q < F; ++q) out[c * F + q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+    }
+}
+
 }  // namespace
+
+size_t cell_table_units(const NetMeta& net, int n_levels, unsigned long long* offsets) {
+    size_t units = 0;
+    for (int l = 0; l < n_levels && l < (int)net.n_levels; ++l) {
+        if (offsets) offsets[l] = units;
+        units += (size_t)net.level[l].res * net.level[l].res * net.level[l].res * net.n_features;
+    }
+    return units;
+}
+
+void launch_build_cell_tables(const NetMeta& net, const __half* table, int n_levels, uint4* out, cudaStream_t stream) {
+    unsigned long long off[kMaxLevels];
+    cell_table_units(net, n_levels, off);
+    for (int l = 0; l < n_levels && l < (int)net.n_levels; ++l) {
+        if (net.n_features == 2) k_build_cell_table<2><<<148 * 8, 256, 0, stream>>>(net, table, l, out + off[l]);
+        else k_build_cell_table<4><<<148 * 8, 256, 0, stream>>>(net, table, l, out + off[l]);
+    }
+}
+
+void launch_build_activation_table(const DevCfg& g, float* lut, cudaStream_t stream) {
+    k_build_activation_table<<<256, 256, 0, stream>>>(g, lut);
+}
+
+void launch_table_to_f32(const __half* table, size_t n, float* out, cudaStream_t stream) {
+    if (n) k_table_to_f32<<<148 * 8, 256, 0, stream>>>(table, n, out);
+}
 
 void launch_field_network_tc(const NetMeta& net, const __half* table, const __half* w_density, const __half* w_rgb,
                              const float4* pos_dt, const uint32_t* sample_ray, const float4* ray_dir_t,
                              const float* coords7, uint64_t n, uint2* rgbsigma, float4* shaded, const DevCfg* g,
                              const DevView* v, unsigned int* error_flags, cudaStream_t stream,
-                             const uint32_t* n_chunks_dev, uint32_t ray_shift, const uint4* ray_sh) {
+                             const uint32_t* n_chunks_dev, uint32_t ray_shift, const uint4* ray_sh,
+                             const float* table_f32, const uint4* cell_table, int n_cell_levels, const float* act_lut) {
     if (n == 0 && !n_chunks_dev) return;
     // Staged levels: as many leading dense levels as fit into `stage_budget` bytes of shared memory (default: none).
     // Shared memory taken here is L1 taken from the gathers of the other levels.
     static const long stage_budget = [] { const char* e = getenv("SRF_B200_STAGE_BYTES"); return e ? atol(e) : 0l; }();
     int n_staged = 0;
     size_t stage_bytes = 0;
-    for (uint32_t l = 0; l < net.n_levels && net.level[l].dense; ++l) {
+    for (uint32_t l = 0; !table_f32 && l < net.n_levels && net.level[l].dense; ++l) {
         const size_t b = (size_t)net.level[l].size * net.n_features * sizeof(__half);
         if ((long)(stage_bytes + b) > stage_budget || kSmTotal + stage_bytes + b > (size_t)kSmLimit) break;
         stage_bytes += b; ++n_staged;
@@ -411,8 +485,10 @@ void launch_field_network_tc(const NetMeta& net, const __half* table, const __ha
     // per device and cheap: set on every launch rather than cached per process
     // no more shared memory than the CTA needs: the rest of the unified array serves the gathers as L1
     const int carveout = (smem_bytes * 100 + 228 * 1024 - 1) / (228 * 1024);
-    const void* kernels[4] = {(const void*)k_field_network_tc<2, true>, (const void*)k_field_network_tc<2, false>,
-                              (const void*)k_field_network_tc<4, true>, (const void*)k_field_network_tc<4, false>};
+    const void* kernels[] = {(const void*)k_field_network_tc<2, true, false>, (const void*)k_field_network_tc<2, false, false>,
+                             (const void*)k_field_network_tc<4, true, false>, (const void*)k_field_network_tc<4, false, false>,
+                             (const void*)k_field_network_tc<2, true, true>, (const void*)k_field_network_tc<2, false, true>,
+                             (const void*)k_field_network_tc<4, true, true>, (const void*)k_field_network_tc<4, false, true>};
     for (const void* k : kernels) {
         cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, carveout);
@@ -428,11 +504,21 @@ void launch_field_network_tc(const NetMeta& net, const __half* table, const __ha
     if (g) g0 = *g;
     if (v) v0 = *v;
     const bool frame = shaded && ray_sh && pos_dt && sample_ray && !coords7;
-#define SRF_TC_LAUNCH(FEAT, FRAME)                                                                                          \
-    k_field_network_tc<FEAT, FRAME><<<grid, kTcBlock, smem_bytes, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, \
-        ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0, error_flags, n_chunks_dev, ray_shift, ray_sh, n_staged)
-    if (net.n_features == 2) { if (frame) SRF_TC_LAUNCH(2, true); else SRF_TC_LAUNCH(2, false); }
-    else { if (frame) SRF_TC_LAUNCH(4, true); else SRF_TC_LAUNCH(4, false); }
+    const void* tab = table_f32 ? (const void*)table_f32 : (const void*)table;
+    CellTables ct;
+    memset(&ct, 0, sizeof(ct));
+    if (cell_table && n_cell_levels > 0 && !table_f32) {
+        ct.base = cell_table;
+        ct.n_levels = n_cell_levels < (int)net.n_levels ? n_cell_levels : (int)net.n_levels;
+        cell_table_units(net, ct.n_levels, ct.offset);
+    }
+#define SRF_TC_LAUNCH(FEAT, FRAME, T32)                                                                                     \
+    k_field_network_tc<FEAT, FRAME, T32><<<grid, kTcBlock, smem_bytes, stream>>>(net, tab, w_density, w_rgb, pos_dt, sample_ray, \
+        ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0, error_flags, n_chunks_dev, ray_shift, ray_sh, n_staged, ct, act_lut)
+#define SRF_TC_LAUNCH2(FEAT, FRAME) do { if (table_f32) SRF_TC_LAUNCH(FEAT, FRAME, true); else SRF_TC_LAUNCH(FEAT, FRAME, false); } while (0)
+    if (net.n_features == 2) { if (frame) SRF_TC_LAUNCH2(2, true); else SRF_TC_LAUNCH2(2, false); }
+    else { if (frame) SRF_TC_LAUNCH2(4, true); else SRF_TC_LAUNCH2(4, false); }
+#undef SRF_TC_LAUNCH2
 #undef SRF_TC_LAUNCH
 }
 

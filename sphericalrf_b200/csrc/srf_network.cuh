@@ -25,21 +25,42 @@ struct EncLevel {
     uint32_t res, r2, size, mask, pad;   // mask = size - 1 (hashed levels hold 2^k entries)
     const uint32_t* base;                // first entry of the level, as 32-bit words
 };
+struct __align__(16) EncCellLevel {      // what a read from a level's cell-major copy needs: one 16-byte load
+    float scale;
+    uint32_t res;
+    const uint4* cells;                  // record of cell (0, 0, 0)
+};
 struct EncMeta {
     EncLevel level[kMaxLevels];
+    EncCellLevel cell[kMaxLevels];
     int n_levels, n_dense;               // levels [0, n_dense) are dense, the rest hashed
     int n_staged;                        // levels [0, n_staged) were copied to shared memory (their base points there)
+    int n_cell;                          // levels [0, n_cell) have a cell-major copy
+};
+
+// Cell-major copies of the leading levels (optional): for every cell (cx, cy, cz) of a level, cx + res*(cy + res*cz),
+// the fp16 entries of its eight corners in corner order, so that a sample reads one 16*F-byte record per level instead
+// of eight scattered entries.  Same numbers as the table: the copy is rebuilt whenever the table is uploaded.
+struct CellTables {
+    const uint4* base;
+    unsigned long long offset[kMaxLevels];     // first record of the level, in uint4 units
+    int n_levels;
 };
 
 // Filled once per CTA (all threads call it, followed by a barrier the caller provides).
 // Dense levels always precede hashed ones: the resolution grows with the level.
-__device__ __forceinline__ void prepare_enc_meta(const NetMeta& net, const __half* __restrict__ table, EncMeta* m) {
+// `words_per_entry`: 32-bit words one table entry occupies in the array behind `table` (n_features/2 for the fp16
+// table, n_features for its fp32 copy).
+__device__ __forceinline__ void prepare_enc_meta(const NetMeta& net, const void* __restrict__ table, EncMeta* m,
+                                                 uint32_t words_per_entry = 0) {
+    if (words_per_entry == 0) words_per_entry = net.n_features / 2;
     const int t = threadIdx.x;
     if (t < (int)net.n_levels) {
         const LevelMeta& L = net.level[t];
         m->level[t].scale = L.scale; m->level[t].res = L.res; m->level[t].r2 = L.res * L.res;
         m->level[t].size = L.size; m->level[t].mask = L.size - 1u; m->level[t].pad = 0u;
-        m->level[t].base = reinterpret_cast<const uint32_t*>(table) + (size_t)L.offset * (net.n_features / 2);
+        m->level[t].base = reinterpret_cast<const uint32_t*>(table) + (size_t)L.offset * words_per_entry;
+        m->cell[t].scale = L.scale; m->cell[t].res = L.res; m->cell[t].cells = nullptr;
     }
     if (t == 0) {
         int d = 0;
@@ -47,7 +68,25 @@ __device__ __forceinline__ void prepare_enc_meta(const NetMeta& net, const __hal
         m->n_levels = (int)net.n_levels;
         m->n_dense = d;
         m->n_staged = 0;
+        m->n_cell = 0;
     }
+}
+
+// After prepare_enc_meta and a barrier: points the leading levels at their cell-major copies.
+__device__ __forceinline__ void attach_cell_tables(const CellTables& ct, EncMeta* m) {
+    const int t = threadIdx.x;
+    if (ct.base && t < ct.n_levels) m->cell[t].cells = ct.base + ct.offset[t];
+    if (ct.base && t == 0) m->n_cell = ct.n_levels;
+}
+
+// Index of corner (x, y, z) in a level, as the encoder computes it.
+__device__ __forceinline__ uint32_t corner_index(const LevelMeta& L, uint32_t x, uint32_t y, uint32_t z) {
+    if (L.dense) {
+        uint32_t i = x + y * L.res + z * L.res * L.res;
+        if (i >= L.size) i %= L.size;
+        return i;
+    }
+    return (x ^ (y * 2654435761u) ^ (z * 805459861u)) & (L.size - 1u);
 }
 
 struct LevelCell {
@@ -64,8 +103,25 @@ __device__ __forceinline__ LevelCell level_cell(float scale, float x, float y, f
     return c;
 }
 
-template <int F>
-__device__ __forceinline__ void level_interpolate(const LevelCell& c, const uint32_t (&raw)[8][F / 2], float (&acc)[F]) {
+// Entries are read either from the fp16 table (T32 = false: one 32-bit word holds two features) or from its fp32
+// copy (T32 = true: one word per feature, no conversion; the values are the same numbers).
+template <int F, bool T32>
+__device__ __forceinline__ void load_entry(const uint32_t* base, uint32_t idx, uint32_t (&raw)[T32 ? F : F / 2]) {
+    if constexpr (!T32) {
+        const uint32_t* e = base + (size_t)idx * (F / 2);
+#pragma unroll
+        for (int f = 0; f < F / 2; ++f) raw[f] = __ldg(e + f);
+    } else if constexpr (F == 2) {
+        const uint2 v = __ldg(reinterpret_cast<const uint2*>(base) + idx);
+        raw[0] = v.x; raw[1] = v.y;
+    } else {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(base) + idx);
+        raw[0] = v.x; raw[1] = v.y; raw[2] = v.z; raw[3] = v.w;
+    }
+}
+
+template <int F, bool T32 = false>
+__device__ __forceinline__ void level_interpolate(const LevelCell& c, const uint32_t (&raw)[8][T32 ? F : F / 2], float (&acc)[F]) {
     const float ux = 1.f - c.wx, uy = 1.f - c.wy, uz = 1.f - c.wz;
     const float wxy[4] = {ux * uy, c.wx * uy, ux * c.wy, c.wx * c.wy};
 #pragma unroll
@@ -73,19 +129,24 @@ __device__ __forceinline__ void level_interpolate(const LevelCell& c, const uint
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
         const float wt = wxy[k & 3] * ((k & 4) ? c.wz : uz);
+        if constexpr (T32) {
 #pragma unroll
-        for (int f = 0; f < F / 2; ++f) {
-            const __half2 h = *reinterpret_cast<const __half2*>(&raw[k][f]);
-            acc[2 * f] = fmaf(wt, __low2float(h), acc[2 * f]);
-            acc[2 * f + 1] = fmaf(wt, __high2float(h), acc[2 * f + 1]);
+            for (int f = 0; f < F; ++f) acc[f] = fmaf(wt, __uint_as_float(raw[k][f]), acc[f]);
+        } else {
+#pragma unroll
+            for (int f = 0; f < F / 2; ++f) {
+                const __half2 h = *reinterpret_cast<const __half2*>(&raw[k][f]);
+                acc[2 * f] = fmaf(wt, __low2float(h), acc[2 * f]);
+                acc[2 * f + 1] = fmaf(wt, __high2float(h), acc[2 * f + 1]);
+            }
         }
     }
 }
 
-template <int F>
-__device__ __forceinline__ void level_finish(const LevelCell& c, const uint32_t (&raw)[8][F / 2], int l, uint32_t (&out)[16]) {
+template <int F, bool T32 = false>
+__device__ __forceinline__ void level_finish(const LevelCell& c, const uint32_t (&raw)[8][T32 ? F : F / 2], int l, uint32_t (&out)[16]) {
     float acc[F];
-    level_interpolate<F>(c, raw, acc);
+    level_interpolate<F, T32>(c, raw, acc);
 #pragma unroll
     for (int f = 0; f < F / 2; ++f) {
         const __half2 h = __floats2half2_rn(acc[2 * f], acc[2 * f + 1]);
@@ -95,23 +156,27 @@ __device__ __forceinline__ void level_finish(const LevelCell& c, const uint32_t 
 
 // One dense level.  STAGED: the level's entries were copied to shared memory and `base` points there (plain loads);
 // otherwise they are read from global memory through the read-only path.
-template <int F, bool STAGED>
+template <int F, bool STAGED, bool T32 = false>
 __device__ __forceinline__ void dense_level(const EncMeta* m, int l, float x, float y, float z, uint32_t (&out)[16]) {
     const EncLevel L = m->level[l];
     const uint32_t* base = L.base;
     const LevelCell c = level_cell(L.scale, x, y, z);
     const uint32_t y0 = c.iy * L.res, z0 = c.iz * L.r2;
     const uint32_t xy[4] = {c.ix + y0, c.ix + 1u + y0, c.ix + y0 + L.res, c.ix + 1u + y0 + L.res};
-    uint32_t raw[8][F / 2];
+    uint32_t raw[8][T32 ? F : F / 2];
     // Fast path when the largest of the eight indices is inside the level (almost always).  The test must hold in
     // exact arithmetic, not modulo 2^32: a position far outside [0,1] gives cell coordinates near 2^32 whose sum
     // wraps back below the level size; cell coordinates below 4096 cannot wrap (dense levels have res <= 256).
     if ((c.ix | c.iy | c.iz) < 4096u && xy[3] + z0 + L.r2 < L.size) {
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-            const uint32_t* e = base + (size_t)(xy[k & 3] + ((k & 4) ? z0 + L.r2 : z0)) * (F / 2);
+            const uint32_t i = xy[k & 3] + ((k & 4) ? z0 + L.r2 : z0);
+            if constexpr (STAGED) {
 #pragma unroll
-            for (int f = 0; f < F / 2; ++f) raw[k][f] = STAGED ? e[f] : __ldg(e + f);
+                for (int f = 0; f < F / 2; ++f) raw[k][f] = base[(size_t)i * (F / 2) + f];
+            } else {
+                load_entry<F, T32>(base, i, raw[k]);
+            }
         }
     } else {                                 // cells touching the upper faces of a dense level
 #pragma unroll
@@ -121,9 +186,52 @@ __device__ __forceinline__ void dense_level(const EncMeta* m, int l, float x, fl
                 i -= L.size;
                 if (i >= L.size) i %= L.size;
             }
-            const uint32_t* e = base + (size_t)i * (F / 2);
+            if constexpr (STAGED) {
 #pragma unroll
-            for (int f = 0; f < F / 2; ++f) raw[k][f] = STAGED ? e[f] : __ldg(e + f);
+                for (int f = 0; f < F / 2; ++f) raw[k][f] = base[(size_t)i * (F / 2) + f];
+            } else {
+                load_entry<F, T32>(base, i, raw[k]);
+            }
+        }
+    }
+    level_finish<F, T32>(c, raw, l, out);
+}
+
+#ifndef SRF_CELL_UNROLL
+#define SRF_CELL_UNROLL 2
+#endif
+constexpr int kCellUnroll = SRF_CELL_UNROLL;
+
+// One level read from its cell-major copy.  Cells outside the level (positions outside [0,1]) take the scattered path.
+template <int F>
+__device__ __forceinline__ void cell_level(const EncMeta* m, int l, float x, float y, float z, uint32_t (&out)[16]) {
+    const EncCellLevel C = m->cell[l];
+    const LevelCell c = level_cell(C.scale, x, y, z);
+    uint32_t raw[8][F / 2];
+    if (c.ix < C.res && c.iy < C.res && c.iz < C.res) {
+        const uint4* e = C.cells + ((size_t)(c.iz * C.res + c.iy) * C.res + c.ix) * (size_t)F;     // 8 * F/2 words = F uint4
+        if constexpr (F == 2) {                   // one 32-byte record: a single 256-bit load
+            uint32_t* r = &raw[0][0];
+            asm("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "l"(e));
+        } else {
+#pragma unroll
+            for (int q = 0; q < F; ++q) {
+                const uint4 v = __ldg(e + q);
+                uint32_t* r = &raw[0][0] + 4 * q;
+                r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
+            }
+        }
+    } else {
+        const EncLevel L = m->level[l];
+        const bool dense = l < m->n_dense;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t cx = c.ix + (k & 1), cy = c.iy + ((k >> 1) & 1), cz = c.iz + (k >> 2);
+            uint32_t i;
+            if (dense) { i = cx + cy * L.res + cz * L.r2; if (i >= L.size) i %= L.size; }
+            else i = (cx ^ (cy * 2654435761u) ^ (cz * 805459861u)) & L.mask;
+            load_entry<F, false>(L.base, i, raw[k]);
         }
     }
     level_finish<F>(c, raw, l, out);
@@ -132,17 +240,25 @@ __device__ __forceinline__ void dense_level(const EncMeta* m, int l, float x, fl
 // Encodes levels [l_begin, l_end) of one position into the packed pairs out[l*F/2 ...] (pair i = features
 // 2i, 2i+1 of the 32-half encoding).  `m` lives in shared memory (prepare_enc_meta).  Callers that want to
 // interleave the encoding with other work call it on successive level ranges.
-template <int F>
-__device__ __forceinline__ void hash_encode_range(const EncMeta* m, const __half* __restrict__ table, float x, float y,
+template <int F, bool T32 = false>
+__device__ __forceinline__ void hash_encode_range(const EncMeta* m, const void* __restrict__ table, float x, float y,
                                                   float z, int l_begin, int l_end, uint32_t (&out)[16]) {
     (void)table;                                  // the level bases in `m` were derived from it
     const int n_dense = m->n_dense;
+    if constexpr (!T32) {
+        const int cell_end = l_end < m->n_cell ? l_end : m->n_cell;
+#pragma unroll kCellUnroll
+        for (int l = l_begin; l < cell_end; ++l) cell_level<F>(m, l, x, y, z, out);
+        if (l_begin < cell_end) l_begin = cell_end;
+    }
     const int dense_end = l_end < n_dense ? l_end : n_dense;
     const int staged_end = dense_end < m->n_staged ? dense_end : m->n_staged;
 #pragma unroll 1
-    for (int l = l_begin; l < staged_end; ++l) dense_level<F, true>(m, l, x, y, z, out);
+    for (int l = l_begin; l < staged_end; ++l) {
+        if constexpr (!T32) dense_level<F, true>(m, l, x, y, z, out);          // only the fp16 table is ever staged
+    }
 #pragma unroll 1
-    for (int l = l_begin > staged_end ? l_begin : staged_end; l < dense_end; ++l) dense_level<F, false>(m, l, x, y, z, out);
+    for (int l = l_begin > staged_end ? l_begin : staged_end; l < dense_end; ++l) dense_level<F, false, T32>(m, l, x, y, z, out);
 #pragma unroll 3
     for (int l = l_begin > n_dense ? l_begin : n_dense; l < l_end; ++l) {
         const float scale = m->level[l].scale;
@@ -152,42 +268,18 @@ __device__ __forceinline__ void hash_encode_range(const EncMeta* m, const __half
         const uint32_t y0 = c.iy * 2654435761u, y1 = y0 + 2654435761u;
         const uint32_t z0 = c.iz * 805459861u, z1 = z0 + 805459861u;
         const uint32_t xy[4] = {c.ix ^ y0, (c.ix + 1u) ^ y0, c.ix ^ y1, (c.ix + 1u) ^ y1};
-        uint32_t raw[8][F / 2];
+        uint32_t raw[8][T32 ? F : F / 2];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const uint32_t* e = base + (size_t)((xy[k & 3] ^ ((k & 4) ? z1 : z0)) & mask) * (F / 2);
-#pragma unroll
-            for (int f = 0; f < F / 2; ++f) raw[k][f] = __ldg(e + f);
-        }
-        level_finish<F>(c, raw, l, out);
+        for (int k = 0; k < 8; ++k) load_entry<F, T32>(base, (xy[k & 3] ^ ((k & 4) ? z1 : z0)) & mask, raw[k]);
+        level_finish<F, T32>(c, raw, l, out);
     }
-}
-
-// One hashed level (the level holds 2^k entries).
-template <int F>
-__device__ __forceinline__ void hashed_level(const EncMeta* m, int l, float x, float y, float z, uint32_t (&out)[16]) {
-    const float scale = m->level[l].scale;
-    const uint32_t mask = m->level[l].mask;
-    const uint32_t* base = m->level[l].base;
-    const LevelCell c = level_cell(scale, x, y, z);
-    const uint32_t y0 = c.iy * 2654435761u, y1 = y0 + 2654435761u;
-    const uint32_t z0 = c.iz * 805459861u, z1 = z0 + 805459861u;
-    const uint32_t xy[4] = {c.ix ^ y0, (c.ix + 1u) ^ y0, c.ix ^ y1, (c.ix + 1u) ^ y1};
-    uint32_t raw[8][F / 2];
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        const uint32_t* e = base + (size_t)((xy[k & 3] ^ ((k & 4) ? z1 : z0)) & mask) * (F / 2);
-#pragma unroll
-        for (int f = 0; f < F / 2; ++f) raw[k][f] = __ldg(e + f);
-    }
-    level_finish<F>(c, raw, l, out);
 }
 
 // Encodes one position into 32 halves, returned as 16 packed pairs.
-template <int F>
-__device__ __forceinline__ void hash_encode_packed(const EncMeta* m, const __half* __restrict__ table, float x, float y,
+template <int F, bool T32 = false>
+__device__ __forceinline__ void hash_encode_packed(const EncMeta* m, const void* __restrict__ table, float x, float y,
                                                    float z, uint32_t (&out)[16]) {
-    hash_encode_range<F>(m, table, x, y, z, 0, m->n_levels, out);
+    hash_encode_range<F, T32>(m, table, x, y, z, 0, m->n_levels, out);
 }
 
 // Same, written as 32 consecutive halves.

@@ -151,6 +151,10 @@ class Renderer:
                                      None if stats is None else C.byref(stats)))
         return (img, stats.as_dict()) if want_stats else img
 
+    def set_cell_table_budget(self, n_bytes):
+        """Bytes the frame path may spend on cell-major copies of the leading hash-grid levels (0 = none)."""
+        self._ck(self.lib.srf_set_cell_table_budget(self.ctx, int(n_bytes)))
+
     def set_wave_schedule(self, steps):
         """March steps per ray of the leading waves of a frame ([] = one pass); see srf_set_wave_schedule."""
         a = (C.c_uint32 * max(len(steps), 1))(*steps)

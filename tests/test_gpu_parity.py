@@ -5,7 +5,7 @@ order is unspecified) and bit-exact (checked as <= 1e-5) for the fp32 analytic f
 import numpy as np
 import pytest
 
-from sphericalrf_b200 import abi
+from sphericalrf_b200 import abi, synth
 
 from helpers import make_oracle, make_renderer, small_scene
 
@@ -463,3 +463,38 @@ def test_waves_change_nothing_but_the_work(built_lib, monkeypatch, kind, budgets
     monkeypatch.setenv("SRF_B200_WAVES", "0")
     counts_one = make_renderer(sc).render_frame(sc["view"], post, want_counts=True)["n_samples"]
     assert np.array_equal(counts_waves, counts_one) and int(counts_one.sum()) == s1["n_samples"]
+
+
+@pytest.mark.parametrize("levels,features", [(16, 2), (8, 4)])
+def test_table_copies_change_nothing(built_lib, monkeypatch, levels, features):
+    """Cell-major copies of the leading hash-grid levels (dense and hashed ones) and the tabulated activations are
+    memory layouts, not arithmetic: frames, raw network outputs (also for coordinates outside the unit cube, which take
+    the scattered path) and the frame after a second srf_upload_network are byte-identical with and without them."""
+    sc = small_scene(kind="net", width=24, height=16)
+    cfg = sc["cfg"]
+    cfg.n_levels = levels; cfg.n_features_per_level = features
+    t, d, c = synth.network_params(cfg, 11, 12, table_range=0.5)
+    sc.update(hash_table=t, density_mlp=d, rgb_mlp=c)
+    t2, _, _ = synth.network_params(cfg, 21, 12, table_range=0.5)
+    rng = np.random.Generator(np.random.PCG64(5))
+    coords = rng.random((20000, 7), dtype=np.float32)
+    coords[:4000, :3] = coords[:4000, :3] * 3.0 - 1.0          # outside [0,1]: cells outside the levels
+    coords[4000:4100, :3] = np.array([1.0, 1.0, 1.0], np.float32)
+    coords[4100:4200, :3] = 0.0
+    post = abi.default_post()
+    out = {}
+    for key in ("plain", "copies"):
+        monkeypatch.setenv("SRF_B200_ACT_LUT", "0" if key == "plain" else "1")
+        r = make_renderer(sc)
+        r.set_cell_table_budget(0 if key == "plain" else 96 << 20)
+        a = r.render_frame(sc["view"], post, want_raw=True)
+        v3 = abi.View.from_buffer_copy(sc["view"]); v3.render_mode = abi.MODE_AO
+        b = r.render_frame(v3, post, want_raw=True)
+        raw = r.network_inference(coords)
+        r.upload_network(t2, sc["density_mlp"], sc["rgb_mlp"])
+        a2 = r.render_frame(sc["view"], post, want_raw=True)
+        out[key] = (a["out"], a["rgba_raw"], b["out"], raw.view(np.uint16), a2["out"], a2["rgba_raw"])
+        r.check_errors()
+    for x, y in zip(out["plain"], out["copies"]):
+        assert _bits_equal(np.asarray(x), np.asarray(y))
+    assert not _bits_equal(out["copies"][0], out["copies"][4])      # the second upload did change the picture
