@@ -57,7 +57,6 @@ struct srf_ctx {
     uint32_t* skip_yz = nullptr;
     bool skip_capable = false;
     __half* table = nullptr;
-    float* table_f32 = nullptr;          // fp32 copy of the table for the tcgen05 field kernel (optional)
     uint4* cell_table = nullptr;         // cell-major copies of the leading levels of the table (see CellTables)
     int n_cell_levels = 0;               // levels the allocation covers
     uint64_t cell_budget = 4ull << 30;   // bytes the copies may take (srf_set_cell_table_budget); 0: none
@@ -510,10 +509,6 @@ srf_status srf_create(const srf_config_t* cfg, int device, srf_ctx** out) {
             launch_build_activation_table(ctx->g, ctx->act_lut, 0);
             CK_CREATE(cudaDeviceSynchronize());
         }
-        if (const char* e = getenv("SRF_B200_TABLE_F32")) {
-            if (atoi(e) != 0)
-                CK_CREATE(cudaMalloc((void**)&ctx->table_f32, (size_t)ctx->n_table_entries * cfg->n_features_per_level * sizeof(float)));
-        }
         CK_CREATE(cudaMalloc((void**)&ctx->w_density, (64 * 32 + 16 * 64) * sizeof(__half)));
         CK_CREATE(cudaMalloc((void**)&ctx->w_rgb, (64 * 32 + 64 * 64 + 16 * 64) * sizeof(__half)));
     }
@@ -536,7 +531,7 @@ srf_status srf_create(const srf_config_t* cfg, int device, srf_ctx** out) {
 void srf_destroy(srf_ctx* ctx) {
     if (!ctx) return;
     DeviceGuard guard(ctx->device);
-    void* ptrs[] = {ctx->grid, ctx->grid_current, ctx->partial_a, ctx->partial_b, ctx->mean, ctx->bits, ctx->table, ctx->table_f32, ctx->cell_table, ctx->act_lut,
+    void* ptrs[] = {ctx->grid, ctx->grid_current, ctx->partial_a, ctx->partial_b, ctx->mean, ctx->bits, ctx->table, ctx->cell_table, ctx->act_lut,
                     ctx->w_density, ctx->w_rgb, ctx->skip_shell, ctx->skip_yz, ctx->train_flags.p, ctx->train_rank.p, ctx->loss_rgb.p, ctx->ray_sh.p, ctx->ray_ordinal.p, ctx->ray_total.p, ctx->ray_rgba.p, ctx->ray_ncomp.p, ctx->blobs, ctx->cmap, ctx->d_counters, ctx->ray_dir_t.p, ctx->ray_end.p,
                     ctx->counts.p, ctx->offsets.p, ctx->scan_scratch.p, ctx->pos_dt.p, ctx->sample_ray.p, ctx->rgbs.p,
                     ctx->img_out.p, ctx->img_accum.p, ctx->pool_pos.p, ctx->pool_shaded.p, ctx->chunk_ray.p, ctx->chunk_next.p,
@@ -578,10 +573,6 @@ srf_status srf_upload_network(srf_ctx* ctx, const uint16_t* h_table, size_t n_ta
     if (n_c != 64 * 32 + 64 * 64 + 16 * 64) return fail(ctx, SRF_ERR_ARG, "colour MLP must hold 64x32 + 64x64 + 16x64 halves");
     DeviceGuard guard(ctx->device);
     SRF_CK(ctx, cudaMemcpy(ctx->table, h_table, n_table * sizeof(__half), cudaMemcpyHostToDevice));
-    if (ctx->table_f32) {
-        launch_table_to_f32(ctx->table, n_table, ctx->table_f32, 0);
-        SRF_CK(ctx, cudaDeviceSynchronize());
-    }
     ctx->cell_dirty = true;
     SRF_CK(ctx, cudaMemcpy(ctx->w_density, h_d, n_d * sizeof(__half), cudaMemcpyHostToDevice));
     SRF_CK(ctx, cudaMemcpy(ctx->w_rgb, h_c, n_c * sizeof(__half), cudaMemcpyHostToDevice));
@@ -929,7 +920,7 @@ srf_status srf_sample_emit(srf_ctx* ctx, const srf_view_t* view, const uint64_t*
 // Cell-major copies of as many leading levels as the budget allows, (re)built on `stream` when the table changed.
 static srf_status ensure_cell_tables(srf_ctx* ctx, cudaStream_t stream) {
     int want = 0;
-    if (ctx->use_tcgen05 && !ctx->table_f32) {
+    if (ctx->use_tcgen05) {
         for (int l = 1; l <= (int)ctx->net.n_levels; ++l) {
             if (ctx->cell_levels_forced >= 0 ? l > ctx->cell_levels_forced
                                              : cell_table_units(ctx->net, l, nullptr) * sizeof(uint4) > ctx->cell_budget) break;
@@ -969,7 +960,7 @@ srf_status srf_network_inference(srf_ctx* ctx, const float* d_coords, uint64_t n
     if (ctx->use_tcgen05)
         launch_field_network_tc(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, nullptr, nullptr, nullptr, d_coords, n,
                                 (uint2*)d_rgbsigma, nullptr, nullptr, nullptr, &ctx->d_counters->error_flags, (cudaStream_t)stream,
-                                nullptr, 0, nullptr, ctx->table_f32, ctx->cell_table, ctx->n_cell_levels);
+                                nullptr, 0, nullptr, ctx->cell_table, ctx->n_cell_levels);
     else
         launch_field_network(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, nullptr, nullptr, nullptr, d_coords, n,
                              (uint2*)d_rgbsigma, nullptr, nullptr, nullptr, (cudaStream_t)stream);
@@ -1104,7 +1095,7 @@ static srf_status render_frame_impl(srf_ctx* ctx, const srf_view_t* view, const 
                                         (const uint32_t*)ctx->chunk_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, 0, nullptr,
                                         (float4*)ctx->pool_shaded.p, &ctx->g, &v, &ctx->d_counters->error_flags, s,
                                         ctx->d_chunk_cursor, kChunkShift, sh_per_ray ? (const uint4*)ctx->ray_sh.p : nullptr,
-                                        ctx->table_f32, ctx->cell_table, ctx->n_cell_levels, ctx->act_lut);
+                                        ctx->cell_table, ctx->n_cell_levels, ctx->act_lut);
             else
                 launch_field_network(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, (const float4*)ctx->pool_pos.p,
                                      (const uint32_t*)ctx->chunk_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, 0, nullptr,

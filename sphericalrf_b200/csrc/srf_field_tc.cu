@@ -48,10 +48,8 @@ constexpr int kGroup = 128;
 constexpr int kTcBlock = kGroup * kGroups;
 constexpr uint32_t kTmemCols = 64 * kGroups;      // 64 per group: the whole tensor memory of the SM
 constexpr uint32_t kWaitLimit = 1u << 20;
-#ifndef SRF_TC_PAIR
-#define SRF_TC_PAIR 1
-#endif
-constexpr int kPair = SRF_TC_PAIR;                // groups that share one commit round trip per layer (1, 2 or 4)
+constexpr int kPair = 1;                          // groups that share one commit round trip per layer: sets of 2 and 4
+                                                  // groups were slower (159.5 and 181.9 ms against 153.1 per benchmark frame)
 
 // shared-memory map (bytes)
 constexpr int kSmW_D1 = 0;                        // [4][64][8]
@@ -172,10 +170,9 @@ __device__ __forceinline__ bool group_any(int group, bool v) {
 
 // FRAME: the frame path's argument set (paged pool records in, per-ray SH table, shaded records out), fixed at compile
 // time so that the stage entry points' alternatives cost it neither branches nor registers.
-// T32: `table` is the fp32 copy of the hash table (one 8- or 16-byte load per corner, no conversions).
-template <int F, bool FRAME, bool T32>
+template <int F, bool FRAME>
 __global__ void __launch_bounds__(kTcBlock, 1)
-k_field_network_tc(const NetMeta net, const void* __restrict__ table, const __half* __restrict__ wd,
+k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __half* __restrict__ wd,
                    const __half* __restrict__ wc, const float4* __restrict__ pos_dt,
                    const uint32_t* __restrict__ sample_ray, const float4* __restrict__ ray_dir_t,
                    const float* __restrict__ coords7, uint64_t n, uint2* __restrict__ rgbsigma,
@@ -192,8 +189,8 @@ k_field_network_tc(const NetMeta net, const void* __restrict__ table, const __ha
     const uint32_t bar = smem_u32(bar_ptr);
 
     EncMeta* enc_meta = reinterpret_cast<EncMeta*>(smem + kSmEnc);
-    prepare_enc_meta(net, table, enc_meta, T32 ? F : F / 2);
-    if (!T32) attach_cell_tables(cells, enc_meta);
+    prepare_enc_meta(net, table, enc_meta);
+    attach_cell_tables(cells, enc_meta);
     load_weight_image(wd, 64, 32, smem + kSmW_D1);
     load_weight_image(wd + 64 * 32, 16, 64, smem + kSmW_D2);
     load_weight_image(wc, 64, 32, smem + kSmW_C1);
@@ -218,7 +215,7 @@ k_field_network_tc(const NetMeta net, const void* __restrict__ table, const __ha
         uint32_t off = 0;
         for (int l = 0; l < n_staged; ++l) {
             const uint32_t words = net.level[l].size * (F / 2);
-            const uint32_t* src = reinterpret_cast<const uint32_t*>(table) + (size_t)net.level[l].offset * (F / 2);   // fp16 table only
+            const uint32_t* src = reinterpret_cast<const uint32_t*>(table) + (size_t)net.level[l].offset * (F / 2); 
             for (uint32_t i = tid; i < words; i += kTcBlock) stage[off + i] = __ldg(src + i);
             if (tid == 0) enc_meta->level[l].base = stage + off;
             off += words;
@@ -297,7 +294,7 @@ k_field_network_tc(const NetMeta net, const void* __restrict__ table, const __ha
         }
         {
             uint32_t enc[16];
-            hash_encode_packed<F, T32>(enc_meta, table, x, y, z, enc);
+            hash_encode_packed<F>(enc_meta, table, x, y, z, enc);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
                 *reinterpret_cast<uint4*>(act + ((size_t)j * 128 + row) * 16) =
@@ -403,11 +400,6 @@ k_field_network_tc(const NetMeta net, const void* __restrict__ table, const __ha
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(kTmemCols) : "memory");
 }
 
-__global__ void k_table_to_f32(const __half* __restrict__ in, size_t n, float* __restrict__ out) {
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
-        out[i] = __half2float(in[i]);
-}
-
 __global__ void k_build_activation_table(const DevCfg g, float* __restrict__ lut) {
     const uint32_t h = blockIdx.x * blockDim.x + threadIdx.x;
     if (h >= 65536u) return;
@@ -460,23 +452,19 @@ void launch_build_activation_table(const DevCfg& g, float* lut, cudaStream_t str
     k_build_activation_table<<<256, 256, 0, stream>>>(g, lut);
 }
 
-void launch_table_to_f32(const __half* table, size_t n, float* out, cudaStream_t stream) {
-    if (n) k_table_to_f32<<<148 * 8, 256, 0, stream>>>(table, n, out);
-}
-
 void launch_field_network_tc(const NetMeta& net, const __half* table, const __half* w_density, const __half* w_rgb,
                              const float4* pos_dt, const uint32_t* sample_ray, const float4* ray_dir_t,
                              const float* coords7, uint64_t n, uint2* rgbsigma, float4* shaded, const DevCfg* g,
                              const DevView* v, unsigned int* error_flags, cudaStream_t stream,
                              const uint32_t* n_chunks_dev, uint32_t ray_shift, const uint4* ray_sh,
-                             const float* table_f32, const uint4* cell_table, int n_cell_levels, const float* act_lut) {
+                             const uint4* cell_table, int n_cell_levels, const float* act_lut) {
     if (n == 0 && !n_chunks_dev) return;
     // Staged levels: as many leading dense levels as fit into `stage_budget` bytes of shared memory (default: none).
     // Shared memory taken here is L1 taken from the gathers of the other levels.
     static const long stage_budget = [] { const char* e = getenv("SRF_B200_STAGE_BYTES"); return e ? atol(e) : 0l; }();
     int n_staged = 0;
     size_t stage_bytes = 0;
-    for (uint32_t l = 0; !table_f32 && l < net.n_levels && net.level[l].dense; ++l) {
+    for (uint32_t l = 0; l < net.n_levels && net.level[l].dense; ++l) {
         const size_t b = (size_t)net.level[l].size * net.n_features * sizeof(__half);
         if ((long)(stage_bytes + b) > stage_budget || kSmTotal + stage_bytes + b > (size_t)kSmLimit) break;
         stage_bytes += b; ++n_staged;
@@ -485,10 +473,8 @@ void launch_field_network_tc(const NetMeta& net, const __half* table, const __ha
     // per device and cheap: set on every launch rather than cached per process
     // no more shared memory than the CTA needs: the rest of the unified array serves the gathers as L1
     const int carveout = (smem_bytes * 100 + 228 * 1024 - 1) / (228 * 1024);
-    const void* kernels[] = {(const void*)k_field_network_tc<2, true, false>, (const void*)k_field_network_tc<2, false, false>,
-                             (const void*)k_field_network_tc<4, true, false>, (const void*)k_field_network_tc<4, false, false>,
-                             (const void*)k_field_network_tc<2, true, true>, (const void*)k_field_network_tc<2, false, true>,
-                             (const void*)k_field_network_tc<4, true, true>, (const void*)k_field_network_tc<4, false, true>};
+    const void* kernels[] = {(const void*)k_field_network_tc<2, true>, (const void*)k_field_network_tc<2, false>,
+                             (const void*)k_field_network_tc<4, true>, (const void*)k_field_network_tc<4, false>};
     for (const void* k : kernels) {
         cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, carveout);
@@ -504,21 +490,18 @@ void launch_field_network_tc(const NetMeta& net, const __half* table, const __ha
     if (g) g0 = *g;
     if (v) v0 = *v;
     const bool frame = shaded && ray_sh && pos_dt && sample_ray && !coords7;
-    const void* tab = table_f32 ? (const void*)table_f32 : (const void*)table;
     CellTables ct;
     memset(&ct, 0, sizeof(ct));
-    if (cell_table && n_cell_levels > 0 && !table_f32) {
+    if (cell_table && n_cell_levels > 0) {
         ct.base = cell_table;
         ct.n_levels = n_cell_levels < (int)net.n_levels ? n_cell_levels : (int)net.n_levels;
         cell_table_units(net, ct.n_levels, ct.offset);
     }
-#define SRF_TC_LAUNCH(FEAT, FRAME, T32)                                                                                     \
-    k_field_network_tc<FEAT, FRAME, T32><<<grid, kTcBlock, smem_bytes, stream>>>(net, tab, w_density, w_rgb, pos_dt, sample_ray, \
+#define SRF_TC_LAUNCH(FEAT, FRAME)                                                                                          \
+    k_field_network_tc<FEAT, FRAME><<<grid, kTcBlock, smem_bytes, stream>>>(net, table, w_density, w_rgb, pos_dt, sample_ray, \
         ray_dir_t, coords7, n, rgbsigma, shaded, g0, v0, error_flags, n_chunks_dev, ray_shift, ray_sh, n_staged, ct, act_lut)
-#define SRF_TC_LAUNCH2(FEAT, FRAME) do { if (table_f32) SRF_TC_LAUNCH(FEAT, FRAME, true); else SRF_TC_LAUNCH(FEAT, FRAME, false); } while (0)
-    if (net.n_features == 2) { if (frame) SRF_TC_LAUNCH2(2, true); else SRF_TC_LAUNCH2(2, false); }
-    else { if (frame) SRF_TC_LAUNCH2(4, true); else SRF_TC_LAUNCH2(4, false); }
-#undef SRF_TC_LAUNCH2
+    if (net.n_features == 2) { if (frame) SRF_TC_LAUNCH(2, true); else SRF_TC_LAUNCH(2, false); }
+    else { if (frame) SRF_TC_LAUNCH(4, true); else SRF_TC_LAUNCH(4, false); }
 #undef SRF_TC_LAUNCH
 }
 

@@ -88,7 +88,7 @@ void launch_field_network_tc(const NetMeta& net, const __half* table, const __ha
                              const float* coords7, uint64_t n, uint2* rgbsigma, float4* shaded, const DevCfg* g,
                              const DevView* v, unsigned int* error_flags, cudaStream_t stream,
                              const uint32_t* n_chunks_dev = nullptr, uint32_t ray_shift = 0, const uint4* ray_sh = nullptr,
-                             const float* table_f32 = nullptr, const uint4* cell_table = nullptr, int n_cell_levels = 0,
+                             const uint4* cell_table = nullptr, int n_cell_levels = 0,
                              const float* act_lut = nullptr);
 //   act_lut (frame path, optional): the two activation functions tabulated over all fp16 arguments
 //   (launch_build_activation_table: 2 x 65 536 floats).
@@ -97,8 +97,6 @@ void launch_build_activation_table(const DevCfg& g, float* lut, cudaStream_t str
 //   cell_table_units gives the size in 16-byte units and the per-level offsets).
 size_t cell_table_units(const NetMeta& net, int n_levels, unsigned long long* offsets);
 void launch_build_cell_tables(const NetMeta& net, const __half* table, int n_levels, uint4* out, cudaStream_t stream);
-//   table_f32 (optional): the hash table converted to fp32 (launch_table_to_f32); the gathers then read it instead.
-void launch_table_to_f32(const __half* table, size_t n, float* out, cudaStream_t stream);
 //   ray_sh (frame path, optional): the 16 spherical-harmonics halves of every ray's direction, written by the sampler.
 //   n_chunks_dev (frame path): the number of samples is *n_chunks_dev * kChunkSamples, read on the device, and
 //   the ray of sample s is sample_ray[s >> ray_shift] (one entry per chunk).

@@ -49,11 +49,8 @@ struct CellTables {
 
 // Filled once per CTA (all threads call it, followed by a barrier the caller provides).
 // Dense levels always precede hashed ones: the resolution grows with the level.
-// `words_per_entry`: 32-bit words one table entry occupies in the array behind `table` (n_features/2 for the fp16
-// table, n_features for its fp32 copy).
-__device__ __forceinline__ void prepare_enc_meta(const NetMeta& net, const void* __restrict__ table, EncMeta* m,
-                                                 uint32_t words_per_entry = 0) {
-    if (words_per_entry == 0) words_per_entry = net.n_features / 2;
+__device__ __forceinline__ void prepare_enc_meta(const NetMeta& net, const __half* __restrict__ table, EncMeta* m) {
+    const uint32_t words_per_entry = net.n_features / 2;
     const int t = threadIdx.x;
     if (t < (int)net.n_levels) {
         const LevelMeta& L = net.level[t];
@@ -103,25 +100,16 @@ __device__ __forceinline__ LevelCell level_cell(float scale, float x, float y, f
     return c;
 }
 
-// Entries are read either from the fp16 table (T32 = false: one 32-bit word holds two features) or from its fp32
-// copy (T32 = true: one word per feature, no conversion; the values are the same numbers).
-template <int F, bool T32>
-__device__ __forceinline__ void load_entry(const uint32_t* base, uint32_t idx, uint32_t (&raw)[T32 ? F : F / 2]) {
-    if constexpr (!T32) {
-        const uint32_t* e = base + (size_t)idx * (F / 2);
+// One entry of the table (F halves) through the read-only path.
+template <int F>
+__device__ __forceinline__ void load_entry(const uint32_t* base, uint32_t idx, uint32_t (&raw)[F / 2]) {
+    const uint32_t* e = base + (size_t)idx * (F / 2);
 #pragma unroll
-        for (int f = 0; f < F / 2; ++f) raw[f] = __ldg(e + f);
-    } else if constexpr (F == 2) {
-        const uint2 v = __ldg(reinterpret_cast<const uint2*>(base) + idx);
-        raw[0] = v.x; raw[1] = v.y;
-    } else {
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(base) + idx);
-        raw[0] = v.x; raw[1] = v.y; raw[2] = v.z; raw[3] = v.w;
-    }
+    for (int f = 0; f < F / 2; ++f) raw[f] = __ldg(e + f);
 }
 
-template <int F, bool T32 = false>
-__device__ __forceinline__ void level_interpolate(const LevelCell& c, const uint32_t (&raw)[8][T32 ? F : F / 2], float (&acc)[F]) {
+template <int F>
+__device__ __forceinline__ void level_interpolate(const LevelCell& c, const uint32_t (&raw)[8][F / 2], float (&acc)[F]) {
     const float ux = 1.f - c.wx, uy = 1.f - c.wy, uz = 1.f - c.wz;
     const float wxy[4] = {ux * uy, c.wx * uy, ux * c.wy, c.wx * c.wy};
 #pragma unroll
@@ -129,24 +117,19 @@ __device__ __forceinline__ void level_interpolate(const LevelCell& c, const uint
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
         const float wt = wxy[k & 3] * ((k & 4) ? c.wz : uz);
-        if constexpr (T32) {
 #pragma unroll
-            for (int f = 0; f < F; ++f) acc[f] = fmaf(wt, __uint_as_float(raw[k][f]), acc[f]);
-        } else {
-#pragma unroll
-            for (int f = 0; f < F / 2; ++f) {
-                const __half2 h = *reinterpret_cast<const __half2*>(&raw[k][f]);
-                acc[2 * f] = fmaf(wt, __low2float(h), acc[2 * f]);
-                acc[2 * f + 1] = fmaf(wt, __high2float(h), acc[2 * f + 1]);
-            }
+        for (int f = 0; f < F / 2; ++f) {
+            const __half2 h = *reinterpret_cast<const __half2*>(&raw[k][f]);
+            acc[2 * f] = fmaf(wt, __low2float(h), acc[2 * f]);
+            acc[2 * f + 1] = fmaf(wt, __high2float(h), acc[2 * f + 1]);
         }
     }
 }
 
-template <int F, bool T32 = false>
-__device__ __forceinline__ void level_finish(const LevelCell& c, const uint32_t (&raw)[8][T32 ? F : F / 2], int l, uint32_t (&out)[16]) {
+template <int F>
+__device__ __forceinline__ void level_finish(const LevelCell& c, const uint32_t (&raw)[8][F / 2], int l, uint32_t (&out)[16]) {
     float acc[F];
-    level_interpolate<F, T32>(c, raw, acc);
+    level_interpolate<F>(c, raw, acc);
 #pragma unroll
     for (int f = 0; f < F / 2; ++f) {
         const __half2 h = __floats2half2_rn(acc[2 * f], acc[2 * f + 1]);
@@ -156,14 +139,14 @@ __device__ __forceinline__ void level_finish(const LevelCell& c, const uint32_t 
 
 // One dense level.  STAGED: the level's entries were copied to shared memory and `base` points there (plain loads);
 // otherwise they are read from global memory through the read-only path.
-template <int F, bool STAGED, bool T32 = false>
+template <int F, bool STAGED>
 __device__ __forceinline__ void dense_level(const EncMeta* m, int l, float x, float y, float z, uint32_t (&out)[16]) {
     const EncLevel L = m->level[l];
     const uint32_t* base = L.base;
     const LevelCell c = level_cell(L.scale, x, y, z);
     const uint32_t y0 = c.iy * L.res, z0 = c.iz * L.r2;
     const uint32_t xy[4] = {c.ix + y0, c.ix + 1u + y0, c.ix + y0 + L.res, c.ix + 1u + y0 + L.res};
-    uint32_t raw[8][T32 ? F : F / 2];
+    uint32_t raw[8][F / 2];
     // Fast path when the largest of the eight indices is inside the level (almost always).  The test must hold in
     // exact arithmetic, not modulo 2^32: a position far outside [0,1] gives cell coordinates near 2^32 whose sum
     // wraps back below the level size; cell coordinates below 4096 cannot wrap (dense levels have res <= 256).
@@ -175,7 +158,7 @@ __device__ __forceinline__ void dense_level(const EncMeta* m, int l, float x, fl
 #pragma unroll
                 for (int f = 0; f < F / 2; ++f) raw[k][f] = base[(size_t)i * (F / 2) + f];
             } else {
-                load_entry<F, T32>(base, i, raw[k]);
+                load_entry<F>(base, i, raw[k]);
             }
         }
     } else {                                 // cells touching the upper faces of a dense level
@@ -190,17 +173,12 @@ __device__ __forceinline__ void dense_level(const EncMeta* m, int l, float x, fl
 #pragma unroll
                 for (int f = 0; f < F / 2; ++f) raw[k][f] = base[(size_t)i * (F / 2) + f];
             } else {
-                load_entry<F, T32>(base, i, raw[k]);
+                load_entry<F>(base, i, raw[k]);
             }
         }
     }
-    level_finish<F, T32>(c, raw, l, out);
+    level_finish<F>(c, raw, l, out);
 }
-
-#ifndef SRF_CELL_UNROLL
-#define SRF_CELL_UNROLL 2
-#endif
-constexpr int kCellUnroll = SRF_CELL_UNROLL;
 
 // One level read from its cell-major copy.  Cells outside the level (positions outside [0,1]) take the scattered path.
 template <int F>
@@ -231,7 +209,7 @@ __device__ __forceinline__ void cell_level(const EncMeta* m, int l, float x, flo
             uint32_t i;
             if (dense) { i = cx + cy * L.res + cz * L.r2; if (i >= L.size) i %= L.size; }
             else i = (cx ^ (cy * 2654435761u) ^ (cz * 805459861u)) & L.mask;
-            load_entry<F, false>(L.base, i, raw[k]);
+            load_entry<F>(L.base, i, raw[k]);
         }
     }
     level_finish<F>(c, raw, l, out);
@@ -240,25 +218,21 @@ __device__ __forceinline__ void cell_level(const EncMeta* m, int l, float x, flo
 // Encodes levels [l_begin, l_end) of one position into the packed pairs out[l*F/2 ...] (pair i = features
 // 2i, 2i+1 of the 32-half encoding).  `m` lives in shared memory (prepare_enc_meta).  Callers that want to
 // interleave the encoding with other work call it on successive level ranges.
-template <int F, bool T32 = false>
-__device__ __forceinline__ void hash_encode_range(const EncMeta* m, const void* __restrict__ table, float x, float y,
+template <int F>
+__device__ __forceinline__ void hash_encode_range(const EncMeta* m, const __half* __restrict__ table, float x, float y,
                                                   float z, int l_begin, int l_end, uint32_t (&out)[16]) {
     (void)table;                                  // the level bases in `m` were derived from it
     const int n_dense = m->n_dense;
-    if constexpr (!T32) {
-        const int cell_end = l_end < m->n_cell ? l_end : m->n_cell;
-#pragma unroll kCellUnroll
-        for (int l = l_begin; l < cell_end; ++l) cell_level<F>(m, l, x, y, z, out);
-        if (l_begin < cell_end) l_begin = cell_end;
-    }
+    const int cell_end = l_end < m->n_cell ? l_end : m->n_cell;
+#pragma unroll 2
+    for (int l = l_begin; l < cell_end; ++l) cell_level<F>(m, l, x, y, z, out);
+    if (l_begin < cell_end) l_begin = cell_end;
     const int dense_end = l_end < n_dense ? l_end : n_dense;
     const int staged_end = dense_end < m->n_staged ? dense_end : m->n_staged;
 #pragma unroll 1
-    for (int l = l_begin; l < staged_end; ++l) {
-        if constexpr (!T32) dense_level<F, true>(m, l, x, y, z, out);          // only the fp16 table is ever staged
-    }
+    for (int l = l_begin; l < staged_end; ++l) dense_level<F, true>(m, l, x, y, z, out);
 #pragma unroll 1
-    for (int l = l_begin > staged_end ? l_begin : staged_end; l < dense_end; ++l) dense_level<F, false, T32>(m, l, x, y, z, out);
+    for (int l = l_begin > staged_end ? l_begin : staged_end; l < dense_end; ++l) dense_level<F, false>(m, l, x, y, z, out);
 #pragma unroll 3
     for (int l = l_begin > n_dense ? l_begin : n_dense; l < l_end; ++l) {
         const float scale = m->level[l].scale;
@@ -268,18 +242,18 @@ __device__ __forceinline__ void hash_encode_range(const EncMeta* m, const void* 
         const uint32_t y0 = c.iy * 2654435761u, y1 = y0 + 2654435761u;
         const uint32_t z0 = c.iz * 805459861u, z1 = z0 + 805459861u;
         const uint32_t xy[4] = {c.ix ^ y0, (c.ix + 1u) ^ y0, c.ix ^ y1, (c.ix + 1u) ^ y1};
-        uint32_t raw[8][T32 ? F : F / 2];
+        uint32_t raw[8][F / 2];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) load_entry<F, T32>(base, (xy[k & 3] ^ ((k & 4) ? z1 : z0)) & mask, raw[k]);
-        level_finish<F, T32>(c, raw, l, out);
+        for (int k = 0; k < 8; ++k) load_entry<F>(base, (xy[k & 3] ^ ((k & 4) ? z1 : z0)) & mask, raw[k]);
+        level_finish<F>(c, raw, l, out);
     }
 }
 
 // Encodes one position into 32 halves, returned as 16 packed pairs.
-template <int F, bool T32 = false>
-__device__ __forceinline__ void hash_encode_packed(const EncMeta* m, const void* __restrict__ table, float x, float y,
+template <int F>
+__device__ __forceinline__ void hash_encode_packed(const EncMeta* m, const __half* __restrict__ table, float x, float y,
                                                    float z, uint32_t (&out)[16]) {
-    hash_encode_range<F, T32>(m, table, x, y, z, 0, m->n_levels, out);
+    hash_encode_range<F>(m, table, x, y, z, 0, m->n_levels, out);
 }
 
 // Same, written as 32 consecutive halves.
