@@ -44,7 +44,7 @@ ALG_BYTES_PER_SAMPLE = 588.0      # hash encoding: 12 B position + 16 levels x 8
 ALG_FLOP_PER_SAMPLE = 18816.0     # the two MLPs
 # DRAM bytes per sample of the two dominant kernels, from the ncu captures named in `roofline.scaled_from`
 # (dram__bytes_read.sum + dram__bytes_write.sum of one launch / its samples)
-FIELD_DRAM_BYTES_PER_SAMPLE = 33.1
+FIELD_DRAM_BYTES_PER_SAMPLE = 36.4
 SAMPLER_DRAM_BYTES_PER_SAMPLE = 16.1
 
 
@@ -393,7 +393,7 @@ def run_ours(args):
     roof_ms = t_field / max(n_batches, 1)
     roof_traffic = FIELD_DRAM_BYTES_PER_SAMPLE * n_samples / max(n_batches, 1)
     roof_capture = "profiles/field_network_tcgen05_config1_320x208.md"
-    roof_limiter = "instruction issue and L1/L2 gather latency (ncu: issue-active 70 %, L1 60 %, DRAM 4 %, tensor pipe 10 %)"
+    roof_limiter = "gather latency and instruction issue (ncu: issue-active 63 %, top stall long_scoreboard, L1 62 %, DRAM 5 %, tensor pipe 10 %)"
     if cfg.field_type != abi.FIELD_NETWORK:
         # sampler + compositing configurations: the sampler is the kernel of interest (28 B/sample + 80 B/ray)
         roof_kernel = "k_march_paged (single-pass sampler)"
@@ -401,7 +401,7 @@ def run_ours(args):
         achieved = (28.0 * n_samples + 80.0 * n_local) / (t_sampler * 1e-3) / 1e9 if t_sampler > 0 else 0.0
         roof_traffic = SAMPLER_DRAM_BYTES_PER_SAMPLE * n_samples / max(n_batches, 1)
         roof_capture = "profiles/march_paged_config1_320x208.md"
-        roof_limiter = "dependent arithmetic per march step (ncu: issue-active 50 %, top stall wait, DRAM 10 %)"
+        roof_limiter = "dependent arithmetic per march step (ncu: issue-active 58 %, top stall wait, DRAM 12 %)"
     line = {
         "metric": "render throughput", "value": value, "unit": "Mrays/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
@@ -612,9 +612,11 @@ def run_single_process(args):
     sampler = ClockSampler(0)
     sampler.start()
     ms = 0.0
+    t0 = time.perf_counter()
     for _ in range(args.steps):
         comm.render(views, post, 1, host_images=False)
         ms += max(comm.timings())
+    wall_resident = time.perf_counter() - t0
     clocks = sampler.stop()
     t0 = time.perf_counter()
     for _ in range(args.steps):
@@ -635,6 +637,7 @@ def run_single_process(args):
         "e2e": {"value": rays_per_step * args.steps / wall / 1e6, "unit": "Mrays/s",
                 "h2d_bytes_per_step": int(C.sizeof(abi.View) + C.sizeof(abi.Post)) * n_views, "d2h_bytes_per_step": int(HEIGHT * WIDTH * 16 * n_views)},
         "gpu_launches": None, "mode": "single process, srf_comm",
+        "wall_ms_per_step": wall_resident * 1e3 / args.steps,     # host clock around the same calls: must agree with ms_per_step
     }
     print(json.dumps(line), flush=True)
 

@@ -17,6 +17,7 @@
 #include <cstring>
 #include <new>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "srf_kernels.cuh"
@@ -1283,27 +1284,48 @@ srf_status srf_render_frames_sharded(srf_comm* c, const srf_view_t* views, uint3
         DeviceGuard guard(root->device);
         if (cudaEventRecord(c->go, c->stream[0]) != cudaSuccess) return comm_fail(c, SRF_ERR_CUDA, "cudaEventRecord failed");
     }
-    for (uint32_t r = 0; r < n; ++r) {
+    // One host thread per device enqueues that device's frames: a frame is a few dozen launches, a batch of views
+    // more than a stream's launch queue holds, and a single enqueuing thread would block on the first device's queue
+    // while the others sit idle.
+    std::vector<srf_status> status(n, SRF_OK);
+    std::vector<std::string> message(n);
+    auto enqueue = [&](uint32_t r) {
         srf_ctx* ctx = c->ctx[r];
         DeviceGuard guard(ctx->device);
-        if (r > 0 && cudaStreamWaitEvent(c->stream[r], c->go, 0) != cudaSuccess) return comm_fail(c, SRF_ERR_CUDA, "cudaStreamWaitEvent failed");
+        if (r > 0 && cudaStreamWaitEvent(c->stream[r], c->go, 0) != cudaSuccess) {
+            status[r] = SRF_ERR_CUDA; message[r] = "cudaStreamWaitEvent failed";
+            return;
+        }
         cudaEventRecord(c->begin[r], c->stream[r]);
-        for (uint32_t k = 0; k < n_views; ++k) {
+        for (uint32_t k = 0; k < n_views && status[r] == SRF_OK; ++k) {
             srf_view_t v = views[k];
             v.shard_rows = v.shard_rows ? v.shard_rows : 8;
             v.shard_count = n;
             v.shard_rank = r;
             const uint64_t n_local = shard_rows_total(v) * v.width;
             srf_status st = ensure(ctx, ctx->img_accum, (size_t)std::max<uint64_t>(n_local, 1) * sizeof(float4));
-            if (st != SRF_OK) return comm_fail(c, st, ctx->err);
-            for (uint32_t i = 0; i < spp; ++i) {
+            for (uint32_t i = 0; i < spp && st == SRF_OK; ++i) {
                 v.spp_index = i;
                 st = srf_render_frame_scatter(ctx, &v, post, d_images + (size_t)k * px * 4, (float*)ctx->img_accum.p, nullptr, c->stream[r]);
-                if (st != SRF_OK) return comm_fail(c, st, ctx->err);
             }
+            if (st != SRF_OK) { status[r] = st; message[r] = ctx->err; }
         }
         cudaEventRecord(c->done[r], c->stream[r]);
+    };
+    {
+        std::vector<std::thread> workers;
+        for (uint32_t r = 1; r < n; ++r) workers.emplace_back(enqueue, r);
+        enqueue(0);
+        for (std::thread& w : workers) w.join();
     }
+    for (uint32_t r = 0; r < n; ++r)
+        if (status[r] != SRF_OK) {
+            for (uint32_t q = 0; q < n; ++q) {           // leave no work of this call in flight
+                DeviceGuard guard(c->ctx[q]->device);
+                cudaStreamSynchronize(c->stream[q]);
+            }
+            return comm_fail(c, status[r], message[r]);
+        }
     {   // the image is complete when every device's part is: the first device's stream waits for all of them
         DeviceGuard guard(root->device);
         for (uint32_t r = 1; r < n; ++r)
