@@ -126,21 +126,28 @@ __device__ __forceinline__ void level_interpolate(const LevelCell& c, const uint
     }
 }
 
-template <int F>
-__device__ __forceinline__ void level_finish(const LevelCell& c, const uint32_t (&raw)[8][F / 2], int l, uint32_t (&out)[16]) {
+// `out(i, word)` receives packed pair i (features 2i, 2i+1 of the 32-half encoding) of every level: an array in
+// registers or local memory (ArraySink), or a store straight into the place the encoding is needed.
+struct ArraySink {
+    uint32_t (&a)[16];
+    __device__ __forceinline__ void operator()(int i, uint32_t w) const { a[i] = w; }
+};
+
+template <int F, class Sink>
+__device__ __forceinline__ void level_finish(const LevelCell& c, const uint32_t (&raw)[8][F / 2], int l, const Sink& out) {
     float acc[F];
     level_interpolate<F>(c, raw, acc);
 #pragma unroll
     for (int f = 0; f < F / 2; ++f) {
         const __half2 h = __floats2half2_rn(acc[2 * f], acc[2 * f + 1]);
-        out[l * (F / 2) + f] = *reinterpret_cast<const uint32_t*>(&h);
+        out(l * (F / 2) + f, *reinterpret_cast<const uint32_t*>(&h));
     }
 }
 
 // One dense level.  STAGED: the level's entries were copied to shared memory and `base` points there (plain loads);
 // otherwise they are read from global memory through the read-only path.
-template <int F, bool STAGED>
-__device__ __forceinline__ void dense_level(const EncMeta* m, int l, float x, float y, float z, uint32_t (&out)[16]) {
+template <int F, bool STAGED, class Sink>
+__device__ __forceinline__ void dense_level(const EncMeta* m, int l, float x, float y, float z, const Sink& out) {
     const EncLevel L = m->level[l];
     const uint32_t* base = L.base;
     const LevelCell c = level_cell(L.scale, x, y, z);
@@ -181,8 +188,8 @@ __device__ __forceinline__ void dense_level(const EncMeta* m, int l, float x, fl
 }
 
 // One level read from its cell-major copy.  Cells outside the level (positions outside [0,1]) take the scattered path.
-template <int F>
-__device__ __forceinline__ void cell_level(const EncMeta* m, int l, float x, float y, float z, uint32_t (&out)[16]) {
+template <int F, class Sink>
+__device__ __forceinline__ void cell_level(const EncMeta* m, int l, float x, float y, float z, const Sink& out) {
     const EncCellLevel C = m->cell[l];
     const LevelCell c = level_cell(C.scale, x, y, z);
     uint32_t raw[8][F / 2];
@@ -215,17 +222,81 @@ __device__ __forceinline__ void cell_level(const EncMeta* m, int l, float x, flo
     level_finish<F>(c, raw, l, out);
 }
 
+// B consecutive levels read from their cell-major copies with the B loads issued back to back (no branch between
+// them: the cell coordinates are clamped into the level for the load, and a level whose cell was outside is read
+// again through the scattered path afterwards, which positions inside [0,1] never need).
+#ifndef SRF_CELL_BATCH
+#define SRF_CELL_BATCH 2
+#endif
+constexpr int kCellBatch = SRF_CELL_BATCH;
+#ifndef SRF_HASHED_UNROLL
+#define SRF_HASHED_UNROLL 3
+#endif
+constexpr int kHashedUnroll = SRF_HASHED_UNROLL;
+template <int F, int B, class Sink>
+__device__ __forceinline__ void cell_levels(const EncMeta* m, int l, float x, float y, float z, const Sink& out) {
+    LevelCell c[B];
+    uint32_t raw[B][8][F / 2];
+    bool inside[B];
+    bool all_inside = true;
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+        const EncCellLevel C = m->cell[l + b];
+        c[b] = level_cell(C.scale, x, y, z);
+        inside[b] = c[b].ix < C.res && c[b].iy < C.res && c[b].iz < C.res;
+        all_inside = all_inside && inside[b];
+        const uint32_t hi = C.res - 1u;
+        const uint32_t cx = min(c[b].ix, hi), cy = min(c[b].iy, hi), cz = min(c[b].iz, hi);
+        const uint4* e = C.cells + ((size_t)(cz * C.res + cy) * C.res + cx) * (size_t)F;
+        if constexpr (F == 2) {
+            uint32_t* r = &raw[b][0][0];
+            asm("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "l"(e));
+        } else {
+#pragma unroll
+            for (int q = 0; q < F; ++q) {
+                const uint4 v = __ldg(e + q);
+                uint32_t* r = &raw[b][0][0] + 4 * q;
+                r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
+            }
+        }
+    }
+    if (!all_inside) {
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+            if (inside[b]) continue;
+            const EncLevel L = m->level[l + b];
+            const bool dense = l + b < m->n_dense;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const uint32_t cx = c[b].ix + (k & 1), cy = c[b].iy + ((k >> 1) & 1), cz = c[b].iz + (k >> 2);
+                uint32_t i;
+                if (dense) { i = cx + cy * L.res + cz * L.r2; if (i >= L.size) i %= L.size; }
+                else i = (cx ^ (cy * 2654435761u) ^ (cz * 805459861u)) & L.mask;
+                load_entry<F>(L.base, i, raw[b][k]);
+            }
+        }
+    }
+#pragma unroll
+    for (int b = 0; b < B; ++b) level_finish<F>(c[b], raw[b], l + b, out);
+}
+
 // Encodes levels [l_begin, l_end) of one position into the packed pairs out[l*F/2 ...] (pair i = features
 // 2i, 2i+1 of the 32-half encoding).  `m` lives in shared memory (prepare_enc_meta).  Callers that want to
 // interleave the encoding with other work call it on successive level ranges.
-template <int F>
+template <int F, class Sink>
 __device__ __forceinline__ void hash_encode_range(const EncMeta* m, const __half* __restrict__ table, float x, float y,
-                                                  float z, int l_begin, int l_end, uint32_t (&out)[16]) {
+                                                  float z, int l_begin, int l_end, const Sink& out) {
     (void)table;                                  // the level bases in `m` were derived from it
     const int n_dense = m->n_dense;
     const int cell_end = l_end < m->n_cell ? l_end : m->n_cell;
-#pragma unroll 2
-    for (int l = l_begin; l < cell_end; ++l) cell_level<F>(m, l, x, y, z, out);
+    {
+        int l = l_begin;
+#pragma unroll 1
+        for (; l + kCellBatch <= cell_end; l += kCellBatch) cell_levels<F, kCellBatch>(m, l, x, y, z, out);
+#pragma unroll 1
+        for (; l < cell_end; ++l) cell_level<F>(m, l, x, y, z, out);
+    }
     if (l_begin < cell_end) l_begin = cell_end;
     const int dense_end = l_end < n_dense ? l_end : n_dense;
     const int staged_end = dense_end < m->n_staged ? dense_end : m->n_staged;
@@ -233,7 +304,7 @@ __device__ __forceinline__ void hash_encode_range(const EncMeta* m, const __half
     for (int l = l_begin; l < staged_end; ++l) dense_level<F, true>(m, l, x, y, z, out);
 #pragma unroll 1
     for (int l = l_begin > staged_end ? l_begin : staged_end; l < dense_end; ++l) dense_level<F, false>(m, l, x, y, z, out);
-#pragma unroll 3
+#pragma unroll kHashedUnroll
     for (int l = l_begin > n_dense ? l_begin : n_dense; l < l_end; ++l) {
         const float scale = m->level[l].scale;
         const uint32_t mask = m->level[l].mask;
@@ -253,7 +324,7 @@ __device__ __forceinline__ void hash_encode_range(const EncMeta* m, const __half
 template <int F>
 __device__ __forceinline__ void hash_encode_packed(const EncMeta* m, const __half* __restrict__ table, float x, float y,
                                                    float z, uint32_t (&out)[16]) {
-    hash_encode_range<F>(m, table, x, y, z, 0, m->n_levels, out);
+    hash_encode_range<F>(m, table, x, y, z, 0, m->n_levels, ArraySink{out});
 }
 
 // Same, written as 32 consecutive halves.
