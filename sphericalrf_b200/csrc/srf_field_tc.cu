@@ -292,25 +292,17 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
                 }
             }
         }
-#if defined(SRF_TC_ENC_ARRAY)
         {
+            // The 16 packed pairs are collected in an array indexed by the level (it lives in local memory, which L1
+            // serves) and stored as four 16-byte units; storing each pair straight into the A image (sixteen 4-byte
+            // stores, four-way bank conflicts) measured 134.9 ms per benchmark frame against 132.0.
             uint32_t enc[16];
-            hash_encode_packed<F>(enc_meta, table, x, y, z, enc);
+                        hash_encode_packed<F, true>(enc_meta, table, x, y, z, enc);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
                 *reinterpret_cast<uint4*>(act + ((size_t)j * 128 + row) * 16) =
                     make_uint4(enc[4 * j], enc[4 * j + 1], enc[4 * j + 2], enc[4 * j + 3]);
         }
-#else
-        {
-            // Every level's packed pair goes straight to its place in the A image (pair i = word i%4 of unit i/4): an
-            // array indexed by the level would live in local memory, 64 KB of L1 per CTA that the gathers can use.
-            unsigned char* my_units = act + (size_t)row * 16;
-            hash_encode_range<F>(enc_meta, table, x, y, z, 0, enc_meta->n_levels, [my_units](int i, uint32_t w) {
-                *reinterpret_cast<uint32_t*>(my_units + (size_t)(i >> 2) * (128 * 16) + (i & 3) * 4) = w;
-            });
-        }
-#endif
         // Spherical harmonics of the direction: read later from the per-ray table the sampler wrote (frame path), or
         // computed here and kept in registers (stage entry points).
         const bool sh_from_ray = FRAME || (ray_sh && !coords7);

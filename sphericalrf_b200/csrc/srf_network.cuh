@@ -225,14 +225,9 @@ __device__ __forceinline__ void cell_level(const EncMeta* m, int l, float x, flo
 // B consecutive levels read from their cell-major copies with the B loads issued back to back (no branch between
 // them: the cell coordinates are clamped into the level for the load, and a level whose cell was outside is read
 // again through the scattered path afterwards, which positions inside [0,1] never need).
-#ifndef SRF_CELL_BATCH
-#define SRF_CELL_BATCH 2
-#endif
-constexpr int kCellBatch = SRF_CELL_BATCH;
-#ifndef SRF_HASHED_UNROLL
-#define SRF_HASHED_UNROLL 3
-#endif
-constexpr int kHashedUnroll = SRF_HASHED_UNROLL;
+constexpr int kCellBatch = 2;          // 1: 139.0, 2: 132.0, 3: 140.4 ms per benchmark frame (3 spills at 64 registers)
+// (Leaving the second read out on the frame path, whose positions always lie inside [0,1]^3, measured slower: 135.9
+// against 131.8 ms per benchmark frame.)
 template <int F, int B, class Sink>
 __device__ __forceinline__ void cell_levels(const EncMeta* m, int l, float x, float y, float z, const Sink& out) {
     LevelCell c[B];
@@ -284,27 +279,28 @@ __device__ __forceinline__ void cell_levels(const EncMeta* m, int l, float x, fl
 // Encodes levels [l_begin, l_end) of one position into the packed pairs out[l*F/2 ...] (pair i = features
 // 2i, 2i+1 of the 32-half encoding).  `m` lives in shared memory (prepare_enc_meta).  Callers that want to
 // interleave the encoding with other work call it on successive level ranges.
-template <int F, class Sink>
+// CELLS: the caller attaches cell-major copies (attach_cell_tables); callers that never do compile without that path.
+template <int F, bool CELLS, class Sink>
 __device__ __forceinline__ void hash_encode_range(const EncMeta* m, const __half* __restrict__ table, float x, float y,
                                                   float z, int l_begin, int l_end, const Sink& out) {
     (void)table;                                  // the level bases in `m` were derived from it
     const int n_dense = m->n_dense;
-    const int cell_end = l_end < m->n_cell ? l_end : m->n_cell;
-    {
+    if constexpr (CELLS) {
+        const int cell_end = l_end < m->n_cell ? l_end : m->n_cell;
         int l = l_begin;
 #pragma unroll 1
         for (; l + kCellBatch <= cell_end; l += kCellBatch) cell_levels<F, kCellBatch>(m, l, x, y, z, out);
 #pragma unroll 1
         for (; l < cell_end; ++l) cell_level<F>(m, l, x, y, z, out);
+        if (l_begin < cell_end) l_begin = cell_end;
     }
-    if (l_begin < cell_end) l_begin = cell_end;
     const int dense_end = l_end < n_dense ? l_end : n_dense;
     const int staged_end = dense_end < m->n_staged ? dense_end : m->n_staged;
 #pragma unroll 1
     for (int l = l_begin; l < staged_end; ++l) dense_level<F, true>(m, l, x, y, z, out);
 #pragma unroll 1
     for (int l = l_begin > staged_end ? l_begin : staged_end; l < dense_end; ++l) dense_level<F, false>(m, l, x, y, z, out);
-#pragma unroll kHashedUnroll
+#pragma unroll 3
     for (int l = l_begin > n_dense ? l_begin : n_dense; l < l_end; ++l) {
         const float scale = m->level[l].scale;
         const uint32_t mask = m->level[l].mask;
@@ -321,10 +317,10 @@ __device__ __forceinline__ void hash_encode_range(const EncMeta* m, const __half
 }
 
 // Encodes one position into 32 halves, returned as 16 packed pairs.
-template <int F>
+template <int F, bool CELLS = false>
 __device__ __forceinline__ void hash_encode_packed(const EncMeta* m, const __half* __restrict__ table, float x, float y,
                                                    float z, uint32_t (&out)[16]) {
-    hash_encode_range<F>(m, table, x, y, z, 0, m->n_levels, ArraySink{out});
+    hash_encode_range<F, CELLS>(m, table, x, y, z, 0, m->n_levels, ArraySink{out});
 }
 
 // Same, written as 32 consecutive halves.
