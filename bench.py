@@ -44,7 +44,7 @@ ALG_BYTES_PER_SAMPLE = 588.0      # hash encoding: 12 B position + 16 levels x 8
 ALG_FLOP_PER_SAMPLE = 18816.0     # the two MLPs
 # DRAM bytes per sample of the two dominant kernels, from the ncu captures named in `roofline.scaled_from`
 # (dram__bytes_read.sum + dram__bytes_write.sum of one launch / its samples)
-FIELD_DRAM_BYTES_PER_SAMPLE = 36.4
+FIELD_DRAM_BYTES_PER_SAMPLE = 36.3
 SAMPLER_DRAM_BYTES_PER_SAMPLE = 16.1
 
 
@@ -393,7 +393,7 @@ def run_ours(args):
     roof_ms = t_field / max(n_batches, 1)
     roof_traffic = FIELD_DRAM_BYTES_PER_SAMPLE * n_samples / max(n_batches, 1)
     roof_capture = "profiles/field_network_tcgen05_config1_320x208.md"
-    roof_limiter = "gather latency and instruction issue (ncu: issue-active 63 %, top stall long_scoreboard, L1 62 %, DRAM 5 %, tensor pipe 10 %)"
+    roof_limiter = "instruction issue and the group barriers around the five tcgen05.mma issues (ncu: issue-active 72 %, top stall barrier, L1 68 %, DRAM 5 %, tensor pipe 12 %)"
     if cfg.field_type != abi.FIELD_NETWORK:
         # sampler + compositing configurations: the sampler is the kernel of interest (28 B/sample + 80 B/ray)
         roof_kernel = "k_march_paged (single-pass sampler)"

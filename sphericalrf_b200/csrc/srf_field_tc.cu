@@ -43,7 +43,8 @@ namespace srf {
 
 namespace {
 
-constexpr int kGroups = 8;                      // groups of 128 threads per CTA
+constexpr int kGroups = 8;                      // groups of 128 threads per CTA (6 groups at 80 registers: 146 ms per
+                                                // benchmark frame against 132)
 constexpr int kGroup = 128;
 constexpr int kTcBlock = kGroup * kGroups;
 constexpr uint32_t kTmemCols = 64 * kGroups;      // 64 per group: the whole tensor memory of the SM
@@ -67,6 +68,7 @@ constexpr int kSmLimit = 227 * 1024;
 static_assert(kTmemCols == 512, "the CTA owns the SM's tensor memory");
 static_assert(kSmTotal > 227 * 1024 / 2, "a second CTA must not fit: it would wait for tensor memory forever");
 static_assert(kSmTotal <= kSmLimit, "shared memory of one SM");
+static_assert(kSmEnc % 16 == 0 && kSmBar % 8 == 0, "EncMeta holds 16-byte records, the barriers are 8-byte objects");
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -395,6 +397,9 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
                 }
             }
         }
+        // (Measured and left as they are, in ms per benchmark frame against 132.0: no barrier here -- the one after the
+        // next tile's gather orders the same accesses -- 131.4-132.4; two tcgen05.ld in flight in the epilogues 134.0;
+        // every warp polling the commit barrier itself, agreement at the end of the tile, 131.2-144.0.)
         tc_fence_before();
         group_sync(group);
     }
