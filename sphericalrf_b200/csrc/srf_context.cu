@@ -931,8 +931,20 @@ static srf_status ensure_cell_tables(srf_ctx* ctx, cudaStream_t stream) {
     if (want != ctx->n_cell_levels) {
         if (ctx->cell_table) { SRF_CK(ctx, cudaFree(ctx->cell_table)); ctx->cell_table = nullptr; }
         ctx->n_cell_levels = 0;
+        // The copies are an optimisation: when the device cannot spare the memory, take fewer levels (or none)
+        // instead of failing the frame.
+        const int asked = want;
+        while (want > 0) {
+            if (cudaMalloc((void**)&ctx->cell_table, cell_table_units(ctx->net, want, nullptr) * sizeof(uint4)) == cudaSuccess) break;
+            cudaGetLastError();
+            ctx->cell_table = nullptr;
+            --want;
+        }
+        if (want < asked) {                       // remember what fitted, so that later frames do not try again
+            ctx->cell_budget = cell_table_units(ctx->net, want, nullptr) * sizeof(uint4);
+            if (ctx->cell_levels_forced >= 0) ctx->cell_levels_forced = want;
+        }
         if (want > 0) {
-            SRF_CK(ctx, cudaMalloc((void**)&ctx->cell_table, cell_table_units(ctx->net, want, nullptr) * sizeof(uint4)));
             ctx->n_cell_levels = want;
             ctx->cell_dirty = true;
         }
