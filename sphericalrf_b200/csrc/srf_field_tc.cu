@@ -62,7 +62,8 @@ constexpr int kSmAct = kSmW_C3 + 8 * 16 * 16;     // kGroups x [8][128][8]: the 
 constexpr int kActBytes = 8 * 128 * 16;
 constexpr int kSmBar = kSmAct + kGroups * kActBytes;   // kGroups mbarriers + tensor-memory base (4 B)
 constexpr int kSmEnc = kSmBar + kGroups * 8 + 16;  // per-level constants of the encoding
-constexpr int kSmStage = (kSmEnc + (int)sizeof(EncMeta) + 15) / 16 * 16;   // coarse levels of the hash table (optional, dynamic size)
+constexpr int kSmDesc = (kSmEnc + (int)sizeof(EncMeta) + 15) / 16 * 16;    // operand descriptors: [group][layer][k step] x (A, B)
+constexpr int kSmStage = kSmDesc + kGroups * 5 * 4 * 16;                    // coarse levels of the hash table (optional, dynamic size)
 constexpr int kSmTotal = kSmStage;                // without staged levels
 constexpr int kSmLimit = 227 * 1024;
 static_assert(kTmemCols == 512, "the CTA owns the SM's tensor memory");
@@ -95,6 +96,16 @@ __device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t a_desc, uint64
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
         "}\n"
         :: "r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The same with the accumulate flag fixed at compile time (no predicate to compute at run time).
+template <bool ACCUMULATE>
+__device__ __forceinline__ void mma_f16_fixed(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+    if (ACCUMULATE)
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.b32 p, 0, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+                     :: "r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc) : "memory");
+    else
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 0, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+                     :: "r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc) : "memory");
 }
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
@@ -198,6 +209,16 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
     load_weight_image(wc, 64, 32, smem + kSmW_C1);
     load_weight_image(wc + 64 * 32, 64, 64, smem + kSmW_C2);
     load_weight_image(wc + 64 * 32 + 64 * 64, 16, 64, smem + kSmW_C3);
+    if (tid < kGroups * 20) {                      // operand descriptors: [group][layer][k step] = (A, B)
+        const int gq = tid / 20, layer = (tid % 20) / 4, kk = tid % 4;
+        const uint32_t b_img = smem_u32(smem + (layer == 0 ? kSmW_D1 : layer == 1 ? kSmW_D2 : layer == 2 ? kSmW_C1 : layer == 3 ? kSmW_C2 : kSmW_C3));
+        const uint32_t n_out = (layer == 1 || layer == 4) ? 16u : 64u;
+        const uint32_t a_img = smem_u32(smem + kSmAct + gq * kActBytes);
+        ulonglong2 d;
+        d.x = make_desc(a_img + (uint32_t)kk * 2u * (128u * 16u), 128u * 16u, 128u);
+        d.y = make_desc(b_img + (uint32_t)kk * 2u * n_out * 16u, n_out * 16u, 128u);
+        reinterpret_cast<ulonglong2*>(smem + kSmDesc)[tid] = d;
+    }
     if (row == 0 && group % kPair == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -231,22 +252,28 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
 
     unsigned char* act = smem + kSmAct + group * kActBytes;
     const uint32_t act_addr = smem_u32(act);
-    const uint32_t wD1 = smem_u32(smem + kSmW_D1), wD2 = smem_u32(smem + kSmW_D2), wC1 = smem_u32(smem + kSmW_C1),
-                   wC2 = smem_u32(smem + kSmW_C2), wC3 = smem_u32(smem + kSmW_C3);
     constexpr uint32_t kIdesc64 = make_idesc(64), kIdesc16 = make_idesc(16);
-    constexpr uint32_t kALbo = 128 * 16, kSbo = 128;          // A images have 128 rows
 
-    // One dense layer: K/16 instructions over the A image in the activation region and a B image (n_out rows).
-    auto issue_layer = [&](uint32_t b_img, uint32_t n_out, int k16, uint32_t idesc) {
-        if (row == 0 && group % kPair == 0) {
+    // One dense layer: K/16 instructions over the A image in the activation region and the layer's B image.  The
+    // operand descriptors were computed once per CTA (desc_tab, filled below the weight images): the issuing thread
+    // is one thread among 32 busy warps, and every instruction it spends here is time its whole group waits (the
+    // issue took 420-670 cycles per layer with the descriptors built on the spot).
+    const ulonglong2* my_desc = reinterpret_cast<const ulonglong2*>(smem + kSmDesc) + group * 20;
+    auto issue_layer = [&](int layer, int k16, uint32_t idesc) {
+        if (row == 0) {
             tc_fence_after();
-#pragma unroll
-            for (int u = 0; u < kPair; ++u)
-                for (int kk = 0; kk < k16; ++kk) {
-                    const uint64_t da = make_desc(act_addr + (uint32_t)u * kActBytes + (uint32_t)kk * 2u * kALbo, kALbo, kSbo);
-                    const uint64_t db = make_desc(b_img + (uint32_t)kk * 2u * n_out * 16u, n_out * 16u, kSbo);
-                    mma_f16(tmem_group + (uint32_t)u * 64u, da, db, idesc, kk > 0 ? 1u : 0u);
-                }
+            const ulonglong2* d = my_desc + layer * 4;
+            const ulonglong2 d0 = d[0], d1 = d[1];
+            if (k16 == 4) {
+                const ulonglong2 d2 = d[2], d3 = d[3];
+                mma_f16_fixed<false>(tmem_group, d0.x, d0.y, idesc);
+                mma_f16_fixed<true>(tmem_group, d1.x, d1.y, idesc);
+                mma_f16_fixed<true>(tmem_group, d2.x, d2.y, idesc);
+                mma_f16_fixed<true>(tmem_group, d3.x, d3.y, idesc);
+            } else {
+                mma_f16_fixed<false>(tmem_group, d0.x, d0.y, idesc);
+                mma_f16_fixed<true>(tmem_group, d1.x, d1.y, idesc);
+            }
             mma_commit(bar);
         }
     };
@@ -319,7 +346,7 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
         group_sync(group);
 
         // ---- density layer 1: 32 -> 64, ReLU ----
-        issue_layer(wD1, 64, 2, kIdesc64);
+        issue_layer(0, 2, kIdesc64);
         if (FRAME) {                                  // hint only: bring the next tile's records into L2
             const uint64_t sn = s + tile_stride * kGroup;
             if (sn < n) {
@@ -334,7 +361,7 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
         fence_async_smem();
         group_sync(group);
         // ---- density layer 2: 64 -> 16 ----
-        issue_layer(wD2, 16, 4, kIdesc16);
+        issue_layer(1, 4, kIdesc16);
         if (!wait_layer()) { failed = true; break; }
         tc_fence_after();
         uint32_t sigma_half;
@@ -355,7 +382,7 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
         fence_async_smem();
         group_sync(group);
         // ---- colour layer 1: 32 -> 64, ReLU ----
-        issue_layer(wC1, 64, 2, kIdesc64);
+        issue_layer(2, 2, kIdesc64);
         if (!wait_layer()) { failed = true; break; }
         tc_fence_after();
         hidden_epilogue();
@@ -363,7 +390,7 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
         fence_async_smem();
         group_sync(group);
         // ---- colour layer 2: 64 -> 64, ReLU ----
-        issue_layer(wC2, 64, 4, kIdesc64);
+        issue_layer(3, 4, kIdesc64);
         if (!wait_layer()) { failed = true; break; }
         tc_fence_after();
         hidden_epilogue();
@@ -371,7 +398,7 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
         fence_async_smem();
         group_sync(group);
         // ---- colour layer 3: 64 -> 16 (3 used) ----
-        issue_layer(wC3, 16, 4, kIdesc16);
+        issue_layer(4, 4, kIdesc16);
         if (!wait_layer()) { failed = true; break; }
         tc_fence_after();
         {
