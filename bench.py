@@ -412,7 +412,8 @@ def run_ours(args):
                    "partition": f"rows in blocks of 8 round-robin over {world} rank(s)", "gather": gather_kind,
                    "gather_check": gather_check,
                    "l2": "per-frame working set (sample buffers) far larger than L2; no flush needed",
-                   "schedule": f"{stats.n_batches} ray batch(es) x {stats.n_waves} wave(s) per frame (trailing waves empty when every ray has ended)"},
+                   "schedule": f"{stats.n_batches} ray batch(es) x {stats.n_waves} wave(s) per frame (trailing waves empty when every ray has ended)",
+                   "device_memory": "library defaults: 16 GB sample pool; cell-major copies of the leading hash-grid levels within 4 GiB (network workloads)"},
         "frames_per_s": n_views / (ms_step * 1e-3),
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "Mrays/s", "h2d_bytes_per_step": int(C.sizeof(abi.View) + C.sizeof(abi.Post)) * n_views,
