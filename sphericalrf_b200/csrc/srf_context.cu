@@ -20,6 +20,8 @@
 #include <thread>
 #include <vector>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "srf_kernels.cuh"
 
 using namespace srf;
@@ -317,6 +319,15 @@ struct DeviceGuard {
     int prev = -1;
     explicit DeviceGuard(int dev) { cudaGetDevice(&prev); if (prev != dev) cudaSetDevice(dev); else prev = -1; }
     ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+// NVTX range for the lifetime of the object: names the library's stages in a timeline profiler (a few nanoseconds
+// when no tool is attached).
+struct NvtxRange {
+    explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+    ~NvtxRange() { nvtxRangePop(); }
+    NvtxRange(const NvtxRange&) = delete;
+    NvtxRange& operator=(const NvtxRange&) = delete;
 };
 
 srf_status ensure_ray_buffers(srf_ctx* ctx, uint64_t n_rays) {
@@ -679,6 +690,7 @@ srf_status srf_refresh_reset(srf_ctx* ctx, uint64_t seed) {
 }
 
 srf_status srf_refresh_grid(srf_ctx* ctx, uint32_t training_step, void* stream) {
+    NvtxRange nvtx_range("srf_refresh_grid");
     if (!ctx) return SRF_ERR_ARG;
     if (ctx->cfg.field_type != SRF_FIELD_NETWORK) return fail(ctx, SRF_ERR_STATE, "the grid refresh queries the network field");
     srf_status st = check_ready(ctx);
@@ -761,6 +773,7 @@ srf_status srf_sample_training_rays(srf_ctx* ctx, const srf_train_views_t* views
                                     uint32_t n_coords, uint64_t rng_state, uint64_t rng_inc, int snap_to_pixel_centers,
                                     uint32_t* d_ray_counter, uint32_t* d_numsteps_counter, float* d_rays, float* d_rays_rgba,
                                     uint32_t* d_numsteps, float* d_coords, void* stream) {
+    NvtxRange nvtx_range("srf_sample_training_rays");
     if (!ctx || !d_ray_counter || !d_numsteps_counter || !d_rays || !d_rays_rgba || !d_numsteps || !d_coords) return SRF_ERR_ARG;
     if (n_rays == 0) return fail(ctx, SRF_ERR_ARG, "n_rays must be positive");
     TrainViews tv;
@@ -807,6 +820,7 @@ srf_status srf_volume_rendering_loss(srf_ctx* ctx, const srf_loss_params_t* p, c
                                      uint32_t* d_ray_coord_indices, const float* d_rays_rgba, const float* d_coords,
                                      const uint16_t* d_network_output, float* d_compacted_coords, uint32_t* d_n_compacted_counter,
                                      uint16_t* d_dloss_doutput, float* d_loss_output, float* d_reg_distortion, void* stream) {
+    NvtxRange nvtx_range("srf_volume_rendering_loss");
     if (!ctx || !p || !d_n_rays_counter || !d_ray_coord_indices || !d_rays_rgba || !d_coords || !d_network_output ||
         !d_compacted_coords || !d_n_compacted_counter || !d_dloss_doutput)
         return SRF_ERR_ARG;
@@ -1010,6 +1024,7 @@ srf_status srf_volume_rendering(srf_ctx* ctx, const srf_view_t* view, const uint
 static srf_status render_frame_impl(srf_ctx* ctx, const srf_view_t* view, const srf_post_t* post, float* d_out, float* d_accum,
                                     float* d_rgba_raw, uint32_t* d_n_samples, srf_frame_stats_t* stats, void* stream,
                                     int out_by_pixel) {
+    NvtxRange nvtx_range("srf_render_frame");
     if (!ctx) return SRF_ERR_ARG;
     srf_status st = check_ready(ctx);
     if (st != SRF_OK) return st;
@@ -1091,12 +1106,15 @@ static srf_status render_frame_impl(srf_ctx* ctx, const srf_view_t* view, const 
         for (uint32_t wave = 0; wave < n_waves; ++wave) {
             SRF_CK(ctx, cudaMemsetAsync(ctx->d_chunk_cursor, 0, sizeof(uint32_t), s));
             if (tm) cudaEventRecord(ctx->ev[2], s);
+            nvtxRangePushA("srf sampler");
             launch_march_paged(ctx->g, v, bits, r0, r1, (float4*)ctx->pool_pos.p, (uint32_t*)ctx->chunk_ray.p,
                                (uint32_t*)ctx->chunk_next.p, pool_chunks, ctx->d_chunk_cursor, (float4*)ctx->ray_dir_t.p,
                                (uint8_t*)ctx->ray_end.p, (uint32_t*)ctx->counts.p, (uint32_t*)ctx->ray_head.p, ctx->d_counters, s,
                                wave, budgets[wave], waves ? (uint32_t*)ctx->ray_ordinal.p : nullptr,
                                waves ? (uint32_t*)ctx->ray_total.p : nullptr, sh_per_ray ? (uint4*)ctx->ray_sh.p : nullptr);
+            nvtxRangePop();
             if (tm) cudaEventRecord(ctx->ev[3], s);
+            nvtxRangePushA("srf field");
             if (blobs)
                 launch_field_blobs(ctx->g, v, ctx->blobs, ctx->n_blobs, ctx->cmap, (const float4*)ctx->pool_pos.p, 0,
                                    (float4*)ctx->pool_shaded.p, s, ctx->d_chunk_cursor);
@@ -1113,7 +1131,9 @@ static srf_status render_frame_impl(srf_ctx* ctx, const srf_view_t* view, const 
                 launch_field_network(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, (const float4*)ctx->pool_pos.p,
                                      (const uint32_t*)ctx->chunk_ray.p, (const float4*)ctx->ray_dir_t.p, nullptr, 0, nullptr,
                                      (float4*)ctx->pool_shaded.p, &ctx->g, &v, s, ctx->d_chunk_cursor, kChunkShift);
+            nvtxRangePop();
             if (tm) cudaEventRecord(ctx->ev[4], s);
+            NvtxRange composite_range("srf composite");
             launch_composite_paged(ctx->g, v, dp, r0, r1, (const uint32_t*)ctx->ray_head.p, (const uint32_t*)ctx->counts.p,
                                    (const uint32_t*)ctx->chunk_next.p, (const float4*)ctx->pool_shaded.p, (uint8_t*)ctx->ray_end.p,
                                    (float4*)d_out, (float4*)d_accum, (float4*)d_rgba_raw, nullptr, ctx->d_counters, s, wave,
@@ -1169,6 +1189,7 @@ srf_status srf_render_frame_scatter(srf_ctx* ctx, const srf_view_t* view, const 
 
 srf_status srf_render(srf_ctx* ctx, const srf_view_t* view, const srf_post_t* post, uint32_t spp, float* h_image,
                       srf_frame_stats_t* stats) {
+    NvtxRange nvtx_range("srf_render");
     if (!ctx || !view || !h_image) return SRF_ERR_ARG;
     if ((view->shard_count ? view->shard_count : 1) != 1) return fail(ctx, SRF_ERR_ARG, "srf_render renders whole images: shard_count must be 1");
     if (spp == 0) return fail(ctx, SRF_ERR_ARG, "spp must be positive");
@@ -1273,6 +1294,7 @@ const char* srf_comm_last_error(const srf_comm* c) { return c ? c->err.c_str() :
 
 srf_status srf_render_frames_sharded(srf_comm* c, const srf_view_t* views, uint32_t n_views, const srf_post_t* post, uint32_t spp,
                                      float* d_images, float* h_images, srf_frame_stats_t* stats) {
+    NvtxRange nvtx_range("srf_render_frames_sharded");
     if (!c || !views || n_views == 0) return comm_fail(c, SRF_ERR_ARG, "no views");
     if (spp == 0) return comm_fail(c, SRF_ERR_ARG, "spp must be positive");
     const uint32_t n = (uint32_t)c->ctx.size();
