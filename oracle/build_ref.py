@@ -1,7 +1,7 @@
 """Builds oracle/_ref/libsrf_ref.so: the reference's own kernels compiled for the host.  TEST INFRASTRUCTURE.
 
 The kernels and device functions are cut, by line range, out of the reference's source files where they lie
-(REFERENCE_ROOT, default /root/reference), written to a temporary directory and compiled together with
+(the directory SRF_REFERENCE_ROOT names, or the default checkout location below), written to a temporary directory and compiled together with
 oracle/ref_harness.cpp and the stand-in headers under oracle/ref_stub/.  Nothing of the reference is copied into
 this repository: only the shared object under oracle/_ref/ (git-ignored) remains.  Where the reference is not
 mounted, build() returns None and callers skip.

@@ -6,7 +6,7 @@ with nvcc's defaults, and runs them in the reference's host loop; the network is
 pipelines.  So the two sides differ in exactly what parity is about: the CUDA math library and nvcc's contraction in the
 reference's kernels against this library's own elementary functions and kernels.  Sampling is a chain of float steps
 tested against cell boundaries, so a last-bit difference moves a sample across a boundary now and then; the test bounds
-how often and reports the measured numbers (gpurun_out/reference_cuda_parity.json when that directory exists).
+how often and reports the measured numbers (written as reference_cuda_parity.json into the run's output directory when it exists).
 """
 import json
 from pathlib import Path
