@@ -983,11 +983,12 @@ srf_status srf_network_inference(srf_ctx* ctx, const float* d_coords, uint64_t n
     srf_status st = check_ready(ctx);
     if (st != SRF_OK) return st;
     DeviceGuard guard(ctx->device);
-    if ((st = ensure_cell_tables(ctx, (cudaStream_t)stream)) != SRF_OK) return st;
+    // The cell-major level copies are used when a frame has built them since the last upload; this entry point does not
+    // build them itself (a trainer that uploads parameters before every batch would pay the rebuild each time).
     if (ctx->use_tcgen05)
         launch_field_network_tc(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, nullptr, nullptr, nullptr, d_coords, n,
                                 (uint2*)d_rgbsigma, nullptr, nullptr, nullptr, &ctx->d_counters->error_flags, (cudaStream_t)stream,
-                                nullptr, 0, nullptr, ctx->cell_table, ctx->n_cell_levels);
+                                nullptr, 0, nullptr, ctx->cell_table, ctx->cell_dirty ? 0 : ctx->n_cell_levels);
     else
         launch_field_network(ctx->net, ctx->table, ctx->w_density, ctx->w_rgb, nullptr, nullptr, nullptr, d_coords, n,
                              (uint2*)d_rgbsigma, nullptr, nullptr, nullptr, (cudaStream_t)stream);
