@@ -30,7 +30,6 @@ namespace {
 
 thread_local std::string g_create_error;
 
-constexpr uint64_t kCoarse = 4096;                    // rays per entry of the coarse offset table
 constexpr uint64_t kAutoSampleCapacity = 512ull << 20;  // default upper bound of the sample pool (32 B per slot)
 
 struct DevBuf {
@@ -89,8 +88,6 @@ struct srf_ctx {
     DevBuf img_out, img_accum;
     FrameCounters* d_counters = nullptr;
     FrameCounters* h_counters = nullptr;     // pinned
-    uint64_t* h_coarse = nullptr;            // pinned
-    size_t h_coarse_entries = 0;
     uint64_t reserve_samples = 0;
 
     // refresh
@@ -337,13 +334,6 @@ srf_status ensure_ray_buffers(srf_ctx* ctx, uint64_t n_rays) {
     if ((st = ensure(ctx, ctx->counts, n_rays * sizeof(uint32_t))) != SRF_OK) return st;
     if ((st = ensure(ctx, ctx->offsets, (n_rays + 1) * sizeof(uint64_t))) != SRF_OK) return st;
     if ((st = ensure(ctx, ctx->scan_scratch, scan_scratch_bytes(n_rays))) != SRF_OK) return st;
-    const size_t coarse = (size_t)(n_rays / kCoarse) + 2;
-    if (coarse > ctx->h_coarse_entries) {
-        if (ctx->h_coarse) cudaFreeHost(ctx->h_coarse);
-        ctx->h_coarse = nullptr;
-        SRF_CK(ctx, cudaMallocHost((void**)&ctx->h_coarse, coarse * sizeof(uint64_t)));
-        ctx->h_coarse_entries = coarse;
-    }
     return SRF_OK;
 }
 
@@ -401,18 +391,6 @@ srf_status count_and_scan(srf_ctx* ctx, const DevView& v, cudaStream_t s) {
                      (uint32_t*)ctx->counts.p, ctx->d_counters, s);
     launch_scan((const uint32_t*)ctx->counts.p, v.n_rays, (uint64_t*)ctx->offsets.p, ctx->scan_scratch.p, s);
     SRF_CK(ctx, cudaGetLastError());
-    return SRF_OK;
-}
-
-// Copies offsets[k * kCoarse] (k = 0 .. n/kCoarse) and offsets[n] to the pinned table; synchronises.
-srf_status read_coarse_offsets(srf_ctx* ctx, uint64_t n_rays, cudaStream_t s, uint64_t* total) {
-    const size_t n_coarse = (size_t)(n_rays / kCoarse) + 1;     // entries 0, kCoarse, 2*kCoarse, ... <= n_rays
-    const uint64_t* off = (const uint64_t*)ctx->offsets.p;
-    SRF_CK(ctx, cudaMemcpy2DAsync(ctx->h_coarse, sizeof(uint64_t), off, kCoarse * sizeof(uint64_t), sizeof(uint64_t),
-                                  n_coarse, cudaMemcpyDeviceToHost, s));
-    SRF_CK(ctx, cudaMemcpyAsync(ctx->h_coarse + n_coarse, off + n_rays, sizeof(uint64_t), cudaMemcpyDeviceToHost, s));
-    SRF_CK(ctx, cudaStreamSynchronize(s));
-    *total = ctx->h_coarse[n_coarse];
     return SRF_OK;
 }
 
@@ -550,7 +528,6 @@ void srf_destroy(srf_ctx* ctx) {
                     ctx->ray_head.p, ctx->d_chunk_cursor, ctx->d_ticket};
     for (void* p : ptrs) if (p) cudaFree(p);
     if (ctx->h_counters) cudaFreeHost(ctx->h_counters);
-    if (ctx->h_coarse) cudaFreeHost(ctx->h_coarse);
     for (int i = 0; i < 8; ++i) if (ctx->ev[i]) cudaEventDestroy(ctx->ev[i]);
     delete ctx;
 }

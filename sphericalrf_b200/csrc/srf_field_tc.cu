@@ -49,8 +49,8 @@ constexpr int kGroup = 128;
 constexpr int kTcBlock = kGroup * kGroups;
 constexpr uint32_t kTmemCols = 64 * kGroups;      // 64 per group: the whole tensor memory of the SM
 constexpr uint32_t kWaitLimit = 1u << 20;
-constexpr int kPair = 1;                          // groups that share one commit round trip per layer: sets of 2 and 4
-                                                  // groups were slower (159.5 and 181.9 ms against 153.1 per benchmark frame)
+// (Sets of two or four groups sharing one commit round trip per layer were slower: 159.5 and 181.9 ms per benchmark
+// frame against 153.1 with every group on its own.)
 
 // shared-memory map (bytes)
 constexpr int kSmW_D1 = 0;                        // [4][64][8]
@@ -88,16 +88,7 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t n) {
     return (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24);
 }
 
-__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-        "}\n"
-        :: "r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// The same with the accumulate flag fixed at compile time (no predicate to compute at run time).
+// tcgen05.mma, kind::f16, one CTA; the accumulate flag is fixed at compile time (no predicate to compute at run time).
 template <bool ACCUMULATE>
 __device__ __forceinline__ void mma_f16_fixed(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
     if (ACCUMULATE)
@@ -172,12 +163,12 @@ __device__ __forceinline__ void store_units(const uint32_t (&acc)[16], unsigned 
 
 // group-local named barriers 1..kGroups (id 0 is __syncthreads)
 __device__ __forceinline__ void group_sync(int group) {
-    asm volatile("bar.sync %0, %1;" :: "r"(group / kPair + 1), "n"(128 * kPair) : "memory");
+    asm volatile("bar.sync %0, 128;" :: "r"(group + 1) : "memory");
 }
 __device__ __forceinline__ bool group_any(int group, bool v) {
     uint32_t r;
-    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.or.pred q, %2, %3, p;\n\tselp.u32 %0, 1, 0, q;\n\t}\n"
-                 : "=r"(r) : "r"((uint32_t)v), "r"(group / kPair + 1), "n"(128 * kPair) : "memory");
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.or.pred q, %2, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}\n"
+                 : "=r"(r) : "r"((uint32_t)v), "r"(group + 1) : "memory");
     return r != 0;
 }
 
@@ -197,7 +188,7 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, warp = tid >> 5;
     const int group = tid >> 7, row = tid & 127;
-    uint64_t* bar_ptr = reinterpret_cast<uint64_t*>(smem + kSmBar) + group / kPair * kPair;   // the set's barrier
+    uint64_t* bar_ptr = reinterpret_cast<uint64_t*>(smem + kSmBar) + group;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kSmBar + kGroups * 8);
     const uint32_t bar = smem_u32(bar_ptr);
 
@@ -219,7 +210,7 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
         d.y = make_desc(b_img + (uint32_t)kk * 2u * n_out * 16u, n_out * 16u, 128u);
         reinterpret_cast<ulonglong2*>(smem + kSmDesc)[tid] = d;
     }
-    if (row == 0 && group % kPair == 0) {
+    if (row == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -251,7 +242,6 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
     const uint32_t tmem_row = tmem_group + ((uint32_t)((warp & 3) * 32) << 16);          // this warp's quarter of the lanes
 
     unsigned char* act = smem + kSmAct + group * kActBytes;
-    const uint32_t act_addr = smem_u32(act);
     constexpr uint32_t kIdesc64 = make_idesc(64), kIdesc16 = make_idesc(16);
 
     // One dense layer: K/16 instructions over the A image in the activation region and the layer's B image.  The
@@ -294,15 +284,13 @@ k_field_network_tc(const NetMeta net, const __half* __restrict__ table, const __
     // barrier of group_any() instead of spending issue slots on a spin loop.
     auto wait_layer = [&]() -> bool {
         bool expired = false;
-        if ((warp & (4 * kPair - 1)) == 0) expired = !mbar_wait(bar, phase);
+        if ((warp & 3) == 0) expired = !mbar_wait(bar, phase);
         phase ^= 1;
         return !group_any(group, expired);
     };
     const uint64_t n_tiles = (n + kGroup - 1) / kGroup;
     const uint64_t tile_stride = (uint64_t)gridDim.x * kGroups;
-    // The groups of a set run the same number of rounds (a group whose tile lies past the end works on zeros).
-    for (uint64_t tile0 = (uint64_t)blockIdx.x * kGroups + group / kPair * kPair; tile0 < n_tiles; tile0 += tile_stride) {
-        const uint64_t tile = tile0 + group % kPair;
+    for (uint64_t tile = (uint64_t)blockIdx.x * kGroups + group; tile < n_tiles; tile += tile_stride) {
         const uint64_t s = tile * kGroup + row;
         // ---- encode: one thread per sample, written as 16-byte units of the A image ----
         float x = 0.f, y = 0.f, z = 0.f, dx = 0.5f, dy = 0.5f, dz = 0.5f;
