@@ -1326,8 +1326,13 @@ srf_status srf_render_frames_sharded(srf_comm* c, const srf_view_t* views, uint3
     };
     {
         std::vector<std::thread> workers;
-        for (uint32_t r = 1; r < n; ++r) workers.emplace_back(enqueue, r);
+        uint32_t started = 1;                       // devices [1, started) have a thread of their own
+        try {
+            for (; started < n; ++started) workers.emplace_back(enqueue, started);
+        } catch (...) {                             // no more threads to be had: this thread does the rest
+        }
         enqueue(0);
+        for (uint32_t r = started; r < n; ++r) enqueue(r);
         for (std::thread& w : workers) w.join();
     }
     for (uint32_t r = 0; r < n; ++r)
