@@ -10,7 +10,7 @@ from sphericalrf_b200 import abi, sharding, synth
 from sphericalrf_b200 import pyngp as ngp
 from sphericalrf_b200.testbed import config_from_json
 
-Testbed = ngp.Testbed
+NgpTestbed = ngp.Testbed
 
 # The structure of experiment/srf_nerfsynthetic/config/srf_lego.json (keys as the reference spells them).
 LEGO = {
@@ -53,13 +53,13 @@ def test_config_errors_use_the_reference_messages():
         config_from_json(bad)
     with pytest.raises(RuntimeError, match="samlper"):
         config_from_json({"sampler": {}})         # the section is spelled "samlper"
-    t = Testbed()
+    t = NgpTestbed()
     with pytest.raises(RuntimeError, match="The model config must exist."):
         t.load_model_config("/nonexistent/config.json")
 
 
 def test_fov_setters_take_radians_and_getters_return_degrees():
-    t = Testbed()
+    t = NgpTestbed()
     t.fov = math.radians(50.0)
     assert abs(t.rendering_buffer.relative_focal_length[0] - 0.5 / math.tan(math.radians(25.0))) < 1e-6
     assert abs(t.fov - 50.0) < 1e-3
@@ -69,7 +69,7 @@ def test_fov_setters_take_radians_and_getters_return_degrees():
 
 
 def test_set_nerf_camera_matrix_convention():
-    t = Testbed()
+    t = NgpTestbed()
     cam = np.array([[1, 0, 0, 0.1], [0, 1, 0, 0.2], [0, 0, 1, 0.3]], np.float32)
     t.set_nerf_camera_matrix(cam)
     want = np.array([[1, 0, 0, 0.6], [0, -1, 0, 0.7], [0, 0, -1, 0.8]], np.float32)
@@ -135,7 +135,7 @@ def test_cpp_json_reader_accepts_what_the_reference_configs_contain(tmp_path):
     assert c.sampling_type == abi.SAMPLING_DISPARITY and c.grid_size == 64 and abs(c.near_distance - 0.1) < 1e-7
     p = tmp_path / "cfg.json"
     p.write_text(text)
-    t = Testbed()
+    t = NgpTestbed()
     try:
         t.load_model_config(str(p))            # parses, then needs a GPU for the context
     except RuntimeError as e:
